@@ -1,0 +1,253 @@
+/* onyxia_cuda.h — C ABI of the B200 execution backend for the Onyxia IR.
+ *
+ * This is the surface a Rust `onyxia-backend-cuda` crate binds to implement
+ * the two traits of the reference unchanged:
+ *
+ *   trait Backend { fn supports(&self,&str)->bool; fn prepare(&self, Module)->Result<Session>; }
+ *   trait Session { fn upload(..); async fn run(..); async fn download(..); }
+ *       — crates/onyxia-ir/src/backend.rs:24-54
+ *
+ * A `Module` (crates/onyxia-ir/src/graph.rs:253-275) crosses the boundary
+ * through the builder calls below, which mirror `GraphBuilder`
+ * (crates/onyxia-ir/src/builder.rs:39-248): primitives are type-inferred as
+ * they are added, composites declare their output types.
+ *
+ * Rules: plain pointers and sizes only; no exceptions cross the boundary;
+ * every fallible call returns an `ox_status` and leaves a message readable
+ * with `ox_last_error()` (per thread). One session is used by one host thread
+ * at a time (`&mut self` in the reference).
+ */
+#ifndef ONYXIA_CUDA_H
+#define ONYXIA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error kinds = the variants of onyxia_ir::Error (crates/onyxia-ir/src/lib.rs:55-89). */
+typedef enum ox_status {
+    OX_OK = 0,
+    OX_ERR_SHAPE = 1,
+    OX_ERR_INVALID_GRAPH = 2,
+    OX_ERR_DTYPE = 3,
+    OX_ERR_ATTRIBUTE = 4,
+    OX_ERR_BINDING = 5,
+    OX_ERR_INTERP = 6,
+    OX_ERR_UNSUPPORTED = 7,
+    OX_ERR_RUNTIME = 8
+} ox_status;
+
+/* Element types (crates/onyxia-ir/src/types.rs:13-26). U4/I4 are bit-packed,
+ * two elements per byte, low nibble first, total rounded up to a byte. */
+typedef enum ox_dtype {
+    OX_F32 = 0, OX_F16, OX_I64, OX_I32, OX_U32, OX_U8, OX_I8, OX_BOOL, OX_U4, OX_I4
+} ox_dtype;
+
+/* Primitive kinds (crates/onyxia-ir/src/prim.rs:130-214), in declaration order. */
+typedef enum ox_prim_kind {
+    OX_PRIM_UNARY = 0, OX_PRIM_BINARY, OX_PRIM_COMPARE, OX_PRIM_SELECT, OX_PRIM_CAST,
+    OX_PRIM_MATMUL, OX_PRIM_REDUCE, OX_PRIM_RESHAPE, OX_PRIM_TRANSPOSE, OX_PRIM_BROADCAST,
+    OX_PRIM_CONCAT, OX_PRIM_SLICE, OX_PRIM_GATHER, OX_PRIM_SCATTER, OX_PRIM_IOTA,
+    OX_PRIM_DIM_VALUES, OX_PRIM_DEQUANTIZE
+} ox_prim_kind;
+
+/* Operator codes for ox_prim_desc.op (crates/onyxia-ir/src/prim.rs:27-107). */
+enum { OX_NEG = 0, OX_ABS, OX_SQRT, OX_RSQRT, OX_EXP, OX_LOG, OX_SIN, OX_COS, OX_TANH, OX_ERF,
+       OX_FLOOR, OX_CEIL, OX_NOT };
+enum { OX_ADD = 0, OX_SUB, OX_MUL, OX_DIV, OX_POW, OX_MAX, OX_MIN, OX_AND, OX_OR, OX_XOR };
+enum { OX_EQ = 0, OX_NE, OX_LT, OX_LE, OX_GT, OX_GE };
+enum { OX_SUM = 0, OX_MEAN, OX_RMAX, OX_RMIN, OX_PROD };
+
+/* A symbolic dimension: sum of terms, each coeff × product of symbols
+ * (crates/onyxia-ir/src/dim.rs:131-162). A constant c is one term with
+ * n_syms = 0; zero is n_terms = 0. Symbols are ids from
+ * ox_module_intern_symbol. */
+#define OX_MAX_TERM_SYMS 6
+typedef struct ox_dimterm {
+    int64_t coeff;
+    int32_t n_syms;
+    int32_t syms[OX_MAX_TERM_SYMS];
+} ox_dimterm;
+
+typedef struct ox_dimexpr {
+    const ox_dimterm* terms;
+    int32_t n_terms;
+} ox_dimexpr;
+
+typedef struct ox_slice_spec {
+    uint64_t axis;
+    ox_dimexpr start; /* inclusive, in the direction of travel */
+    ox_dimexpr end;   /* exclusive */
+    int64_t step;     /* never 0 */
+} ox_slice_spec;
+
+/* Parameters of one primitive; only the fields of `kind` are read. */
+typedef struct ox_prim_desc {
+    int32_t kind;             /* ox_prim_kind */
+    int32_t op;               /* unary / binary / compare / reduce operator */
+    int32_t dtype;            /* Cast target, Iota element type */
+    int32_t trans_a, trans_b; /* MatMul */
+    int32_t keepdims;         /* Reduce */
+    const uint64_t* axes;     /* Reduce axes (sorted) or Transpose perm */
+    int32_t n_axes;
+    const ox_dimexpr* shape;  /* Reshape/Broadcast target, Dequantize out_shape, DimValues exprs */
+    int32_t n_shape;
+    uint64_t axis;            /* Concat / Gather */
+    const ox_slice_spec* specs;
+    int32_t n_specs;
+    ox_dimexpr len;           /* Iota */
+    uint64_t block_size;      /* Dequantize */
+} ox_prim_desc;
+
+/* Composite attribute (crates/onyxia-ir/src/attrs.rs:12-23). */
+typedef enum ox_attr_kind { OX_ATTR_INT = 0, OX_ATTR_INTS, OX_ATTR_FLOAT, OX_ATTR_FLOATS, OX_ATTR_STR, OX_ATTR_BOOL } ox_attr_kind;
+typedef struct ox_attr {
+    const char* name;
+    int32_t kind; /* ox_attr_kind */
+    int64_t i;    /* INT, BOOL */
+    double f;     /* FLOAT */
+    const char* s;
+    const int64_t* ints;
+    const double* floats;
+    int32_t n; /* element count for INTS / FLOATS */
+} ox_attr;
+
+typedef struct ox_tensor_type {
+    int32_t dtype;
+    const ox_dimexpr* dims;
+    int32_t rank;
+} ox_tensor_type;
+
+typedef struct ox_module ox_module;
+typedef struct ox_backend ox_backend;
+typedef struct ox_session ox_session;
+typedef struct ox_tensor ox_tensor;
+
+/* Message of the last failed call on this thread (includes the node name for
+ * execution errors, like crates/onyxia-backend-wgpu/src/session.rs:583-587). */
+const char* ox_last_error(void);
+
+/* ── Module construction ≙ GraphBuilder (crates/onyxia-ir/src/builder.rs) ── */
+ox_module* ox_module_new(void);
+void ox_module_free(ox_module*);
+/* Deep copy of the graph; constant bytes are shared, not copied. */
+ox_module* ox_module_clone(const ox_module*);
+/* ≙ GraphBuilder::sym (builder.rs:69-71). */
+int32_t ox_module_intern_symbol(ox_module*, const char* name);
+/* ≙ GraphBuilder::constant (builder.rs:127-135). With borrow != 0 the bytes
+ * are not copied and must stay valid until the module (and its clones) have
+ * been prepared or freed. */
+ox_status ox_module_add_const(ox_module*, int32_t dtype, const uint64_t* dims, int32_t rank,
+                              const void* bytes, size_t nbytes, int32_t borrow, int32_t* out_value);
+/* ≙ GraphBuilder::input (builder.rs:115-124). */
+ox_status ox_module_add_input(ox_module*, const char* name, int32_t dtype, const ox_dimexpr* dims,
+                              int32_t rank, int32_t* out_value);
+/* ≙ GraphBuilder::prim (builder.rs:152-191): infers the output type. */
+ox_status ox_module_add_prim(ox_module*, const ox_prim_desc*, const int32_t* inputs, int32_t n_in,
+                             int32_t* out_value);
+/* ≙ GraphBuilder::composite (builder.rs:196-234). */
+ox_status ox_module_add_composite(ox_module*, const char* name, const ox_attr* attrs, int32_t n_attrs,
+                                  const int32_t* inputs, int32_t n_in, const ox_tensor_type* outs,
+                                  int32_t n_out, int32_t* out_values);
+/* ≙ GraphBuilder::output (builder.rs:237-242). */
+ox_status ox_module_add_output(ox_module*, const char* name, int32_t value);
+/* ≙ GraphBuilder::constrain (builder.rs:102-112). */
+ox_status ox_module_add_constraint(ox_module*, const ox_dimexpr* left, const ox_dimexpr* right,
+                                   const char* context);
+/* ≙ GraphBuilder::set_loc (builder.rs:79-81); NULL clears. */
+void ox_module_set_loc(ox_module*, const char* node_name, const char* op_type);
+/* ≙ validate::validate (crates/onyxia-ir/src/validate.rs:15). */
+ox_status ox_module_validate(const ox_module*);
+/* ≙ decomp::inline_composites (crates/onyxia-ir/src/decomp.rs:73-133) with
+ * `supports(name) = name ∈ keep`. Rewrites the module in place. */
+ox_status ox_module_inline_composites(ox_module*, const char* const* keep, int32_t n_keep);
+
+/* Introspection used by callers such as LlmSession (crates/onyxia-cli/src/llm.rs:47-61,232-246). */
+int32_t ox_module_num_nodes(const ox_module*);
+int32_t ox_module_num_values(const ox_module*);
+int32_t ox_module_num_inputs(const ox_module*);
+int32_t ox_module_num_outputs(const ox_module*);
+const char* ox_module_input_name(const ox_module*, int32_t i);
+const char* ox_module_output_name(const ox_module*, int32_t i);
+/* dtype and rank of input i. */
+ox_status ox_module_input_desc(const ox_module*, int32_t i, int32_t* dtype, int32_t* rank);
+/* Evaluate input i's declared shape under symbol bindings given by name. */
+ox_status ox_module_eval_input_shape(const ox_module*, int32_t i, const char* const* sym_names,
+                                     const uint64_t* sym_values, int32_t n_syms, uint64_t* out_dims);
+/* Name of node i's operation ("matmul", "com.microsoft.MatMulNBits", …). */
+const char* ox_module_node_op(const ox_module*, int32_t i);
+/* Type of a value rendered as text, e.g. "f16[batch_size, 1, 1152]". The
+ * pointer is valid until the next call on this thread. */
+const char* ox_module_value_type_str(const ox_module*, int32_t value);
+
+/* ── Backend ≙ impl Backend (crates/onyxia-backend-wgpu/src/session.rs:107-242) ── */
+/* Options for ox_backend_create_ex; zero-initialise for defaults. */
+typedef struct ox_backend_options {
+    int32_t without_fused_kernels; /* ≙ WgpuBackend::without_fused_kernels (session.rs:125-134) */
+    int32_t disable_graphs;        /* launch kernels one by one instead of replaying CUDA graphs */
+    int32_t disable_pattern_fusion;/* keep every node its own launch (no cross-node fusion) */
+    int32_t reserved[5];
+} ox_backend_options;
+
+/* One backend per process and device set. `device_ordinals` lists the CUDA
+ * devices (1 entry = single GPU). */
+ox_status ox_backend_create(const int32_t* device_ordinals, int32_t n_devices, ox_backend** out);
+ox_status ox_backend_create_ex(const int32_t* device_ordinals, int32_t n_devices,
+                               const ox_backend_options* options, ox_backend** out);
+void ox_backend_free(ox_backend*);
+/* ≙ Backend::supports (backend.rs:28-31): 1 if a fused kernel is registered under this name. */
+int32_t ox_backend_supports(const ox_backend*, const char* composite_name);
+/* ≙ Backend::prepare (backend.rs:33-34). Consumes `module` (also on failure). */
+ox_status ox_backend_prepare(ox_backend*, ox_module* module, ox_session** out);
+
+/* ── Session ≙ impl Session (backend.rs:37-54; wgpu session.rs:510-649) ── */
+void ox_session_free(ox_session*);
+/* ≙ Session::upload. Host layout = interp::Tensor (crates/onyxia-ir/src/interp.rs:29-49). */
+ox_status ox_session_upload(ox_session*, int32_t dtype, const uint64_t* shape, int32_t rank,
+                            const void* bytes, size_t nbytes, ox_tensor** out);
+/* ≙ Session::run: inputs matched by name against the module signature; all
+ * module outputs are returned in signature order. `out_names[i]` points into
+ * session-owned storage; `out_tensors[i]` are new handles the caller releases. */
+ox_status ox_session_run(ox_session*, const char* const* names, ox_tensor* const* inputs, int32_t n_in,
+                         const char** out_names, ox_tensor** out_tensors, int32_t out_cap, int32_t* n_out);
+/* ≙ Session::download: blocks until the tensor's producer has finished. */
+ox_status ox_session_download(ox_session*, const ox_tensor*, void* dst, size_t cap, size_t* written);
+
+/* Device tensor handles: cheap to clone (≙ `type Tensor: Clone`, backend.rs:41-42). */
+ox_tensor* ox_tensor_clone(const ox_tensor*);
+void ox_tensor_release(ox_tensor*);
+ox_status ox_tensor_describe(const ox_tensor*, int32_t* dtype, uint64_t* shape, int32_t shape_cap, int32_t* rank);
+size_t ox_tensor_nbytes(const ox_tensor*);
+
+/* Inherent session methods of the reference GPU backend
+ * (crates/onyxia-backend-wgpu/src/session.rs:280-340). */
+ox_status ox_session_wait_idle(ox_session*);
+uint64_t ox_session_resident_bytes(const ox_session*);
+uint64_t ox_session_peak_resident_bytes(const ox_session*);
+void ox_session_pool_stats(const ox_session*, uint64_t* fresh_allocations, uint64_t* reuses);
+/* Per-launch device timing ≙ enable_profiling / take_timings
+ * (crates/onyxia-backend-wgpu/src/profile.rs:18-28). */
+typedef struct ox_kernel_timing {
+    const char* kernel; /* kernel label */
+    const char* node;   /* IR node name or op */
+    uint64_t time_ns;
+} ox_kernel_timing;
+int32_t ox_session_enable_profiling(ox_session*, int32_t on);
+/* Copies up to `cap` records; returns the number available. Strings stay valid
+ * until the next take. */
+int32_t ox_session_take_timings(ox_session*, ox_kernel_timing* out, int32_t cap);
+/* Number of kernel launches (graph nodes included) issued since prepare. */
+uint64_t ox_session_launch_count(const ox_session*);
+/* Greedy sampling on the device: index of the maximum over the last axis of
+ * `logits`, highest index among equal maxima (≙ sampling::sample_greedy,
+ * crates/onyxia-cli/src/sampling.rs:71-80, which keeps the last maximum).
+ * Returns an I64 tensor shaped like `logits` without its last axis. */
+ox_status ox_session_argmax_last(ox_session*, const ox_tensor* logits, ox_tensor** out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONYXIA_CUDA_H */
