@@ -1,0 +1,315 @@
+"""Benchmark: decode tokens/s of a Gemma-3-1B-architecture int4 decoder, batch 1.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one greedy decode token after a 512-token seeded prompt (weights are
+random-init, the prompt is synthetic). Prints ONE JSON line:
+
+* ``value``  tokens/s with everything resident on the device: each step's
+  input token is the previous step's on-device argmax, timed with CUDA events
+  on the session's stream.
+* ``e2e``    the same loop through the host-facing calls a user of the
+  reference makes (upload ids + mask → run → download logits → host argmax).
+* ``roofline``  the int4 GEMV kernel: algorithmic bytes per launch ÷ its mean
+  device time (per-launch CUDA events, taken in a separate profiled pass).
+* ``cpu_baseline``  the CPU oracle (a C++ port of the reference interpreter)
+  on the host cores, on a bounded sample of the same workload.
+
+With ``--gpus N`` every rank runs an independent replica (a single KV head
+cannot be sharded); ``value`` is the sum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s (Gemma-3-1B-arch int4, b=1)"
+PROMPT_LEN = 512
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    c = [x.strip() for x in line.split(",")]
+                    if len(c) < 9:
+                        continue
+                    try:
+                        sm.append(float(c[1]))
+                        mx.append(float(c[2]))
+                    except ValueError:
+                        continue
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                        if v.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = float(np.median(sm))
+            out["sm_max_mhz"] = float(max(mx))
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+        return out
+
+
+def build_model(seed=0):
+    from onyxia_b200 import models
+    cfg = models.config_gemma3_1b()
+    t = time.time()
+    module = models.build_decoder(cfg, seed=seed)
+    return cfg, module, time.time() - t
+
+
+def cpu_reference_run(cfg, module, steps, warmup, threads):
+    """The CPU oracle through the same KV loop: a short prefill, then timed decode steps."""
+    from onyxia_b200 import llm
+    from oracle import ref
+    ref.set_threads(threads)
+    s = llm.LlmSession(ref.RefBackend(), module, 4096)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, 4).tolist()
+    logits = s.prefill(prompt)
+    tok = llm.sample_greedy(logits)
+    for _ in range(warmup):
+        tok = llm.sample_greedy(s.decode(tok))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = llm.sample_greedy(s.decode(tok))
+    dt = time.perf_counter() - t0
+    return steps / dt, dt
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    threads = os.cpu_count() or 1
+
+    from onyxia_b200 import build as ox_build
+    ox_build.ensure_built()
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cfg, module, _ = build_model()
+        steps = min(args.steps, 8)  # a bounded sample: each CPU token takes about a second
+        warm = min(args.warmup, 1)
+        tps, dt = cpu_reference_run(cfg, module, steps, warm, threads)
+        line = {"metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+                "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic", "impl": "reference",
+                "config": {"workload": "gemma3-1b-arch int4 block-32, fp16 activations, batch 1, greedy decode",
+                           "prompt_len": 4, "note": "CPU port of onyxia-backend-ref (the Rust interpreter cannot be "
+                                                    "built offline); decode steps after a 4-token prompt"},
+                "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                                 "sample": f"{steps} decode steps after a 4-token prompt"},
+                "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import torch  # plumbing only: rendezvous, barrier, max over ranks
+    import torch.distributed as dist
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from onyxia_b200 import backend as be
+    from onyxia_b200 import ir, llm
+    from onyxia_b200.ir import HostTensor
+
+    cfg, module, build_s = build_model()
+    cpu_module = module.clone() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+    backend = be.CudaBackend((local_rank,))
+    lm = llm.LlmSession(backend, module, 4096)
+    sess = lm.session
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, PROMPT_LEN).tolist()
+    K, W = args.steps, args.warmup
+
+    # ── prefill (untimed), then the device-resident decode loop ──
+    logits = lm.prefill(prompt)
+    first = llm.sample_greedy(logits)
+    kv = dict(lm.kv_cache)
+    past = lm.past_seq_len
+    masks = [sess.upload(HostTensor.from_numpy(np.ones((1, past + i + 1), np.int64))) for i in range(W + K)]
+    tok = sess.upload(HostTensor.from_numpy(np.array([[first]], np.int64)))
+    names = lm.input_names
+
+    def device_step(i, tok, kv):
+        feed = []
+        for n in names:
+            if n == "input_ids":
+                feed.append((n, tok))
+            elif n == "attention_mask":
+                feed.append((n, masks[i]))
+            else:
+                feed.append((n, kv[n]))
+        outs = dict(sess.run(feed))
+        for present, pst in lm.kv_pairs:
+            kv[pst] = outs[present]
+        return sess.argmax_last(outs["logits"])  # [1, 1] i64 = the next step's input_ids
+
+    for i in range(W):
+        tok = device_step(i, tok, kv)
+    sess.wait_idle()
+    launches0 = sess.launch_count()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sess.timer_start()
+    for i in range(W, W + K):
+        tok = device_step(i, tok, kv)
+    ms = sess.timer_stop()
+    clocks = sampler.stop()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    launches = sess.launch_count() - launches0
+    value = world * K / (ms / 1e3)
+
+    # ── end to end through the host-facing calls (ids + mask up, logits down, host argmax) ──
+    lm.kv_cache, lm.past_seq_len = kv, past + W + K
+    host_tok = int(sess.download(tok).numpy().reshape(-1)[0])
+    e2e_steps = min(K, 64)
+    for _ in range(min(W, 3)):
+        host_tok = llm.sample_greedy(lm.decode(host_tok))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        host_tok = llm.sample_greedy(lm.decode(host_tok))
+    e2e_dt = time.perf_counter() - t0
+    e2e_val = world * e2e_steps / e2e_dt
+    ctx = lm.past_seq_len
+    h2d = 8 + 8 * ctx
+    d2h = cfg.vocab * 2
+
+    # ── per-kernel device times for the roofline (profiled pass, per-launch events) ──
+    sess.enable_profiling(True)
+    prof_steps = 4
+    for _ in range(prof_steps):
+        host_tok = llm.sample_greedy(lm.decode(host_tok))
+    timings = sess.take_timings()
+    sess.enable_profiling(False)
+    by_kernel = {}
+    for kname, _node, ns in timings:
+        a = by_kernel.setdefault(kname, [0, 0])
+        a[0] += 1
+        a[1] += ns
+    peak, peak_kind = load_peaks()
+    gemv = by_kernel.get("nbits_gemv", [0, 0])
+    weight_bytes = cfg.weight_bytes_per_token()
+    # activations in and out of the 7 matrices per layer + lm_head, fp16
+    act_bytes = 2 * (cfg.layers * (cfg.hidden * 4 + cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim +
+                                   3 * cfg.ffn + cfg.hidden * 2) + cfg.hidden + cfg.vocab)
+    alg_bytes_per_step = weight_bytes + act_bytes
+    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+                "kernel": "nbits_gemv", "peak_source": peak_kind}
+    if gemv[0]:
+        gemv_s_per_step = gemv[1] / 1e9 / prof_steps
+        roofline["achieved"] = alg_bytes_per_step / gemv_s_per_step / 1e9
+        roofline["frac"] = roofline["achieved"] / peak
+        roofline["launches_per_step"] = gemv[0] / prof_steps
+        roofline["avg_launch_us"] = gemv[1] / gemv[0] / 1e3
+        roofline["algorithmic_bytes_per_launch"] = alg_bytes_per_step / (gemv[0] / prof_steps)
+    kernel_share = {k: {"launches_per_step": v[0] / prof_steps, "us_per_step": v[1] / 1e3 / prof_steps}
+                    for k, v in sorted(by_kernel.items(), key=lambda kv_: -kv_[1][1])}
+
+    cpu = None
+    if cpu_module is not None:
+        try:
+            tps, dt = cpu_reference_run(cfg, cpu_module, 6, 1, threads)
+            cpu = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
+                   "sample": "6 decode steps after a 4-token prompt, same weights"}
+        except Exception as e:  # the baseline is a report, never a reason to lose the measurement
+            cpu = {"value": None, "unit": "tok/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}
+
+    if rank == 0:
+        kv_bytes = cfg.kv_bytes_per_token(past + W + K // 2)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": "gemma3-1b-arch int4 block-32 (26 layers, hidden 1152, 4Q/1KV heads of 256, FFN 6912, "
+                                   "vocab 262144, 5 local(512):1 global), fp16 activations, batch 1, 512-token prompt, "
+                                   "greedy decode", "prompt_len": PROMPT_LEN, "context_at_timing": [past + W, past + W + K],
+                       "replicas": world, "l2_policy": "per-token weights (562 MB) exceed the 126 MB L2",
+                       "norms": "pre + post (sandwich) RMSNorm per block, no q/k norm"},
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "path": "upload(ids, mask) → run → download(logits) → host argmax"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "model_roofline": {"bytes_per_token": weight_bytes + kv_bytes, "tok_s_at_peak": peak * 1e9 / (weight_bytes + kv_bytes),
+                               "frac": value / world / (peak * 1e9 / (weight_bytes + kv_bytes))},
+            "kernels": kernel_share, "resident_bytes": sess.resident_bytes(), "model_build_s": build_s,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -239,6 +239,11 @@ int32_t ox_session_enable_profiling(ox_session*, int32_t on);
 /* Copies up to `cap` records; returns the number available. Strings stay valid
  * until the next take. */
 int32_t ox_session_take_timings(ox_session*, ox_kernel_timing* out, int32_t cap);
+/* Device-side stopwatch on the session's stream: `start` records an event
+ * behind the work queued so far, `stop` records a second one, waits for it and
+ * returns the elapsed milliseconds between the two. */
+ox_status ox_session_timer_start(ox_session*);
+ox_status ox_session_timer_stop(ox_session*, float* elapsed_ms);
 /* Number of kernel launches (graph nodes included) issued since prepare. */
 uint64_t ox_session_launch_count(const ox_session*);
 /* Greedy sampling on the device: index of the maximum over the last axis of

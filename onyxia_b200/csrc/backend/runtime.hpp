@@ -1,0 +1,146 @@
+// Host runtime of the CUDA backend: device tensors, the buffer pool, the
+// fused-kernel registry, the session (prepare / upload / run / download).
+//
+// Behavioural model: the reference GPU backend's session
+// (crates/onyxia-backend-wgpu/src/session.rs:137-242 prepare, :532-611 run,
+// gpu.rs:400-448 pool), rewritten around CUDA streams and graphs.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../ir/ir.hpp"
+#include "../kernels/kernels.hpp"
+
+namespace oxrt {
+
+using ox::DType;
+using ox::Module;
+using ox::Node;
+using ox::ValueId;
+
+[[noreturn]] void cuda_fail(cudaError_t e, const char* what);
+#define OX_CUDA(expr)                                   \
+    do {                                                \
+        cudaError_t _e = (expr);                        \
+        if (_e != cudaSuccess) ::oxrt::cuda_fail(_e, #expr); \
+    } while (0)
+
+class Pool;
+
+// A device allocation, returned to its pool when the last reference goes.
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    Pool* pool = nullptr;
+    // For KV-cache buffers: rows written so far per head (−1 = not a cache).
+    // Only the view that ends at this row may be appended to in place.
+    int64_t kv_rows = -1;
+    ~DeviceBuffer();
+};
+using BufferRef = std::shared_ptr<DeviceBuffer>;
+
+// Size-bucketed caching allocator with live/peak accounting
+// (≙ BufferPool + MemCounter, gpu.rs:266-448). Buffers are recycled only once
+// nothing references them; all work of a session is ordered on one stream, so
+// a recycled buffer is never written before its previous readers ran.
+class Pool {
+public:
+    explicit Pool(int device) : device_(device) {}
+    ~Pool();
+    BufferRef alloc(size_t bytes);
+    void release(void* ptr, size_t bytes);
+    void trim();
+    uint64_t live_bytes() const { return live_; }
+    uint64_t peak_bytes() const { return peak_; }
+    uint64_t fresh_allocations = 0, reuses = 0;
+
+private:
+    int device_;
+    std::multimap<size_t, void*> free_;
+    std::unordered_map<void*, size_t> real_size_;
+    uint64_t live_ = 0, peak_ = 0, cached_ = 0;
+};
+
+// A device-resident tensor handle (≙ GpuTensor, session.rs:23-30).
+struct DTensor {
+    DType dtype = DType::F32;
+    std::vector<int64_t> shape;
+    BufferRef buf;
+    size_t offset = 0;
+    // Rows per head the buffer has room for when this is a KV cache
+    // [B, KV, T, D] with T ≤ cap; 0 = densely packed.
+    int64_t cap = 0;
+    int64_t numel() const {
+        int64_t n = 1;
+        for (auto d : shape) n *= d;
+        return n;
+    }
+    size_t nbytes() const { return ox::dtype_storage_bytes(dtype, (uint64_t)numel()); }
+    void* ptr() const { return buf ? (char*)buf->ptr + offset : nullptr; }
+};
+
+struct Options {
+    bool without_fused = false;
+    bool disable_graphs = false;
+    bool disable_pattern_fusion = false;
+};
+
+class Session;
+
+// What a fused kernel sees when it is lowered for one concrete binding.
+struct FusedCtx {
+    oxk::Emitter& em;
+    const Node& node;
+    const std::vector<oxk::TRef>& ins;
+    const std::vector<oxk::TRef>& outs;
+    bool kv_in_place = false;
+};
+
+// A hand-written kernel for one composite (≙ CompositeKernel, fused.rs:27-41).
+struct FusedKernel {
+    std::string name;
+    // Whether this node's operand types are ones the kernel handles; other
+    // instances of the composite fall back to the decomposition.
+    bool (*accepts)(const Module&, const Node&);
+    void (*lower)(FusedCtx&);
+};
+
+// ≙ KernelRegistry / standard_kernels (fused.rs:43-86).
+class KernelRegistry {
+public:
+    void add(FusedKernel k) { map_[k.name] = std::move(k); }
+    bool contains(const std::string& name) const { return map_.count(name) > 0; }
+    const FusedKernel* get(const std::string& name) const {
+        auto it = map_.find(name);
+        return it == map_.end() ? nullptr : &it->second;
+    }
+
+private:
+    std::unordered_map<std::string, FusedKernel> map_;
+};
+const KernelRegistry& standard_kernels();
+
+struct Timing {
+    std::string kernel, node;
+    uint64_t time_ns;
+};
+
+class Backend {
+public:
+    Backend(std::vector<int> devices, Options opt);
+    bool supports(const std::string& name) const { return !opt_.without_fused && standard_kernels().contains(name); }
+    std::unique_ptr<Session> prepare(Module m);
+    const Options& options() const { return opt_; }
+    int device() const { return devices_[0]; }
+
+private:
+    std::vector<int> devices_;
+    Options opt_;
+};
+
+}  // namespace oxrt

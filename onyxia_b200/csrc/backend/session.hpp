@@ -1,0 +1,124 @@
+// The prepared session: plans (one per binding of the dimension symbols),
+// their execution, and the host<->device boundary.
+#pragma once
+#include <list>
+
+#include "runtime.hpp"
+
+namespace oxrt {
+
+// Where a value's bytes live while a plan runs.
+struct ValueLoc {
+    enum Kind : uint8_t { None, Arena, Const, Input, Output, Alias } kind = None;
+    uint32_t index = 0;   // Input: position in module.inputs; Output: position in Plan::out_bufs; Alias: root value
+    size_t offset = 0;    // Arena: byte offset; Alias: byte offset into the root
+};
+
+// One output buffer a run has to provide (several module outputs may share it).
+struct OutBuf {
+    size_t bytes = 0;
+    int alias_input = -1;  // ≥ 0: the buffer of that module input is reused (in-place KV append)
+    int64_t kv_cap = 0;    // rows per head for a freshly allocated KV cache
+    int64_t kv_rows = -1;  // rows valid after this run (KV caches)
+};
+
+struct OutSpec {
+    std::string name;
+    ValueId value;
+    DType dtype;
+    std::vector<int64_t> shape;
+    int64_t cap = 0;
+};
+
+// Everything needed to execute the module for one binding of the symbols.
+struct Plan {
+    std::vector<uint64_t> key;
+    std::vector<oxk::LaunchRec> recs;
+    std::vector<ValueLoc> loc;                   // per value
+    std::vector<std::vector<int64_t>> shapes;    // per value, concrete
+    std::vector<OutBuf> out_bufs;
+    std::vector<OutSpec> outputs;                // module outputs, signature order
+    size_t arena_bytes = 0, scratch_bytes = 0;
+    BufferRef arena;                             // arena + scratch, owned by the plan
+    // CUDA graph of the launch list, with the parameter bytes it currently holds.
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<cudaGraphNode_t> graph_nodes;
+    std::vector<std::vector<uint8_t>> graph_params;
+    uint64_t uses = 0;
+    ~Plan();
+};
+
+class Session {
+public:
+    Session(Backend& backend, Module legalized);
+    ~Session();
+
+    DTensor upload(DType dtype, const std::vector<int64_t>& shape, const void* bytes, size_t nbytes);
+    std::vector<std::pair<std::string, DTensor>> run(const std::vector<std::pair<std::string, DTensor>>& inputs);
+    void download(const DTensor& t, void* dst, size_t cap, size_t* written);
+    DTensor argmax_last(const DTensor& logits);
+    void wait_idle();
+    void timer_start();
+    float timer_stop();
+
+    uint64_t resident_bytes() const { return pool_.live_bytes(); }
+    uint64_t peak_resident_bytes() const { return pool_.peak_bytes(); }
+    const Pool& pool() const { return pool_; }
+    bool profiling = false;
+    std::vector<Timing> timings;
+    uint64_t launch_count = 0;
+    const Module& module() const { return module_; }
+    const std::vector<std::string>& output_names() const { return output_names_; }
+
+private:
+    struct NodeInfo {
+        const FusedKernel* fused = nullptr;
+        // Pattern fusion: this node's work is done by `absorbed_by`'s kernel.
+        int absorbed_by = -1;
+        int fuse_with = -1;  // the partner node this node's kernel also covers
+        int fuse_kind = 0;
+        std::string label;
+    };
+    enum { FUSE_NONE = 0, FUSE_GEGLU = 1, FUSE_ADD_NORM = 2 };
+
+    void upload_constants();
+    void analyse();
+    void find_pattern_fusions();
+    std::unique_ptr<Plan> build_plan(const ox::Bindings& bindings, const std::vector<DTensor>& inputs,
+                                     const std::vector<char>& kv_in_place);
+    void lower_node(Plan& plan, oxk::Emitter& em, ox::NodeId nid, ox::Bindings& bindings,
+                    const std::vector<DTensor>& inputs, const std::vector<char>& kv_in_place,
+                    std::vector<oxk::TRef>& trefs);
+    void lower_prim(oxk::Emitter& em, const Node& node, const ox::Bindings& b, const std::vector<oxk::TRef>& ins,
+                    const std::vector<oxk::TRef>& outs);
+    void execute(Plan& plan, const std::vector<DTensor>& inputs, std::vector<BufferRef>& out_bufs);
+    void check_device_error();
+    DTensor dense_copy(const DTensor& t);
+
+    Backend& backend_;
+    Options opt_;
+    int device_;
+    cudaStream_t stream_ = nullptr;
+    Pool pool_;
+    Module module_;
+    std::vector<ox::NodeId> order_;
+    std::vector<int> step_of_node_;
+    std::vector<NodeInfo> info_;            // per node
+    std::vector<ValueId> alias_root_;       // per value (itself when not an alias)
+    std::vector<int> last_use_;             // per root value: last step reading it (−1 never, INT_MAX output)
+    std::vector<std::vector<ValueId>> deaths_;  // per step: roots that die after it
+    std::vector<DTensor> consts_;           // per value (empty unless Origin::Const)
+    std::vector<int> input_index_;          // per value: position in module.inputs or −1
+    std::vector<char> is_output_root_;      // per value
+    std::vector<char> input_needs_dense_;   // per module input
+    std::vector<int> gqa_past_input_[2];    // per node: module-input index feeding past_k / past_v in place, or −1
+    std::vector<std::string> output_names_;
+    oxk::ErrWord* d_err_ = nullptr;
+    oxk::ErrWord* h_err_ = nullptr;
+    bool err_pending_ = false;
+    std::list<std::unique_ptr<Plan>> plans_;  // most recently used first
+    cudaEvent_t ev_a_ = nullptr, ev_b_ = nullptr, ev_t0_ = nullptr, ev_t1_ = nullptr;
+};
+
+}  // namespace oxrt

@@ -1,0 +1,192 @@
+// Host-side interface to the CUDA kernels: one `emit_*` function per kernel
+// family. An emit function does not launch; it appends launch records
+// ({function, grid, block, shared memory, parameter bytes, pointer
+// relocations}) to an Emitter. The session replays the records — directly, or
+// as nodes of a CUDA graph — after patching pointer fields with the current
+// buffer addresses.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <algorithm>
+#include <cmath>
+#include <initializer_list>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace oxk {
+
+// Error codes written to the error word (first writer wins).
+enum : int {
+    ERR_NONE = 0,
+    ERR_GATHER_OOB = 1,
+    ERR_SCATTER_OOB = 2,
+    ERR_INT_DIV_ZERO = 3,
+    ERR_INT_POW_NEG = 4,
+    ERR_SLICE_OOB = 5,
+    ERR_WAIT_TIMEOUT = 6,
+};
+
+struct ErrWord {
+    int code;
+    int node;      // launch tag (IR node index)
+    long long a;   // offending value
+    long long b;   // bound
+};
+
+// A device address known only at execution time: a runtime value slot plus a
+// byte offset into it.
+struct Buf {
+    uint32_t slot = 0xFFFFFFFFu;
+    int64_t off = 0;
+    Buf at(int64_t bytes) const { return Buf{slot, off + bytes}; }
+    bool valid() const { return slot != 0xFFFFFFFFu; }
+};
+// Reserved slots resolved by the session.
+constexpr uint32_t kSlotErr = 0xFFFFFFF0u;      // the session's ErrWord
+constexpr uint32_t kSlotScratch = 0xFFFFFFF1u;  // the plan's scratch area (offset = position in it)
+constexpr uint32_t kSlotNull = 0xFFFFFFF2u;     // resolves to nullptr
+
+struct Reloc {
+    uint32_t field_off;  // byte offset of a pointer field inside the parameter struct
+    Buf buf;
+};
+
+struct LaunchRec {
+    const void* func = nullptr;
+    dim3 grid{1, 1, 1}, block{1, 1, 1};
+    unsigned smem = 0;
+    std::vector<uint8_t> params;
+    std::vector<Reloc> relocs;
+    const char* label = "";
+    int node = -1;  // IR node index, for error messages and profiling
+};
+
+class Emitter {
+public:
+    std::vector<LaunchRec> recs;
+    int node = -1;
+    size_t scratch_bytes = 0;  // high-water mark of scratch requested by this plan
+
+    // Reserve `bytes` of scratch that lives for the duration of one node.
+    Buf scratch(size_t bytes, size_t align = 256) {
+        size_t off = (scratch_cursor_ + align - 1) / align * align;
+        scratch_cursor_ = off + bytes;
+        if (scratch_cursor_ > scratch_bytes) scratch_bytes = scratch_cursor_;
+        return Buf{kSlotScratch, (int64_t)off};
+    }
+    void begin_node(int n) {
+        node = n;
+        scratch_cursor_ = 0;
+    }
+
+    template <class P>
+    void launch(void (*kernel)(const P), dim3 grid, dim3 block, unsigned smem, const P& p,
+                std::initializer_list<std::pair<const void*, Buf>> ptrs, const char* label) {
+        static_assert(sizeof(P) <= 4000, "kernel parameter struct too large");
+        LaunchRec r;
+        r.func = (const void*)kernel;
+        r.grid = grid;
+        r.block = block;
+        r.smem = smem;
+        r.params.resize(sizeof(P));
+        std::memcpy(r.params.data(), &p, sizeof(P));
+        for (auto& pr : ptrs) {
+            Reloc rl;
+            rl.field_off = (uint32_t)((const char*)pr.first - (const char*)&p);
+            rl.buf = pr.second;
+            r.relocs.push_back(rl);
+        }
+        r.label = label;
+        r.node = node;
+        recs.push_back(std::move(r));
+    }
+
+private:
+    size_t scratch_cursor_ = 0;
+};
+
+// A tensor operand at lowering time: symbolic address, dtype code, concrete dims.
+struct TRef {
+    Buf buf;
+    int dtype = 0;
+    std::vector<int64_t> shape;
+    // Physical row capacity of axis 2 for KV-cache tensors ([B, KV, T, D] whose
+    // buffer holds `cap` rows per head); 0 = densely packed.
+    int64_t cap = 0;
+    int64_t numel() const {
+        int64_t n = 1;
+        for (auto d : shape) n *= d;
+        return n;
+    }
+};
+
+inline unsigned grid_for(int64_t n, int block, int64_t max_blocks = 148 * 16) {
+    int64_t g = (n + block - 1) / block;
+    if (g < 1) g = 1;
+    if (g > max_blocks) g = max_blocks;
+    return (unsigned)g;
+}
+
+// ── primitives (one kernel family per IR primitive) ─────────────────────
+void emit_unary(Emitter&, int op, const TRef& x, const TRef& y);
+void emit_binary(Emitter&, int op, const TRef& a, const TRef& b, const TRef& y);
+void emit_compare(Emitter&, int op, const TRef& a, const TRef& b, const TRef& y);
+void emit_select(Emitter&, const TRef& c, const TRef& a, const TRef& b, const TRef& y);
+void emit_cast(Emitter&, const TRef& x, const TRef& y);
+void emit_matmul(Emitter&, const TRef& a, const TRef& b, const TRef& y, bool trans_a, bool trans_b);
+void emit_reduce(Emitter&, int op, const TRef& x, const TRef& y, const std::vector<size_t>& axes);
+void emit_reshape_copy(Emitter&, const TRef& x, const TRef& y);
+void emit_transpose(Emitter&, const TRef& x, const TRef& y, const std::vector<size_t>& perm);
+void emit_broadcast(Emitter&, const TRef& x, const TRef& y);
+void emit_concat(Emitter&, const std::vector<TRef>& xs, const TRef& y, size_t axis);
+void emit_slice(Emitter&, const TRef& x, const TRef& y, const std::vector<int64_t>& starts,
+                const std::vector<int64_t>& steps);
+void emit_gather(Emitter&, const TRef& data, const TRef& idx, const TRef& y, size_t axis);
+void emit_scatter(Emitter&, const TRef& data, const TRef& idx, const TRef& upd, const TRef& y);
+void emit_iota(Emitter&, const TRef& y);
+void emit_dim_values(Emitter&, const std::vector<int64_t>& vals, const TRef& y);
+void emit_dequantize(Emitter&, const TRef& q, const TRef& scales, const TRef* zp, const TRef& y, int64_t block_size);
+
+// ── fused composites ────────────────────────────────────────────────────
+void emit_softmax(Emitter&, const TRef& x, const TRef& y);  // last axis
+// y = x · rsqrt(mean(x²) + eps) · w over the last axis; with `res` the input is
+// x + res and the sum is also written to `sum_out`.
+void emit_rmsnorm(Emitter&, const TRef& x, const TRef& w, const TRef& y, double eps, const TRef* res,
+                  const TRef* sum_out);
+void emit_gelu(Emitter&, const TRef& x, const TRef& y, bool tanh_approx, const TRef* mul);  // optional ·mul (GeGLU)
+void emit_rotary(Emitter&, const TRef& x, const TRef& pos, const TRef& cos, const TRef& sin, const TRef& y,
+                 int64_t heads, int64_t half);
+
+struct GqaDesc {
+    int64_t batch, seq, heads, kv_heads, head_dim, past;  // past = P (logical rows of the past tensors)
+    double scale;
+    int64_t window;        // -1 = none
+    int64_t rot_half;      // 0 = no rotary
+    int64_t cache_rows;    // rows of cos/sin
+    bool has_bias;
+    int64_t bias_b, bias_h;  // bias batch/head extents (1 = broadcast)
+    bool in_place;         // present aliases past: only new rows are written
+};
+void emit_gqa(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef& v, const TRef& past_k,
+              const TRef& past_v, const TRef& seqlens, const TRef* cos, const TRef* sin, const TRef* bias,
+              const TRef& out, const TRef& present_k, const TRef& present_v);
+
+struct NBitsDesc {
+    int64_t m, k, n, block_size, n_blocks;
+    int act_dtype, scale_dtype;
+    bool has_zp;
+};
+// y[m, n] = a[m, :] · dequant(w)[n, :]ᵀ for packed u4 weights [N, n_blocks, bs].
+void emit_matmul_nbits(Emitter&, const NBitsDesc&, const TRef& a, const TRef& w, const TRef& scales,
+                       const TRef* zp, const TRef& y);
+
+// argmax over the last axis, highest index among equal maxima → i64.
+void emit_argmax_last(Emitter&, const TRef& x, const TRef& y);
+
+// Clear the error word (one tiny launch at the head of a plan is not needed:
+// the session clears it with a memset when it reads it).
+}  // namespace oxk
