@@ -116,6 +116,7 @@ SIGNATURES = {
     "ox_session_timer_start": (C.c_int32, [_P]),
     "ox_session_timer_stop": (C.c_int32, [_P, C.POINTER(C.c_float)]),
     "ox_session_launch_count": (C.c_uint64, [_P]),
+    "ox_session_plan_stats": (None, [_P, _u64p]),
     "ox_session_argmax_last": (C.c_int32, [_P, _P, C.POINTER(_P)]),
 }
 

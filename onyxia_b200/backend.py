@@ -130,6 +130,11 @@ class CudaSession:
         check(self._lib.ox_session_timer_stop(self._h, C.byref(ms)))
         return ms.value
 
+    def plan_stats(self) -> dict:
+        out = (C.c_uint64 * 5)()
+        self._lib.ox_session_plan_stats(self._h, out)
+        return dict(zip(("built", "updated", "reused", "graph_launches", "graph_node_updates"), [int(v) for v in out]))
+
     def launch_count(self) -> int:
         return self._lib.ox_session_launch_count(self._h)
 

@@ -157,9 +157,11 @@ int32_t ox_session_enable_profiling(ox_session* s, int32_t on) {
 }
 
 int32_t ox_session_take_timings(ox_session* s, ox_kernel_timing* out, int32_t cap) {
-    cudaDeviceSynchronize();
-    s->taken = std::move(s->s->timings);
-    s->s->timings.clear();
+    try {
+        s->taken = s->s->take_timings();
+    } catch (const std::exception&) {
+        s->taken.clear();
+    }
     int n = (int)s->taken.size();
     for (int i = 0; i < n && i < cap; i++) {
         out[i].kernel = s->taken[i].kernel.c_str();
@@ -184,6 +186,14 @@ ox_status ox_session_timer_stop(ox_session* s, float* elapsed_ms) {
 }
 
 uint64_t ox_session_launch_count(const ox_session* s) { return s->s->launch_count; }
+
+void ox_session_plan_stats(const ox_session* s, uint64_t out[5]) {
+    out[0] = s->s->plans_built;
+    out[1] = s->s->plans_updated;
+    out[2] = s->s->plans_reused;
+    out[3] = s->s->graph_launches;
+    out[4] = s->s->graph_node_updates;
+}
 
 ox_status ox_session_argmax_last(ox_session* s, const ox_tensor* logits, ox_tensor** out) {
     OX_TRY

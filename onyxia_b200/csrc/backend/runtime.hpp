@@ -36,7 +36,8 @@ class Pool;
 struct DeviceBuffer {
     void* ptr = nullptr;
     size_t bytes = 0;
-    Pool* pool = nullptr;
+    // Shared ownership: a tensor handle may outlive the session that made it.
+    std::shared_ptr<Pool> pool;
     // For KV-cache buffers: rows written so far per head (−1 = not a cache).
     // Only the view that ends at this row may be appended to in place.
     int64_t kv_rows = -1;
@@ -48,7 +49,7 @@ using BufferRef = std::shared_ptr<DeviceBuffer>;
 // (≙ BufferPool + MemCounter, gpu.rs:266-448). Buffers are recycled only once
 // nothing references them; all work of a session is ordered on one stream, so
 // a recycled buffer is never written before its previous readers ran.
-class Pool {
+class Pool : public std::enable_shared_from_this<Pool> {
 public:
     explicit Pool(int device) : device_(device) {}
     ~Pool();
@@ -99,6 +100,8 @@ struct FusedCtx {
     const std::vector<oxk::TRef>& ins;
     const std::vector<oxk::TRef>& outs;
     bool kv_in_place = false;
+    // MatMulNBits: the weight constant (input 1) holds the interleaved layout.
+    bool weights_interleaved = false;
 };
 
 // A hand-written kernel for one composite (≙ CompositeKernel, fused.rs:27-41).

@@ -11,7 +11,7 @@ namespace oxrt {
 struct ValueLoc {
     enum Kind : uint8_t { None, Arena, Const, Input, Output, Alias } kind = None;
     uint32_t index = 0;   // Input: position in module.inputs; Output: position in Plan::out_bufs; Alias: root value
-    size_t offset = 0;    // Arena: byte offset; Alias: byte offset into the root
+    size_t offset = 0;    // Arena: byte offset
 };
 
 // One output buffer a run has to provide (several module outputs may share it).
@@ -31,20 +31,31 @@ struct OutSpec {
 };
 
 // Everything needed to execute the module for one binding of the symbols.
+//
+// A plan is a flat list of launch records. Pointers inside the records are
+// symbolic (value slot + offset) and are resolved against the current buffers
+// at every run, so the same plan serves any set of input/output buffers. When
+// only some dimension symbols change between runs (a decode loop: the KV
+// length grows by one), the plan is updated in place: only the nodes whose
+// types mention a changed symbol are lowered again.
 struct Plan {
-    std::vector<uint64_t> key;
+    std::vector<uint64_t> structure;             // what must match exactly (caps, in-place flags)
+    ox::Bindings bindings;
     std::vector<oxk::LaunchRec> recs;
+    std::vector<std::pair<uint32_t, uint32_t>> node_recs;  // per node: [begin, count) in recs
     std::vector<ValueLoc> loc;                   // per value
-    std::vector<std::vector<int64_t>> shapes;    // per value, concrete
+    std::vector<oxk::TRef> trefs;                // per value
+    std::vector<size_t> arena_size;              // per value (Arena values)
     std::vector<OutBuf> out_bufs;
     std::vector<OutSpec> outputs;                // module outputs, signature order
-    size_t arena_bytes = 0, scratch_bytes = 0;
+    size_t arena_bytes = 0, scratch_bytes = 0, scratch_capacity = 0;
     BufferRef arena;                             // arena + scratch, owned by the plan
-    // CUDA graph of the launch list, with the parameter bytes it currently holds.
+    // CUDA graph of the launch list, with the launch state each node currently holds.
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     std::vector<cudaGraphNode_t> graph_nodes;
     std::vector<std::vector<uint8_t>> graph_params;
+    std::vector<dim3> graph_grids;
     uint64_t uses = 0;
     ~Plan();
 };
@@ -61,13 +72,15 @@ public:
     void wait_idle();
     void timer_start();
     float timer_stop();
+    std::vector<Timing> take_timings();
 
-    uint64_t resident_bytes() const { return pool_.live_bytes(); }
-    uint64_t peak_resident_bytes() const { return pool_.peak_bytes(); }
-    const Pool& pool() const { return pool_; }
+    uint64_t resident_bytes() const { return pool_->live_bytes(); }
+    uint64_t peak_resident_bytes() const { return pool_->peak_bytes(); }
+    const Pool& pool() const { return *pool_; }
     bool profiling = false;
-    std::vector<Timing> timings;
     uint64_t launch_count = 0;
+    // planner statistics: plans built from scratch, updated in place, reused as they were
+    uint64_t plans_built = 0, plans_updated = 0, plans_reused = 0, graph_node_updates = 0, graph_launches = 0;
     const Module& module() const { return module_; }
     const std::vector<std::string>& output_names() const { return output_names_; }
 
@@ -79,20 +92,32 @@ private:
         int fuse_with = -1;  // the partner node this node's kernel also covers
         int fuse_kind = 0;
         std::string label;
+        std::vector<ox::SymId> syms;  // symbols the node's lowering depends on
     };
     enum { FUSE_NONE = 0, FUSE_GEGLU = 1, FUSE_ADD_NORM = 2 };
 
     void upload_constants();
+    void interleave_weights();
+    void launch_now(const oxk::Emitter& em, const std::vector<void*>& slots);
     void analyse();
     void find_pattern_fusions();
+    void collect_node_syms();
+
+    std::vector<uint64_t> structure_key(const std::vector<DTensor>& inputs, const std::vector<char>& kv_in_place) const;
     std::unique_ptr<Plan> build_plan(const ox::Bindings& bindings, const std::vector<DTensor>& inputs,
                                      const std::vector<char>& kv_in_place);
-    void lower_node(Plan& plan, oxk::Emitter& em, ox::NodeId nid, ox::Bindings& bindings,
-                    const std::vector<DTensor>& inputs, const std::vector<char>& kv_in_place,
-                    std::vector<oxk::TRef>& trefs);
+    bool update_plan(Plan& plan, const ox::Bindings& bindings, const std::vector<DTensor>& inputs,
+                     const std::vector<char>& kv_in_place);
+    // Shapes, storage and launch records of one node. With `arena` set the
+    // node's outputs are placed (full build); without, their placement is kept
+    // and the call reports false if a size no longer fits (in-place update).
+    bool lower_step(Plan& plan, oxk::Emitter& em, size_t step, ox::Bindings& bindings, const std::vector<DTensor>& inputs,
+                    const std::vector<char>& kv_in_place, void* arena);
     void lower_prim(oxk::Emitter& em, const Node& node, const ox::Bindings& b, const std::vector<oxk::TRef>& ins,
                     const std::vector<oxk::TRef>& outs);
+    void finish_outputs(Plan& plan);
     void execute(Plan& plan, const std::vector<DTensor>& inputs, std::vector<BufferRef>& out_bufs);
+    void build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& params);
     void check_device_error();
     DTensor dense_copy(const DTensor& t);
 
@@ -100,15 +125,17 @@ private:
     Options opt_;
     int device_;
     cudaStream_t stream_ = nullptr;
-    Pool pool_;
+    std::shared_ptr<Pool> pool_;
     Module module_;
     std::vector<ox::NodeId> order_;
     std::vector<int> step_of_node_;
     std::vector<NodeInfo> info_;            // per node
     std::vector<ValueId> alias_root_;       // per value (itself when not an alias)
-    std::vector<int> last_use_;             // per root value: last step reading it (−1 never, INT_MAX output)
+    std::vector<int> last_use_;             // per root value: last step reading it
     std::vector<std::vector<ValueId>> deaths_;  // per step: roots that die after it
     std::vector<DTensor> consts_;           // per value (empty unless Origin::Const)
+    std::vector<char> interleaved_;         // per value: u4 weight constant re-laid out for the tensor-core GEMV
+    unsigned* d_counters_ = nullptr;        // kCounterWords zeroed arrival counters
     std::vector<int> input_index_;          // per value: position in module.inputs or −1
     std::vector<char> is_output_root_;      // per value
     std::vector<char> input_needs_dense_;   // per module input
@@ -118,7 +145,16 @@ private:
     oxk::ErrWord* h_err_ = nullptr;
     bool err_pending_ = false;
     std::list<std::unique_ptr<Plan>> plans_;  // most recently used first
-    cudaEvent_t ev_a_ = nullptr, ev_b_ = nullptr, ev_t0_ = nullptr, ev_t1_ = nullptr;
+    cudaEvent_t ev_t0_ = nullptr, ev_t1_ = nullptr;
+    // profiling: one event pair per launch, read back in take_timings
+    struct ProfRec {
+        cudaEvent_t a, b;
+        const char* kernel;
+        int node;
+    };
+    std::vector<ProfRec> prof_;
+    std::vector<cudaEvent_t> prof_free_;
+    cudaEvent_t prof_event();
 };
 
 }  // namespace oxrt

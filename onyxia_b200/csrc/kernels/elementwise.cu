@@ -309,6 +309,10 @@ struct CastP {
     long long n;
 };
 
+// Rust `as i64` on a float: saturating, NaN → 0 (the hardware conversion
+// saturates too but maps NaN to INT64_MIN).
+__device__ __forceinline__ long long f2ll(float v) { return isnan(v) ? 0ll : (long long)v; }
+
 // Working-domain conversion (interp.rs:210-279): float→int saturates (NaN→0)
 // then wraps to the target width; int→float goes through f64; →bool is != 0.
 template <int SRC, int DST> __device__ __forceinline__ void cast_one(const void* x, void* y, long long i, long long o) {
@@ -323,7 +327,7 @@ template <int SRC, int DST> __device__ __forceinline__ void cast_one(const void*
         if constexpr (DST == DT_F32) ((float*)y)[o] = v;
         else if constexpr (DST == DT_F16) ((__half*)y)[o] = __float2half_rn(v);
         else if constexpr (DST == DT_BOOL) ((unsigned char*)y)[o] = (v != 0.0f) ? 1 : 0;
-        else st<DST>(y, o, (long long)v);  // cvt.rzi.s64.f32 saturates, NaN → 0
+        else st<DST>(y, o, f2ll(v));
     } else if constexpr (SRC == DT_BOOL) {
         bool v = ld<SRC>(x, i);
         if constexpr (DST == DT_F32) ((float*)y)[o] = v ? 1.f : 0.f;
@@ -354,7 +358,7 @@ template <int SRC> __global__ void prim_cast_pack4(const CastP p) {
             long long v;
             if constexpr (SRC == DT_U4) v = ld_u4(p.x, i);
             else if constexpr (SRC == DT_I4) v = ld_i4(p.x, i);
-            else if constexpr (Ty<SRC>::is_float) v = (long long)ld<SRC>(p.x, i);
+            else if constexpr (Ty<SRC>::is_float) v = f2ll(ld<SRC>(p.x, i));
             else v = (long long)ld<SRC>(p.x, i);
             out |= (unsigned char)(((unsigned)v & 0xF) << (4 * h));
         }

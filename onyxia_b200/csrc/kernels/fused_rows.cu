@@ -17,6 +17,27 @@ template <int DT> __device__ __forceinline__ float rnd(float v) {
     if constexpr (DT == DT_F16) return __half2float(__float2half_rn(v));
     else return v;
 }
+// Round an f64 value to the tensor dtype in one step.
+template <int DT> __device__ __forceinline__ float rnd_d(double v) {
+    if constexpr (DT == DT_F16) return __half2float(__double2half(v));
+    else return (float)v;
+}
+// Block-wide f64 sum (the interpreter reduces in f64); `red` is 32 doubles of shared memory.
+__device__ __forceinline__ double block_sum_d(double v, double* red) {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int k = 0; k < nw; k++) t += red[k];
+        red[0] = t;
+    }
+    __syncthreads();
+    return red[0];
+}
 
 // ───────────────────────────── Softmax ──────────────────────────────────
 struct SoftmaxP {
@@ -28,19 +49,18 @@ struct SoftmaxP {
 // One block per row: max, then exp and sum, then divide (decomp.rs:174-183).
 template <int DT> __global__ void __launch_bounds__(256) fused_softmax(const SoftmaxP p) {
     __shared__ float red[32];
+    __shared__ double redd[32];
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const long long base = row * p.cols;
         float mx = -INFINITY;
         for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) mx = fmaxf(mx, ld<DT>(p.x, base + c));
         mx = block_max(mx, red);
-        float sum = 0.f;
+        double dsum = 0.0;
+        for (long long c = threadIdx.x; c < p.cols; c += blockDim.x)
+            dsum += (double)rnd_d<DT>(exp((double)rnd<DT>(ld<DT>(p.x, base + c) - mx)));
+        float sum = rnd_d<DT>(block_sum_d(dsum, redd));
         for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
-            float e = rnd<DT>(expf(rnd<DT>(ld<DT>(p.x, base + c) - mx)));
-            sum += e;
-        }
-        sum = rnd<DT>(block_sum(sum, red));
-        for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
-            float e = rnd<DT>(expf(rnd<DT>(ld<DT>(p.x, base + c) - mx)));
+            float e = rnd_d<DT>(exp((double)rnd<DT>(ld<DT>(p.x, base + c) - mx)));
             st<DT>(p.y, base + c, e / sum);
         }
     }
@@ -71,22 +91,22 @@ struct RmsNormP {
 // (decomp.rs:241-257). The row is kept in registers (≤ 8 values per thread for
 // cols ≤ 2048·… otherwise re-read).
 template <int DT> __global__ void __launch_bounds__(256) fused_rmsnorm(const RmsNormP p) {
-    __shared__ float red[32];
+    __shared__ double redd[32];
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const long long base = row * p.cols;
-        float ss = 0.f;
+        double ss = 0.0;
         for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
             float v = ld<DT>(p.x, base + c);
             if (p.res) {
                 v = rnd<DT>(v + ld<DT>(p.res, base + c));
                 if (p.sum_out) st<DT>(p.sum_out, base + c, v);
             }
-            ss += rnd<DT>(v * v);
+            ss += (double)rnd<DT>(v * v);
         }
-        ss = block_sum(ss, red);
-        float ms = rnd<DT>(ss / (float)p.cols);
+        ss = block_sum_d(ss, redd);
+        float ms = rnd_d<DT>(ss / (double)p.cols);
         float denom = rnd<DT>(ms + p.eps);
-        float inv = rnd<DT>(1.0f / sqrtf(denom));
+        float inv = rnd_d<DT>(1.0 / sqrt((double)denom));
         for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
             float v = ld<DT>(p.x, base + c);
             if (p.res) v = rnd<DT>(v + ld<DT>(p.res, base + c));
@@ -121,14 +141,14 @@ struct GeluP {
     float c_half, c_one, c_coef, c_k, c_inv_sqrt2;  // constants rounded to the tensor dtype
 };
 
-__device__ __forceinline__ float erf_as_f(float xf) {  // Abramowitz–Stegun 7.1.26 (interp.rs:860-872)
+__device__ __forceinline__ double erf_as_f(float xf) {  // Abramowitz–Stegun 7.1.26 (interp.rs:860-872)
     double x = xf;
     double sign = x < 0.0 ? -1.0 : 1.0;
     x = fabs(x);
     double t = 1.0 / (1.0 + 0.3275911 * x);
     double y = 1.0 - (((((1.061405429 * t - 1.453152027) * t) + 1.421413741) * t - 0.284496736) * t + 0.254829592) * t *
                          exp(-x * x);
-    return (float)(sign * y);
+    return sign * y;
 }
 
 template <int DT> __global__ void fused_gelu(const GeluP p) {
@@ -141,10 +161,10 @@ template <int DT> __global__ void fused_gelu(const GeluP p) {
             float cx3 = rnd<DT>(p.c_coef * x3);
             float s = rnd<DT>(x + cx3);
             float sc = rnd<DT>(p.c_k * s);
-            inner = rnd<DT>(tanhf(sc));
+            inner = rnd_d<DT>(tanh((double)sc));
         } else {  // decomp.rs:203-208
             float sc = rnd<DT>(x * p.c_inv_sqrt2);
-            inner = rnd<DT>(erf_as_f(sc));
+            inner = rnd_d<DT>(erf_as_f(sc));
         }
         float one_plus = rnd<DT>(p.c_one + inner);
         float hx = rnd<DT>(p.c_half * x);

@@ -1,5 +1,5 @@
 // com.microsoft.GroupQueryAttention, fused: rotary on q/k, KV-cache append,
-// causal + sliding-window mask, split-K online softmax, P·V.
+// causal + sliding-window mask, softmax, P·V.
 // Specification: the decomposition crates/onyxia-ir/src/decomp.rs:357-613
 // (operand layout from crates/onyxia-lower/src/rules.rs:777-888).
 //
@@ -7,15 +7,23 @@
 // sits at position past_b + j; present = valid past rows ++ new rows ++ zeros;
 // a query sees keys col ≤ qpos and, with a window w ≥ 0, col ≥ qpos − w.
 //
-// Three launches:
-//   gqa_prepare   rotates q into scratch and writes the new K (rotated) / V rows
-//                 into the present cache (copying the valid past unless the
-//                 present buffer *is* the past buffer)
-//   gqa_partial   one CTA per (key split, kv head × head group × query, batch):
-//                 each warp streams K/V rows, lanes hold a slice of the head
-//                 dim, scores are finished with warp shuffles; writes
-//                 (max, sum, acc[D]) per split to scratch
-//   gqa_combine   merges the splits and stores the output row
+// The kernels round where the decomposition's primitives store a tensor
+// (scores, scaled scores, shifted scores, exponentials, their sum, the
+// probabilities, the output) and add in f64 in between, like the interpreter,
+// so for f16 tensors they reproduce its rounding noise instead of adding their
+// own.
+//
+// Three launches, the key range split over CTAs in the last two:
+//   gqa_prepare  rotates q into scratch and writes the new K (rotated) / V rows
+//                into the present cache (copying the valid past unless the
+//                present buffer *is* the past buffer)
+//   gqa_scores   one warp per key: q·k for the heads of one KV group, scaled,
+//                biased, stored as f32 rows of scratch; the last CTA of a query
+//                to finish reduces the row to (max, Σ exp)
+//   gqa_pv       one warp per key again: p = exp(s − max)/Σ, acc += p·v; the
+//                last CTA to finish adds the partial accumulators in split order
+//                and stores the output row
+// "Last CTA" is decided by an arrival counter per query; nothing ever waits.
 //
 // KV tensors are [B, KV, T, D] views of buffers that hold `cap ≥ T` rows per
 // head, so an append never moves the rows already there.
@@ -27,6 +35,16 @@ namespace oxk {
 template <int DT> __device__ __forceinline__ float rnd(float v) {
     if constexpr (DT == DT_F16) return __half2float(__float2half_rn(v));
     else return v;
+}
+template <int DT> __device__ __forceinline__ float rnd_d(double v) {
+    if constexpr (DT == DT_F16) return __half2float(__double2half(v));
+    else return (float)v;
+}
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
 }
 
 struct GqaPrepP {
@@ -125,125 +143,187 @@ struct GqaAttnP {
     const void* pv;
     const int* seqlens;
     const void* bias;
-    float* part;  // [B,S,H,nsplit,D+2]
-    void* out;    // [B,S,H·D]
-    long long B, S, H, KV, D, T, cap, window, chunk;
+    float* scores;      // [B,S,H,span]: scaled, biased, rounded scores of the visible keys (−inf beyond them)
+    float* stats;       // [B,S,H,2]: row max, Σ exp (rounded)
+    double* part;       // [B,S,H,nsplit,D] partial P·V accumulators
+    unsigned* counters; // [2][B·S·KV·groups]
+    void* out;          // [B,S,H·D]
+    long long B, S, H, KV, D, T, cap, window, chunk, span;
     long long bias_sb, bias_sh;
     float scale;  // rounded to the tensor dtype
     int nsplit, groups;  // groups = head-group chunks per kv head
 };
 
-// DPL = head-dim elements per lane (D = 32·DPL), GT = query heads per CTA.
-template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_partial(const GqaAttnP p) {
-    constexpr int NW = 4;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long b = blockIdx.z, split = blockIdx.x;
-    const long long G = p.H / p.KV;
+struct GqaWho {
+    long long b, s, kvh, gc, h0, G, lo, hi, n;  // visible keys are lo..hi (n of them)
+    long long query;                            // linear id of (b, s, kvh, gc) for counters
+};
+
+__device__ __forceinline__ GqaWho gqa_who(const GqaAttnP& p, int GT) {
+    GqaWho w;
+    w.b = blockIdx.z;
+    w.G = p.H / p.KV;
     long long y = blockIdx.y;
-    const long long s = y % p.S;
+    w.s = y % p.S;
     y /= p.S;
-    const long long gc = y % p.groups, kvh = y / p.groups;
-    const long long h0 = kvh * G + gc * GT;
+    w.gc = y % p.groups;
+    w.kvh = y / p.groups;
+    w.h0 = w.kvh * w.G + w.gc * GT;
+    long long tot = (long long)p.seqlens[w.b] + 1, past_b = tot - p.S > 0 ? tot - p.S : 0;
+    long long qpos = past_b + w.s;
+    w.hi = qpos < p.T - 1 ? qpos : p.T - 1;
+    w.lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;
+    w.n = w.hi >= w.lo ? w.hi - w.lo + 1 : 0;
+    w.query = ((w.b * p.S + w.s) * p.KV + w.kvh) * p.groups + w.gc;
+    return w;
+}
 
-    const long long tot = (long long)p.seqlens[b] + 1, past_b = tot - p.S > 0 ? tot - p.S : 0;
-    long long qpos = past_b + s;
-    long long hi = qpos < p.T - 1 ? qpos : p.T - 1;                      // last visible key
-    long long lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;  // first visible key
-    long long t_begin = lo + split * p.chunk, t_end = t_begin + p.chunk - 1;
-    if (t_end > hi) t_end = hi;
-
-    float qv[GT][DPL], acc[GT][DPL], mx[GT], sum[GT];
-#pragma unroll
-    for (int g = 0; g < GT; g++) {
-        mx[g] = -INFINITY;
-        sum[g] = 0.f;
-        bool live = gc * GT + g < G;
-#pragma unroll
-        for (int i = 0; i < DPL; i++) {
-            acc[g][i] = 0.f;
-            qv[g][i] = live ? ld<DT>(p.q, ((b * p.S + s) * p.H + h0 + g) * p.D + lane * DPL + i) : 0.f;
-        }
-    }
-    const long long kv_base = (b * p.KV + kvh) * p.cap * p.D + lane * DPL;
-    for (long long t = t_begin + warp; t <= t_end; t += NW) {
-        float kx[DPL], vx[DPL];
-#pragma unroll
-        for (int i = 0; i < DPL; i++) {
-            kx[i] = ld<DT>(p.pk, kv_base + t * p.D + i);
-            vx[i] = ld<DT>(p.pv, kv_base + t * p.D + i);
-        }
-#pragma unroll
-        for (int g = 0; g < GT; g++) {
-            float dot = 0.f;
-#pragma unroll
-            for (int i = 0; i < DPL; i++) dot = fmaf(qv[g][i], kx[i], dot);
-            dot = warp_sum(dot);
-            float sc = rnd<DT>(rnd<DT>(dot) * p.scale);
-            if (p.bias) sc = rnd<DT>(sc + ld<DT>(p.bias, b * p.bias_sb + (h0 + g) * p.bias_sh + s * p.T + t));
-            float m_new = fmaxf(mx[g], sc);
-            float corr = __expf(mx[g] - m_new), pr = __expf(sc - m_new);
-            if (m_new == -INFINITY) {
-                corr = 1.f;
-                pr = 0.f;
-            }
-            sum[g] = sum[g] * corr + pr;
-#pragma unroll
-            for (int i = 0; i < DPL; i++) acc[g][i] = acc[g][i] * corr + pr * vx[i];
-            mx[g] = m_new;
-        }
-    }
-    // merge the four warps through shared memory
-    __shared__ float sh[NW][GT][32 * DPL + 2];
-#pragma unroll
-    for (int g = 0; g < GT; g++) {
-#pragma unroll
-        for (int i = 0; i < DPL; i++) sh[warp][g][lane * DPL + i] = acc[g][i];
-        if (lane == 0) {
-            sh[warp][g][32 * DPL] = mx[g];
-            sh[warp][g][32 * DPL + 1] = sum[g];
-        }
+// True in exactly one CTA per query: the one whose arrival completes the count.
+__device__ __forceinline__ bool last_cta(unsigned* counter, int expected) {
+    __shared__ unsigned arrived;
+    __syncthreads();
+    if (expected <= 1) return true;
+    __threadfence();
+    if (threadIdx.x == 0) {
+        arrived = atomicAdd(counter, 1u);
+        if (arrived == (unsigned)expected - 1) *counter = 0;  // leave it zero for the next launch
     }
     __syncthreads();
-    const int D = 32 * DPL;
-    for (int idx = threadIdx.x; idx < GT * (D + 2); idx += blockDim.x) {
-        int g = idx / (D + 2), c = idx % (D + 2);
-        if (gc * GT + g >= G) continue;
-        float M = -INFINITY;
+    bool last = arrived == (unsigned)expected - 1;
+    if (last) __threadfence();
+    return last;
+}
+
+// DPL = head-dim elements per lane (D = 32·DPL), GT = query heads per CTA.
+template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_scores(const GqaAttnP p) {
+    constexpr int NW = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long split = blockIdx.x;
+    const GqaWho w = gqa_who(p, GT);
+
+    float qv[GT][DPL];
 #pragma unroll
-        for (int w = 0; w < NW; w++) M = fmaxf(M, sh[w][g][D]);
-        float val;
-        if (c == D) {
-            val = M;
-        } else {
-            val = 0.f;
+    for (int g = 0; g < GT; g++) {
+        bool live = w.gc * GT + g < w.G;
 #pragma unroll
-            for (int w = 0; w < NW; w++) {
-                float f = (sh[w][g][D] == -INFINITY) ? 0.f : __expf(sh[w][g][D] - M);
-                val += f * (c == D + 1 ? sh[w][g][D + 1] : sh[w][g][c]);
-            }
+        for (int i = 0; i < DPL; i++)
+            qv[g][i] = live ? ld<DT>(p.q, ((w.b * p.S + w.s) * p.H + w.h0 + g) * p.D + lane * DPL + i) : 0.f;
+    }
+    const long long kv_base = (w.b * p.KV + w.kvh) * p.cap * p.D + lane * DPL;
+    const long long i_begin = split * p.chunk;
+    long long i_end = i_begin + p.chunk;
+    if (i_end > p.span) i_end = p.span;
+    for (long long i = i_begin + warp; i < i_end; i += NW) {
+        const long long t = w.lo + i;
+        const bool visible = i < w.n;
+        float kx[DPL];
+#pragma unroll
+        for (int e = 0; e < DPL; e++) kx[e] = visible ? ld<DT>(p.pk, kv_base + t * p.D + e) : 0.f;
+#pragma unroll
+        for (int g = 0; g < GT; g++) {
+            if (w.gc * GT + g >= w.G) continue;
+            double dot = 0.0;
+#pragma unroll
+            for (int e = 0; e < DPL; e++) dot += (double)qv[g][e] * (double)kx[e];
+            dot = warp_sum_d(dot);
+            float sc = rnd<DT>(rnd_d<DT>(dot) * p.scale);
+            if (p.bias && visible) sc = rnd<DT>(sc + ld<DT>(p.bias, w.b * p.bias_sb + (w.h0 + g) * p.bias_sh + w.s * p.T + t));
+            if (lane == 0) p.scores[((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span + i] = visible ? sc : -INFINITY;
         }
-        p.part[((((b * p.S + s) * p.H + h0 + g) * p.nsplit) + split) * (D + 2) + c] = val;
+    }
+    if (!last_cta(p.counters + w.query, p.nsplit)) return;
+
+    // row statistics of the decomposition's Softmax (decomp.rs:174-183)
+    __shared__ float red[32];
+    __shared__ double redd[32];
+    for (int g = 0; g < GT; g++) {
+        if (w.gc * GT + g >= w.G) continue;
+        const float* row = p.scores + ((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span;
+        float mx = -INFINITY;
+        for (long long i = threadIdx.x; i < w.n; i += blockDim.x) mx = fmaxf(mx, __ldcg(row + i));
+        mx = block_max(mx, red);
+        double sum = 0.0;
+        for (long long i = threadIdx.x; i < w.n; i += blockDim.x) {
+            float e = rnd_d<DT>(exp((double)rnd<DT>(__ldcg(row + i) - mx)));
+            sum += (double)e;
+        }
+        // block sum in f64
+        sum = warp_sum_d(sum);
+        __syncthreads();
+        if (lane == 0) redd[warp] = sum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int k = 0; k < NW; k++) t += redd[k];
+            float* st_ = p.stats + ((w.b * p.S + w.s) * p.H + w.h0 + g) * 2;
+            st_[0] = mx;
+            st_[1] = rnd_d<DT>(t);
+        }
+        __syncthreads();
     }
 }
 
-template <int DT> __global__ void gqa_combine(const GqaAttnP p) {
-    const long long b = blockIdx.y, sh_ = blockIdx.x;  // sh_ = s·H + h
-    const int D = (int)p.D;
-    const float* part = p.part + ((b * p.S * p.H + sh_) * p.nsplit) * (D + 2);
-    float M = -INFINITY;
-    for (int i = 0; i < p.nsplit; i++) M = fmaxf(M, part[i * (D + 2) + D]);
-    float L = 0.f;
-    for (int i = 0; i < p.nsplit; i++) {
-        float m = part[i * (D + 2) + D];
-        if (m != -INFINITY) L += part[i * (D + 2) + D + 1] * __expf(m - M);
+template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_pv(const GqaAttnP p) {
+    constexpr int NW = 4;
+    constexpr int D = 32 * DPL;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long split = blockIdx.x;
+    const GqaWho w = gqa_who(p, GT);
+
+    float mx[GT], sum[GT];
+    double acc[GT][DPL];
+#pragma unroll
+    for (int g = 0; g < GT; g++) {
+        bool live = w.gc * GT + g < w.G;
+        const float* st_ = p.stats + ((w.b * p.S + w.s) * p.H + w.h0 + g) * 2;
+        mx[g] = live ? st_[0] : 0.f;
+        sum[g] = live ? st_[1] : 1.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) acc[g][i] = 0.0;
     }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float o = 0.f;
-        for (int i = 0; i < p.nsplit; i++) {
-            float m = part[i * (D + 2) + D];
-            if (m != -INFINITY) o += part[i * (D + 2) + d] * __expf(m - M);
+    const long long kv_base = (w.b * p.KV + w.kvh) * p.cap * p.D + lane * DPL;
+    const long long i_begin = split * p.chunk;
+    long long i_end = i_begin + p.chunk;
+    if (i_end > w.n) i_end = w.n;
+    for (long long i = i_begin + warp; i < i_end; i += NW) {
+        const long long t = w.lo + i;
+        float vx[DPL];
+#pragma unroll
+        for (int e = 0; e < DPL; e++) vx[e] = ld<DT>(p.pv, kv_base + t * p.D + e);
+#pragma unroll
+        for (int g = 0; g < GT; g++) {
+            if (w.gc * GT + g >= w.G) continue;
+            float sc = p.scores[((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span + i];
+            float e = rnd_d<DT>(exp((double)rnd<DT>(sc - mx[g])));
+            float pr = rnd<DT>(e / sum[g]);
+#pragma unroll
+            for (int k = 0; k < DPL; k++) acc[g][k] += (double)pr * (double)vx[k];
         }
-        st<DT>(p.out, (b * p.S * p.H + sh_) * D + d, o / L);
+    }
+    // fold the four warps in order
+    __shared__ double sh[NW][GT][D];
+#pragma unroll
+    for (int g = 0; g < GT; g++)
+#pragma unroll
+        for (int k = 0; k < DPL; k++) sh[warp][g][lane * DPL + k] = acc[g][k];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GT * D; idx += blockDim.x) {
+        int g = idx / D, c = idx % D;
+        if (w.gc * GT + g >= w.G) continue;
+        double v = sh[0][g][c] + sh[1][g][c] + sh[2][g][c] + sh[3][g][c];
+        long long head = (w.b * p.S + w.s) * p.H + w.h0 + g;
+        if (p.nsplit == 1) st<DT>(p.out, head * D + c, rnd_d<DT>(v));
+        else p.part[(head * p.nsplit + split) * D + c] = v;
+    }
+    if (p.nsplit == 1) return;
+    if (!last_cta(p.counters + (long long)gridDim.y * gridDim.z + w.query, p.nsplit)) return;
+    for (int idx = threadIdx.x; idx < GT * D; idx += blockDim.x) {
+        int g = idx / D, c = idx % D;
+        if (w.gc * GT + g >= w.G) continue;
+        long long head = (w.b * p.S + w.s) * p.H + w.h0 + g;
+        double v = 0.0;
+        for (int s = 0; s < p.nsplit; s++) v += __ldcg(p.part + (head * p.nsplit + s) * D + c);
+        st<DT>(p.out, head * D + c, rnd_d<DT>(v));
     }
 }
 
@@ -282,41 +362,48 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
         ap.bias_sb = d.bias_b == 1 ? 0 : d.bias_h * S * T;
         ap.bias_sh = d.bias_h == 1 ? 0 : S * T;
     }
-    // Split the visible key range so that the launch fills the machine.
     const long long G = H / KV;
     const int GT = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
     ap.groups = (int)((G + GT - 1) / GT);
-    long long span = (d.window >= 0 && d.window + 1 < T) ? d.window + 1 : T;
-    long long ctas_per_split = B * KV * ap.groups * S;
-    long long want = (148 * 4 + ctas_per_split - 1) / ctas_per_split;  // ≈ 4 CTAs per SM
-    long long max_split = (span + 15) / 16;                           // ≥ 16 keys per CTA
+    ap.span = (d.window >= 0 && d.window + 1 < T) ? d.window + 1 : T;
+    // Split the visible key range so that the launch fills the machine; the
+    // arrival counters bound the number of queries a split launch may have.
+    long long queries = B * KV * ap.groups * S;
+    long long want = (148 * 4 + queries - 1) / queries;   // ≈ 4 CTAs per SM
+    long long max_split = (ap.span + 15) / 16;            // ≥ 16 keys per CTA
     long long nsplit = std::max<long long>(1, std::min<long long>(want, max_split));
+    if (2 * queries > (long long)kCounterWords) nsplit = 1;
     nsplit = std::min<long long>(nsplit, 1024);
-    ap.chunk = (span + nsplit - 1) / nsplit;
-    ap.nsplit = (int)((span + ap.chunk - 1) / ap.chunk);
-    Buf part = em.scratch((size_t)(B * S * H * ap.nsplit * (D + 2) * 4));
+    ap.chunk = (ap.span + nsplit - 1) / nsplit;
+    ap.nsplit = (int)((ap.span + ap.chunk - 1) / ap.chunk);
+    Buf scores = em.scratch((size_t)(B * S * H * ap.span * 4));
+    Buf stats = em.scratch((size_t)(B * S * H * 2 * 4));
+    Buf part = ap.nsplit > 1 ? em.scratch((size_t)(B * S * H * ap.nsplit * D * 8)) : null;
     if (KV * ap.groups * S > 65535 || B > 65535) throw std::runtime_error("fused GQA: grid dimension exceeds 65535");
     dim3 g((unsigned)ap.nsplit, (unsigned)(KV * ap.groups * S), (unsigned)B), blk(128);
     Buf qsrc = d.rot_half ? qrot : q.buf;
-#define GO(DPL, GTT)                                                                                              \
-    em.launch(gqa_partial<DT, DPL, GTT>, g, blk, 0, ap,                                                            \
-              {{&ap.q, qsrc}, {&ap.pk, present_k.buf}, {&ap.pv, present_v.buf}, {&ap.seqlens, seqlens.buf},        \
-               {&ap.bias, bias ? bias->buf : null}, {&ap.part, part}, {&ap.out, out.buf}},                         \
-              "gqa_partial")
-#define GO_D(GTT)                  \
-    switch (D / 32) {              \
-        case 1: GO(1, GTT); break; \
-        case 2: GO(2, GTT); break; \
-        case 4: GO(4, GTT); break; \
-        default: GO(8, GTT); break; \
+#define PTRS                                                                                                       \
+    {{&ap.q, qsrc}, {&ap.pk, present_k.buf}, {&ap.pv, present_v.buf}, {&ap.seqlens, seqlens.buf},                  \
+     {&ap.bias, bias ? bias->buf : null}, {&ap.scores, scores}, {&ap.stats, stats}, {&ap.part, part},              \
+     {&ap.counters, Buf{kSlotCounters, 0}}, {&ap.out, out.buf}}
+#define GO(K, LABEL, DPL, GTT) em.launch(K<DT, DPL, GTT>, g, blk, 0, ap, PTRS, LABEL)
+#define GO_D(K, LABEL, GTT)                  \
+    switch (D / 32) {                        \
+        case 1: GO(K, LABEL, 1, GTT); break; \
+        case 2: GO(K, LABEL, 2, GTT); break; \
+        case 4: GO(K, LABEL, 4, GTT); break; \
+        default: GO(K, LABEL, 8, GTT); break; \
     }
-    if (GT == 4) { GO_D(4) } else if (GT == 2) { GO_D(2) } else { GO_D(1) }
+#define GO_G(K, LABEL)                                  \
+    if (GT == 4) { GO_D(K, LABEL, 4) }                  \
+    else if (GT == 2) { GO_D(K, LABEL, 2) }             \
+    else { GO_D(K, LABEL, 1) }
+    GO_G(gqa_scores, "gqa_scores")
+    GO_G(gqa_pv, "gqa_pv")
+#undef GO_G
 #undef GO_D
 #undef GO
-    em.launch(gqa_combine<DT>, dim3((unsigned)(S * H), (unsigned)B), dim3((unsigned)std::min<long long>(D, 256)), 0, ap,
-              {{&ap.q, qsrc}, {&ap.pk, present_k.buf}, {&ap.pv, present_v.buf}, {&ap.seqlens, seqlens.buf},
-               {&ap.bias, bias ? bias->buf : null}, {&ap.part, part}, {&ap.out, out.buf}},
-              "gqa_combine");
+#undef PTRS
 }
 
 void emit_gqa(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k, const TRef& v, const TRef& past_k,

@@ -49,6 +49,10 @@ struct Buf {
 constexpr uint32_t kSlotErr = 0xFFFFFFF0u;      // the session's ErrWord
 constexpr uint32_t kSlotScratch = 0xFFFFFFF1u;  // the plan's scratch area (offset = position in it)
 constexpr uint32_t kSlotNull = 0xFFFFFFF2u;     // resolves to nullptr
+// A session-lifetime array of kCounterWords zeroed 32-bit arrival counters;
+// kernels that use it leave every word zero again when they finish.
+constexpr uint32_t kSlotCounters = 0xFFFFFFF3u;
+constexpr size_t kCounterWords = 1 << 16;
 
 struct Reloc {
     uint32_t field_off;  // byte offset of a pointer field inside the parameter struct
@@ -179,10 +183,20 @@ struct NBitsDesc {
     int64_t m, k, n, block_size, n_blocks;
     int act_dtype, scale_dtype;
     bool has_zp;
+    // The weight constant was re-laid out by emit_nbits_interleave (backend-
+    // private layout for the tensor-core decode kernel).
+    bool interleaved;
 };
 // y[m, n] = a[m, :] · dequant(w)[n, :]ᵀ for packed u4 weights [N, n_blocks, bs].
 void emit_matmul_nbits(Emitter&, const NBitsDesc&, const TRef& a, const TRef& w, const TRef& scales,
                        const TRef* zp, const TRef& y);
+
+// Tensor-core decode kernel for f16 activations and scales over interleaved weights.
+void emit_matmul_nbits_mma(Emitter&, const NBitsDesc&, const TRef& a, const TRef& w, const TRef& scales,
+                           const TRef* zp, const TRef& y);
+// One-time re-layout of a packed u4 weight constant: within each 32-bit word,
+// nibble j moves to position (j >> 1) + 4·(j & 1).
+void emit_nbits_interleave(Emitter&, Buf src, Buf dst, long long bytes);
 
 // argmax over the last axis, highest index among equal maxima → i64.
 void emit_argmax_last(Emitter&, const TRef& x, const TRef& y);

@@ -9,7 +9,7 @@
 // dtype on store. The interpreter accumulates in f64; f32 accumulation differs
 // from it only by rounding.
 //
-// Decode path (`nbits_gemv`): HBM-bound. Each lane streams whole 16-byte
+// Generic path (`nbits_gemv_simt`, any float dtype mix; the f16 decode path is nbits_mma.cu): Each lane streams whole 16-byte
 // blocks of nibbles with 128-bit loads (one scale per block), keeps the
 // matching activation slice in registers, and rows are finished with warp
 // shuffles. Algorithmic bytes per weight: 0.5 (nibbles) + 2/32 or 4/32
@@ -47,7 +47,7 @@ template <> struct ScaleOps<DT_F32> {
 };
 
 // One warp per weight row; MT activation rows share every weight read.
-template <int ADT, int SDT, int MT> __global__ void __launch_bounds__(256) nbits_gemv(const NBitsGemvP p) {
+template <int ADT, int SDT, int MT> __global__ void __launch_bounds__(256) nbits_gemv_simt(const NBitsGemvP p) {
     const int lane = threadIdx.x & 31;
     const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -101,7 +101,7 @@ template <int ADT, int SDT> static void launch_gemv(Emitter& em, NBitsGemvP p, c
         p.m0 = m0;
         long long left = p.m_total - m0;
 #define GO(MT) \
-    em.launch(nbits_gemv<ADT, SDT, MT>, g, b, 0, p, {{&p.a, a.buf}, {&p.w, w.buf}, {&p.scales, scales.buf}, {&p.zp, zb}, {&p.y, y.buf}}, "nbits_gemv")
+    em.launch(nbits_gemv_simt<ADT, SDT, MT>, g, b, 0, p, {{&p.a, a.buf}, {&p.w, w.buf}, {&p.scales, scales.buf}, {&p.zp, zb}, {&p.y, y.buf}}, "nbits_gemv_simt")
         if (left >= 8) GO(8);
         else if (left > 4) GO(8);
         else if (left > 2) GO(4);
@@ -115,6 +115,10 @@ void emit_matmul_nbits(Emitter& em, const NBitsDesc& d, const TRef& a, const TRe
                        const TRef* zp, const TRef& y) {
     if (d.block_size != 32) throw std::runtime_error("nbits kernels need block_size 32");
     if (d.m == 0 || d.n == 0) return;
+    if (d.interleaved) {
+        emit_matmul_nbits_mma(em, d, a, w, scales, zp, y);
+        return;
+    }
     NBitsGemvP p{};
     p.m_total = d.m;
     p.k = d.k;

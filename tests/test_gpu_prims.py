@@ -34,9 +34,9 @@ def rand(shape, dtype):
     return RNG.integers(max(info.min, -1000), min(info.max, 1000), shape, endpoint=True).astype(dtype)
 
 
-def check_prim(kind, inputs, dtype=f32, **params):
+def check_prim(kind, inputs, tdtype=f32, **params):
     m, feed = single_prim_module(kind, [ht(x) for x in inputs], **params)
-    return differential(m, feed, **tol(dtype))
+    return differential(m, feed, **tol(tdtype))
 
 
 # ── Unary ────────────────────────────────────────────────────────────────
