@@ -231,6 +231,7 @@ def main():
         ms = float(t.item())
     launches = sess.launch_count() - launches0
     value = world * K / (ms / 1e3)
+    plan_stats = sess.plan_stats()
 
     # ── end to end through the host-facing calls (ids + mask up, logits down, host argmax) ──
     lm.kv_cache, lm.past_seq_len = kv, past + W + K
@@ -304,7 +305,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu,
             "model_roofline": {"bytes_per_token": weight_bytes + kv_bytes, "tok_s_at_peak": peak * 1e9 / (weight_bytes + kv_bytes),
                                "frac": value / world / (peak * 1e9 / (weight_bytes + kv_bytes))},
-            "kernels": kernel_share, "resident_bytes": sess.resident_bytes(), "model_build_s": build_s,
+            "planner": plan_stats, "kernels": kernel_share, "resident_bytes": sess.resident_bytes(), "model_build_s": build_s,
         }
         print(json.dumps(line))
     if world > 1:

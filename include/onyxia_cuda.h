@@ -249,8 +249,9 @@ uint64_t ox_session_launch_count(const ox_session*);
 /* Planner counters since prepare: out[0] plans built from scratch, out[1] plans
  * patched in place for a changed symbol binding, out[2] plans reused unchanged,
  * out[3] CUDA-graph launches, out[4] graph kernel nodes whose parameters were
- * rewritten. */
-void ox_session_plan_stats(const ox_session*, uint64_t out[5]);
+ * rewritten, out[5] runs, out[6..8] host microseconds summed over those runs
+ * spent binding inputs, planning, and patching + launching. */
+void ox_session_plan_stats(const ox_session*, uint64_t out[9]);
 /* Greedy sampling on the device: index of the maximum over the last axis of
  * `logits`, highest index among equal maxima (≙ sampling::sample_greedy,
  * crates/onyxia-cli/src/sampling.rs:71-80, which keeps the last maximum).

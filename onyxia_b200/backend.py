@@ -131,9 +131,10 @@ class CudaSession:
         return ms.value
 
     def plan_stats(self) -> dict:
-        out = (C.c_uint64 * 5)()
+        out = (C.c_uint64 * 9)()
         self._lib.ox_session_plan_stats(self._h, out)
-        return dict(zip(("built", "updated", "reused", "graph_launches", "graph_node_updates"), [int(v) for v in out]))
+        return dict(zip(("built", "updated", "reused", "graph_launches", "graph_node_updates", "runs", "bind_us",
+                         "plan_us", "launch_us"), [int(v) for v in out]))
 
     def launch_count(self) -> int:
         return self._lib.ox_session_launch_count(self._h)

@@ -187,7 +187,9 @@ ox_status ox_session_timer_stop(ox_session* s, float* elapsed_ms) {
 
 uint64_t ox_session_launch_count(const ox_session* s) { return s->s->launch_count; }
 
-void ox_session_plan_stats(const ox_session* s, uint64_t out[5]) {
+void ox_session_plan_stats(const ox_session* s, uint64_t out[9]) {
+    out[5] = s->s->host_runs;
+    for (int i = 0; i < 3; i++) out[6 + i] = (uint64_t)s->s->host_us[i];
     out[0] = s->s->plans_built;
     out[1] = s->s->plans_updated;
     out[2] = s->s->plans_reused;

@@ -160,6 +160,13 @@ void gqa_lower(FusedCtx& c) {
         d.bias_h = bs[1];
     }
     d.in_place = c.kv_in_place;
+    // A decode step on a cache that is appended to in place: size the launch for
+    // the next multiple of 256 rows and pass the true length as a per-run scalar.
+    if (d.in_place && d.seq == 1 && !d.has_bias) {
+        d.t_bucket = (d.past + d.seq + 255) / 256 * 256;
+        c.bucket = d.t_bucket;
+        c.bucket_step = 256;
+    }
     oxk::emit_gqa(c.em, d, c.ins[0], c.ins[1], c.ins[2], c.ins[3], c.ins[4], c.ins[5], cosr, sinr, biasr, c.outs[0], c.outs[1], c.outs[2]);
 }
 

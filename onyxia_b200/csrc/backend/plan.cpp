@@ -7,6 +7,7 @@
 // register file, per-node dispatch, frees — restated so that the steady state
 // of a decode loop costs one graph launch and a handful of parameter patches.
 #include <algorithm>
+#include <chrono>
 #include <climits>
 #include <cstring>
 
@@ -261,7 +262,11 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
                 FusedCtx fc{em, node, ins, outs, (bool)kv_in_place[nid], false};
                 if (node.inputs.size() > 1) fc.weights_interleaved = interleaved_[node.inputs[1]] != 0;
                 info_[nid].fused->lower(fc);
+                plan.node_bucket[nid] = fc.bucket;
+                plan.node_bucket_step[nid] = fc.bucket_step;
             }
+            for (size_t j = 0; j < em.dyn_vals.size(); j++) plan.dyn_host[(size_t)nid * oxk::kDynPerNode + j] = em.dyn_vals[j];
+            if (!em.dyn_vals.empty()) plan.dyn_used = true;
         }
     } catch (const Error& e) {
         if (e.kind == ErrKind::Binding) throw;
@@ -302,6 +307,9 @@ std::unique_ptr<Plan> Session::build_plan(const Bindings& bindings_in, const std
     plan->trefs.assign(nv, TRef{});
     plan->arena_size.assign(nv, 0);
     plan->node_recs.assign(m.nodes.size(), {0, 0});
+    plan->dyn_host.assign(m.nodes.size() * oxk::kDynPerNode, 0);
+    plan->node_bucket.assign(m.nodes.size(), 0);
+    plan->node_bucket_step.assign(m.nodes.size(), 0);
     plan->structure = structure_key(inputs, kv_in_place);
     Bindings bindings = bindings_in;
 
@@ -497,6 +505,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
         // leave head-room so a growing scratch area does not move the arena at every step
         plan.arena = pool_->alloc(plan.arena_bytes + plan.scratch_bytes * 2 + 512);
     }
+    if (plan.dyn_used && !plan.dyn_dev) plan.dyn_dev = pool_->alloc(plan.dyn_host.size() * sizeof(int64_t));
     char* arena_base = (char*)plan.arena->ptr;
     size_t scratch_off = (plan.arena_bytes + 255) / 256 * 256;
 
@@ -511,6 +520,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
             case oxk::kSlotErr: return (void*)d_err_;
             case oxk::kSlotNull: return nullptr;
             case oxk::kSlotCounters: return (void*)d_counters_;
+            case oxk::kSlotDyn: return (char*)plan.dyn_dev->ptr + buf.off;
             case oxk::kSlotScratch: return arena_base + scratch_off + buf.off;
             default: break;
         }
@@ -525,6 +535,22 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
         }
         return base + buf.off;
     };
+
+    // per-run scalars: staged through a small ring of pinned copies so the host
+    // may run ahead of the device
+    if (plan.dyn_used) {
+        size_t bytes = plan.dyn_host.size() * sizeof(int64_t);
+        if (!plan.dyn_pinned) {
+            OX_CUDA(cudaMallocHost((void**)&plan.dyn_pinned, bytes * Plan::kDynRing));
+            for (auto& e : plan.dyn_events) OX_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        }
+        unsigned slot = plan.dyn_cursor++ % Plan::kDynRing;
+        if (plan.dyn_cursor > Plan::kDynRing) OX_CUDA(cudaEventSynchronize(plan.dyn_events[slot]));
+        int64_t* stage = plan.dyn_pinned + (size_t)slot * plan.dyn_host.size();
+        std::memcpy(stage, plan.dyn_host.data(), bytes);
+        OX_CUDA(cudaMemcpyAsync(plan.dyn_dev->ptr, stage, bytes, cudaMemcpyHostToDevice, stream_));
+        OX_CUDA(cudaEventRecord(plan.dyn_events[slot], stream_));
+    }
 
     plan.uses++;
     const size_t n = plan.recs.size();
@@ -603,7 +629,14 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
     err_pending_ = true;
 }
 
+namespace {
+inline double now_us() {
+    return std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+}  // namespace
+
 std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std::pair<std::string, DTensor>>& named) {
+    const double t_start = now_us();
     OX_CUDA(cudaSetDevice(device_));
     const Module& m = module_;
     // match by name against the signature (crates/onyxia-ir/src/backend.rs:47-50);
@@ -644,6 +677,7 @@ std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std:
         kv_in_place[n] = ok(tk) && ok(tv) && tk.buf != tv.buf && outs;
     }
 
+    const double t_bound = now_us();
     // ── find, patch or build the plan ──
     std::vector<uint64_t> key = structure_key(inputs, kv_in_place);
     Plan* plan = nullptr;
@@ -672,8 +706,14 @@ std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std:
         while (plans_.size() > 6) plans_.pop_back();
     }
 
+    const double t_planned = now_us();
     std::vector<BufferRef> out_bufs;
     execute(*plan, inputs, out_bufs);
+    const double t_executed = now_us();
+    host_us[0] += t_bound - t_start;
+    host_us[1] += t_planned - t_bound;
+    host_us[2] += t_executed - t_planned;
+    host_runs++;
 
     std::vector<std::pair<std::string, DTensor>> outs;
     outs.reserve(plan->outputs.size());

@@ -102,6 +102,10 @@ struct FusedCtx {
     bool kv_in_place = false;
     // MatMulNBits: the weight constant (input 1) holds the interleaved layout.
     bool weights_interleaved = false;
+    // Set by a kernel that sized its launch for a bucket of a growing dimension
+    // and reads the true value from the per-run scalars: the launch stays valid
+    // while the value stays in (bucket − bucket_step, bucket].
+    int64_t bucket = 0, bucket_step = 0;
 };
 
 // A hand-written kernel for one composite (≙ CompositeKernel, fused.rs:27-41).

@@ -81,6 +81,11 @@ void Pool::trim() {
 Plan::~Plan() {
     if (exec) cudaGraphExecDestroy(exec);
     if (graph) cudaGraphDestroy(graph);
+    if (dyn_pinned) {
+        for (auto e : dyn_events)
+            if (e) cudaEventDestroy(e);
+        cudaFreeHost(dyn_pinned);
+    }
 }
 
 // ───────────────────────────── Backend ──────────────────────────────────
@@ -497,17 +502,10 @@ DTensor Session::argmax_last(const DTensor& logits) {
     out.buf = pool_->alloc(std::max<size_t>(out.nbytes(), 8));
     oxk::Emitter em;
     TRef x{Buf{0, 0}, (int)logits.dtype, logits.shape, 0}, y{Buf{1, 0}, (int)DType::I64, out.shape, 0};
-    oxk::emit_argmax_last(em, x, y);
-    for (auto& r : em.recs) {
-        std::vector<uint8_t> params = r.params;
-        for (auto& rl : r.relocs) {
-            void* p = rl.buf.slot == 0 ? logits.ptr() : out.ptr();
-            std::memcpy(params.data() + rl.field_off, &p, sizeof(void*));
-        }
-        void* args[1] = {params.data()};
-        OX_CUDA(cudaLaunchKernel(r.func, r.grid, r.block, args, r.smem, stream_));
-        launch_count++;
-    }
+    int64_t rows = out.numel();
+    BufferRef part = pool_->alloc(oxk::argmax_scratch_bytes(rows));
+    oxk::emit_argmax_last(em, x, y, Buf{2, 0}, Buf{3, 0});
+    launch_now(em, {logits.ptr(), out.ptr(), part->ptr, (void*)d_counters_});
     return out;
 }
 

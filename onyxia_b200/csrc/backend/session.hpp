@@ -50,6 +50,16 @@ struct Plan {
     std::vector<OutSpec> outputs;                // module outputs, signature order
     size_t arena_bytes = 0, scratch_bytes = 0, scratch_capacity = 0;
     BufferRef arena;                             // arena + scratch, owned by the plan
+    // Per-run scalars (kDynPerNode int64 slots per node) and the bucket each
+    // node's launch was sized for (0 = the node has none).
+    std::vector<int64_t> dyn_host;
+    std::vector<int64_t> node_bucket, node_bucket_step;
+    bool dyn_used = false;
+    BufferRef dyn_dev;
+    static constexpr int kDynRing = 8;
+    int64_t* dyn_pinned = nullptr;               // kDynRing staging copies of dyn_host
+    cudaEvent_t dyn_events[kDynRing] = {};
+    unsigned dyn_cursor = 0;
     // CUDA graph of the launch list, with the launch state each node currently holds.
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -81,6 +91,9 @@ public:
     uint64_t launch_count = 0;
     // planner statistics: plans built from scratch, updated in place, reused as they were
     uint64_t plans_built = 0, plans_updated = 0, plans_reused = 0, graph_node_updates = 0, graph_launches = 0;
+    // host time spent inside run(): binding, planning, patching + launching (µs, summed)
+    double host_us[3] = {0, 0, 0};
+    uint64_t host_runs = 0;
     const Module& module() const { return module_; }
     const std::vector<std::string>& output_names() const { return output_names_; }
 

@@ -88,30 +88,62 @@ struct RmsNormP {
 };
 
 // x·rsqrt(mean(x²) + ε)·w with the decomposition's rounding points
-// (decomp.rs:241-257). The row is kept in registers (≤ 8 values per thread for
-// cols ≤ 2048·… otherwise re-read).
-template <int DT> __global__ void __launch_bounds__(256) fused_rmsnorm(const RmsNormP p) {
+// (decomp.rs:241-257). A row is one CTA; for rows of up to EPT·blockDim
+// elements every operand is fetched in a single round of loads and the row
+// stays in registers (one DRAM latency instead of three).
+template <int DT, int EPT> __global__ void __launch_bounds__(1024) fused_rmsnorm(const RmsNormP p) {
     __shared__ double redd[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const long long base = row * p.cols;
+        float v[EPT > 0 ? EPT : 1], wv[EPT > 0 ? EPT : 1];
         double ss = 0.0;
-        for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
-            float v = ld<DT>(p.x, base + c);
-            if (p.res) {
-                v = rnd<DT>(v + ld<DT>(p.res, base + c));
-                if (p.sum_out) st<DT>(p.sum_out, base + c, v);
+        if constexpr (EPT > 0) {
+#pragma unroll
+            for (int e = 0; e < EPT; e++) {
+                long long c = threadIdx.x + (long long)e * blockDim.x;
+                bool in = c < p.cols;
+                v[e] = in ? ld<DT>(p.x, base + c) : 0.f;
+                wv[e] = in ? ld<DT>(p.w, c) : 0.f;
+                if (p.res && in) v[e] = rnd<DT>(v[e] + ld<DT>(p.res, base + c));
             }
-            ss += (double)rnd<DT>(v * v);
+#pragma unroll
+            for (int e = 0; e < EPT; e++) ss += (double)rnd<DT>(v[e] * v[e]);
+        } else {
+            for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
+                float x = ld<DT>(p.x, base + c);
+                if (p.res) x = rnd<DT>(x + ld<DT>(p.res, base + c));
+                ss += (double)rnd<DT>(x * x);
+            }
         }
-        ss = block_sum_d(ss, redd);
-        float ms = rnd_d<DT>(ss / (double)p.cols);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        __syncthreads();  // redd may still be read by the previous row
+        if (lane == 0) redd[warp] = ss;
+        __syncthreads();
+        double tot = 0.0;
+        for (int k = 0; k < nw; k++) tot += redd[k];
+        float ms = rnd_d<DT>(tot / (double)p.cols);
         float denom = rnd<DT>(ms + p.eps);
         float inv = rnd_d<DT>(1.0 / sqrt((double)denom));
-        for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
-            float v = ld<DT>(p.x, base + c);
-            if (p.res) v = rnd<DT>(v + ld<DT>(p.res, base + c));
-            float normed = rnd<DT>(v * inv);
-            st<DT>(p.y, base + c, normed * ld<DT>(p.w, c));
+        if constexpr (EPT > 0) {
+#pragma unroll
+            for (int e = 0; e < EPT; e++) {
+                long long c = threadIdx.x + (long long)e * blockDim.x;
+                if (c < p.cols) {
+                    if (p.res && p.sum_out) st<DT>(p.sum_out, base + c, v[e]);
+                    st<DT>(p.y, base + c, rnd<DT>(v[e] * inv) * wv[e]);
+                }
+            }
+        } else {
+            for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
+                float x = ld<DT>(p.x, base + c);
+                if (p.res) {
+                    x = rnd<DT>(x + ld<DT>(p.res, base + c));
+                    if (p.sum_out) st<DT>(p.sum_out, base + c, x);
+                }
+                st<DT>(p.y, base + c, rnd<DT>(x * inv) * ld<DT>(p.w, c));
+            }
         }
     }
 }
@@ -123,12 +155,22 @@ void emit_rmsnorm(Emitter& em, const TRef& x, const TRef& w, const TRef& y, doub
     p.rows = p.cols ? x.numel() / p.cols : 0;
     if (p.rows == 0 || p.cols == 0) return;
     p.eps = x.dtype == DT_F16 ? __half2float(__double2half(eps)) : (float)eps;
-    dim3 g((unsigned)std::min<long long>(p.rows, 148 * 32)), b(p.cols <= 1024 ? 128 : 256);
+    // ≤ 4 elements per thread where the row allows it, warps of whole lanes
+    long long threads = std::min<long long>(1024, std::max<long long>(64, ((p.cols + 3) / 4 + 31) / 32 * 32));
+    long long ept = (p.cols + threads - 1) / threads;
+    dim3 g((unsigned)std::min<long long>(p.rows, 148 * 32)), b((unsigned)threads);
     Buf rb = res ? res->buf : Buf{kSlotNull, 0}, sb = sum_out ? sum_out->buf : Buf{kSlotNull, 0};
-    if (x.dtype == DT_F32)
-        em.launch(fused_rmsnorm<DT_F32>, g, b, 0, p, {{&p.x, x.buf}, {&p.res, rb}, {&p.w, w.buf}, {&p.y, y.buf}, {&p.sum_out, sb}}, "fused_rmsnorm");
-    else
-        em.launch(fused_rmsnorm<DT_F16>, g, b, 0, p, {{&p.x, x.buf}, {&p.res, rb}, {&p.w, w.buf}, {&p.y, y.buf}, {&p.sum_out, sb}}, "fused_rmsnorm");
+#define GO(DT, E) \
+    em.launch(fused_rmsnorm<DT, E>, g, b, 0, p, {{&p.x, x.buf}, {&p.res, rb}, {&p.w, w.buf}, {&p.y, y.buf}, {&p.sum_out, sb}}, "fused_rmsnorm")
+#define GO_E(DT)                    \
+    if (ept <= 1) GO(DT, 1);        \
+    else if (ept <= 2) GO(DT, 2);   \
+    else if (ept <= 4) GO(DT, 4);   \
+    else if (ept <= 8) GO(DT, 8);   \
+    else GO(DT, 0);
+    if (x.dtype == DT_F32) { GO_E(DT_F32) } else { GO_E(DT_F16) }
+#undef GO_E
+#undef GO
 }
 
 // ───────────────────────────── Gelu / GeGLU ─────────────────────────────
@@ -252,66 +294,108 @@ void emit_rotary(Emitter& em, const TRef& x, const TRef& pos, const TRef& cos, c
 struct ArgmaxP {
     const void* x;
     long long* y;
+    float* part_v;       // [rows][blocks] best value per block
+    long long* part_i;   // [rows][blocks] its index
+    unsigned* counters;  // one per row
     long long rows, cols;
+    int blocks;          // blocks per row
 };
 
-// Highest index among equal maxima, matching `Iterator::max_by`, which keeps
-// the last maximum (crates/onyxia-cli/src/sampling.rs:71-80).
-template <int DT> __global__ void __launch_bounds__(1024) sample_argmax(const ArgmaxP p) {
+// (v, i) beats (bv, b) if it is larger, or equal with a higher index: among
+// equal maxima the last one wins, like `Iterator::max_by`
+// (crates/onyxia-cli/src/sampling.rs:71-80).
+__device__ __forceinline__ bool am_better(float v, long long i, float bv, long long b) {
+    return b < 0 || (i >= 0 && (v > bv || (v == bv && i > b)));
+}
+__device__ __forceinline__ void am_block(float& best, long long& bi, float* sv, long long* si) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (am_better(ov, oi, best, bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    __syncthreads();
+    if (lane == 0) {
+        sv[w] = best;
+        si[w] = bi;
+    }
+    __syncthreads();
+    best = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : -1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (am_better(ov, oi, best, bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+}
+
+// Each row is split over `blocks` CTAs; the last one to arrive merges.
+template <int DT> __global__ void __launch_bounds__(256) sample_argmax(const ArgmaxP p) {
     __shared__ float sv[32];
     __shared__ long long si[32];
-    long long row = blockIdx.x;
-    const long long base = row * p.cols;
+    __shared__ unsigned arrived;
+    const long long row = blockIdx.y, base = row * p.cols;
+    const long long per = (p.cols + p.blocks - 1) / p.blocks;
+    const long long c0 = blockIdx.x * per, c1 = c0 + per < p.cols ? c0 + per : p.cols;
     float best = -INFINITY;
     long long bi = -1;
-    for (long long c = threadIdx.x; c < p.cols; c += blockDim.x) {
+    for (long long c = c0 + threadIdx.x; c < c1; c += blockDim.x) {
         float v = ld<DT>(p.x, base + c);
         if (bi < 0 || v >= best) {  // columns ascend within a thread, so >= keeps the last maximum
             best = v;
             bi = c;
         }
     }
-    auto better = [](float v, long long i, float bv, long long b) { return b < 0 || (i >= 0 && (v > bv || (v == bv && i > b))); };
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better(ov, oi, best, bi)) {
-            best = ov;
-            bi = oi;
-        }
+    am_block(best, bi, sv, si);
+    if (p.blocks == 1) {
+        if (threadIdx.x == 0) p.y[row] = bi < 0 ? 0 : bi;
+        return;
     }
-    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-    if (lane == 0) {
-        sv[w] = best;
-        si[w] = bi;
+    if (threadIdx.x == 0) {
+        p.part_v[row * p.blocks + blockIdx.x] = best;
+        p.part_i[row * p.blocks + blockIdx.x] = bi;
+        __threadfence();
+        arrived = atomicAdd(p.counters + row, 1u);
+        if (arrived == (unsigned)p.blocks - 1) p.counters[row] = 0;
     }
     __syncthreads();
-    if (w == 0) {
-        best = lane < nw ? sv[lane] : -INFINITY;
-        bi = lane < nw ? si[lane] : -1;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (better(ov, oi, best, bi)) {
-                best = ov;
-                bi = oi;
-            }
+    if (arrived != (unsigned)p.blocks - 1) return;
+    __threadfence();
+    best = -INFINITY;
+    bi = -1;
+    for (int k = threadIdx.x; k < p.blocks; k += blockDim.x) {
+        float v = __ldcg(p.part_v + row * p.blocks + k);
+        long long i = __ldcg(p.part_i + row * p.blocks + k);
+        if (am_better(v, i, best, bi)) {
+            best = v;
+            bi = i;
         }
-        if (lane == 0) p.y[row] = bi < 0 ? 0 : bi;
     }
+    am_block(best, bi, sv, si);
+    if (threadIdx.x == 0) p.y[row] = bi < 0 ? 0 : bi;
 }
 
-void emit_argmax_last(Emitter& em, const TRef& x, const TRef& y) {
+void emit_argmax_last(Emitter& em, const TRef& x, const TRef& y, Buf part, Buf counters) {
     ArgmaxP p{};
     p.cols = x.shape.back();
     p.rows = p.cols ? x.numel() / p.cols : 0;
-    (void)y;
     if (p.rows == 0) return;
-    dim3 g((unsigned)p.rows), b(1024);
-    if (x.dtype == DT_F32) em.launch(sample_argmax<DT_F32>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "sample_argmax");
-    else em.launch(sample_argmax<DT_F16>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "sample_argmax");
+    if (p.rows > 65535 || (size_t)p.rows > kCounterWords) throw std::runtime_error("argmax: too many rows");
+    p.blocks = (int)std::max<long long>(1, std::min<long long>(kArgmaxMaxBlocks, p.cols / 2048));
+    dim3 g((unsigned)p.blocks, (unsigned)p.rows), b(256);
+    Buf pv = part, pi = part.at((int64_t)(p.rows * kArgmaxMaxBlocks * 4));
+    if (x.dtype == DT_F32)
+        em.launch(sample_argmax<DT_F32>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}, {&p.part_v, pv}, {&p.part_i, pi}, {&p.counters, counters}}, "sample_argmax");
+    else
+        em.launch(sample_argmax<DT_F16>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}, {&p.part_v, pv}, {&p.part_i, pi}, {&p.counters, counters}}, "sample_argmax");
 }
 
 }  // namespace oxk

@@ -60,6 +60,7 @@ struct GqaPrepP {
     void* present_k;
     void* present_v;
     ErrWord* err;
+    const long long* dyn_t;  // when set, the present length T is read from here
     long long B, S, H, KV, D, P, T, past_cap, pres_cap, half, cache_rows;
     long long nq;    // threads that rotate q (0 without rotary)
     long long nkv;   // threads that build the present caches
@@ -79,6 +80,7 @@ __device__ __forceinline__ float rope_elem(const void* x, long long base, long l
 
 template <int DT> __global__ void gqa_prepare(const GqaPrepP p) {
     const long long total = p.nq + p.nkv;
+    const long long T = p.dyn_t ? *p.dyn_t : p.T;
     for (long long i = global_tid(); i < total; i += global_threads()) {
         if (i < p.nq) {
             // q rotation: i over [B,S,H,D]
@@ -93,7 +95,7 @@ template <int DT> __global__ void gqa_prepare(const GqaPrepP p) {
             continue;
         }
         long long r = i - p.nq;
-        long long rows = p.in_place ? p.S : p.T;  // rows visited per (b, kv head)
+        long long rows = p.in_place ? p.S : T;  // rows visited per (b, kv head)
         long long e = r % p.D, t0 = (r / p.D) % rows, kvh = (r / (p.D * rows)) % p.KV, b = r / (p.D * rows * p.KV);
         long long tot = (long long)p.seqlens[b] + 1, past_b = tot - p.S > 0 ? tot - p.S : 0;
         long long pres_base = (b * p.KV + kvh) * p.pres_cap * p.D, past_base = (b * p.KV + kvh) * p.past_cap * p.D;
@@ -111,13 +113,13 @@ template <int DT> __global__ void gqa_prepare(const GqaPrepP p) {
         if (p.in_place) {
             // the buffer already holds the valid past; write the new rows ...
             long long j = t0, t = past_b + j;
-            if (t < p.T) {
+            if (t < T) {
                 st<DT>(p.present_k, pres_base + t * p.D + e, new_k(j));
                 st<DT>(p.present_v, pres_base + t * p.D + e, new_v(j));
             }
             // ... and, for a ragged row, clear what lies beyond them
             if (j == p.S - 1)
-                for (long long z = past_b + p.S; z < p.T; z++) {
+                for (long long z = past_b + p.S; z < T; z++) {
                     st<DT>(p.present_k, pres_base + z * p.D + e, 0.f);
                     st<DT>(p.present_v, pres_base + z * p.D + e, 0.f);
                 }
@@ -143,11 +145,13 @@ struct GqaAttnP {
     const void* pv;
     const int* seqlens;
     const void* bias;
-    float* scores;      // [B,S,H,span]: scaled, biased, rounded scores of the visible keys (−inf beyond them)
+    float* scores;      // [B,S,H,span]: scaled, biased, rounded scores of the visible keys (−inf beyond
+                        // them); turned into exp(score − max) by the last CTA of gqa_scores
     float* stats;       // [B,S,H,2]: row max, Σ exp (rounded)
     double* part;       // [B,S,H,nsplit,D] partial P·V accumulators
     unsigned* counters; // [2][B·S·KV·groups]
     void* out;          // [B,S,H·D]
+    const long long* dyn_t;  // when set, the present length T is read from here
     long long B, S, H, KV, D, T, cap, window, chunk, span;
     long long bias_sb, bias_sh;
     float scale;  // rounded to the tensor dtype
@@ -171,7 +175,8 @@ __device__ __forceinline__ GqaWho gqa_who(const GqaAttnP& p, int GT) {
     w.h0 = w.kvh * w.G + w.gc * GT;
     long long tot = (long long)p.seqlens[w.b] + 1, past_b = tot - p.S > 0 ? tot - p.S : 0;
     long long qpos = past_b + w.s;
-    w.hi = qpos < p.T - 1 ? qpos : p.T - 1;
+    const long long T = p.dyn_t ? *p.dyn_t : p.T;
+    w.hi = qpos < T - 1 ? qpos : T - 1;
     w.lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;
     w.n = w.hi >= w.lo ? w.hi - w.lo + 1 : 0;
     w.query = ((w.b * p.S + w.s) * p.KV + w.kvh) * p.groups + w.gc;
@@ -233,33 +238,27 @@ template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_sc
     }
     if (!last_cta(p.counters + w.query, p.nsplit)) return;
 
-    // row statistics of the decomposition's Softmax (decomp.rs:174-183)
-    __shared__ float red[32];
-    __shared__ double redd[32];
-    for (int g = 0; g < GT; g++) {
+    // Row statistics of the decomposition's Softmax (decomp.rs:174-183), one warp
+    // per head: the scores are replaced by their rounded exponentials and the
+    // rounded sum is kept for the P·V pass.
+    for (int g = warp; g < GT; g += NW) {
         if (w.gc * GT + g >= w.G) continue;
-        const float* row = p.scores + ((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span;
+        float* row = p.scores + ((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span;
         float mx = -INFINITY;
-        for (long long i = threadIdx.x; i < w.n; i += blockDim.x) mx = fmaxf(mx, __ldcg(row + i));
-        mx = block_max(mx, red);
+        for (long long i = lane; i < w.n; i += 32) mx = fmaxf(mx, __ldcg(row + i));
+        mx = warp_max(mx);
         double sum = 0.0;
-        for (long long i = threadIdx.x; i < w.n; i += blockDim.x) {
+        for (long long i = lane; i < w.n; i += 32) {
             float e = rnd_d<DT>(exp((double)rnd<DT>(__ldcg(row + i) - mx)));
+            row[i] = e;
             sum += (double)e;
         }
-        // block sum in f64
         sum = warp_sum_d(sum);
-        __syncthreads();
-        if (lane == 0) redd[warp] = sum;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            double t = 0.0;
-            for (int k = 0; k < NW; k++) t += redd[k];
+        if (lane == 0) {
             float* st_ = p.stats + ((w.b * p.S + w.s) * p.H + w.h0 + g) * 2;
             st_[0] = mx;
-            st_[1] = rnd_d<DT>(t);
+            st_[1] = rnd_d<DT>(sum);
         }
-        __syncthreads();
     }
 }
 
@@ -270,13 +269,12 @@ template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_pv
     const long long split = blockIdx.x;
     const GqaWho w = gqa_who(p, GT);
 
-    float mx[GT], sum[GT];
+    float sum[GT];
     double acc[GT][DPL];
 #pragma unroll
     for (int g = 0; g < GT; g++) {
         bool live = w.gc * GT + g < w.G;
         const float* st_ = p.stats + ((w.b * p.S + w.s) * p.H + w.h0 + g) * 2;
-        mx[g] = live ? st_[0] : 0.f;
         sum[g] = live ? st_[1] : 1.f;
 #pragma unroll
         for (int i = 0; i < DPL; i++) acc[g][i] = 0.0;
@@ -293,8 +291,7 @@ template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_pv
 #pragma unroll
         for (int g = 0; g < GT; g++) {
             if (w.gc * GT + g >= w.G) continue;
-            float sc = p.scores[((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span + i];
-            float e = rnd_d<DT>(exp((double)rnd<DT>(sc - mx[g])));
+            float e = p.scores[((w.b * p.S + w.s) * p.H + w.h0 + g) * p.span + i];  // exponentials by now
             float pr = rnd<DT>(e / sum[g]);
 #pragma unroll
             for (int k = 0; k < DPL; k++) acc[g][k] += (double)pr * (double)vx[k];
@@ -340,6 +337,11 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
     pp.B = B; pp.S = S; pp.H = H; pp.KV = KV; pp.D = D; pp.P = P; pp.T = T;
     pp.past_cap = past_k.cap ? past_k.cap : P;
     pp.pres_cap = present_k.cap ? present_k.cap : T;
+    // With a bucket the true length travels through the plan's per-run scalars.
+    const bool dyn = d.t_bucket > 0 && d.in_place && !bias;
+    const long long Tsz = dyn ? d.t_bucket : T;
+    Buf dyn_t = dyn ? em.dyn(T) : null;
+    if (dyn) pp.P = pp.T = 0;
     pp.half = d.rot_half;
     pp.cache_rows = d.cache_rows;
     pp.in_place = d.in_place ? 1 : 0;
@@ -350,11 +352,12 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
     em.launch(gqa_prepare<DT>, dim3(grid_for(pp.nq + pp.nkv, 256)), dim3(256), 0, pp,
               {{&pp.q, q.buf}, {&pp.k, k.buf}, {&pp.v, v.buf}, {&pp.past_k, past_k.buf}, {&pp.past_v, past_v.buf},
                {&pp.seqlens, seqlens.buf}, {&pp.cos, cos ? cos->buf : null}, {&pp.sin, sin ? sin->buf : null},
-               {&pp.q_rot, qrot}, {&pp.present_k, present_k.buf}, {&pp.present_v, present_v.buf}, {&pp.err, Buf{kSlotErr, 0}}},
+               {&pp.q_rot, qrot}, {&pp.present_k, present_k.buf}, {&pp.present_v, present_v.buf}, {&pp.err, Buf{kSlotErr, 0}},
+               {&pp.dyn_t, dyn_t}},
               "gqa_prepare");
 
     GqaAttnP ap{};
-    ap.B = B; ap.S = S; ap.H = H; ap.KV = KV; ap.D = D; ap.T = T;
+    ap.B = B; ap.S = S; ap.H = H; ap.KV = KV; ap.D = D; ap.T = dyn ? 0 : T;
     ap.cap = pp.pres_cap;
     ap.window = d.window;
     ap.scale = DT == DT_F16 ? __half2float(__double2half(d.scale)) : (float)d.scale;
@@ -365,12 +368,12 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
     const long long G = H / KV;
     const int GT = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
     ap.groups = (int)((G + GT - 1) / GT);
-    ap.span = (d.window >= 0 && d.window + 1 < T) ? d.window + 1 : T;
+    ap.span = (d.window >= 0 && d.window + 1 < Tsz) ? d.window + 1 : Tsz;
     // Split the visible key range so that the launch fills the machine; the
     // arrival counters bound the number of queries a split launch may have.
     long long queries = B * KV * ap.groups * S;
     long long want = (148 * 4 + queries - 1) / queries;   // ≈ 4 CTAs per SM
-    long long max_split = (ap.span + 15) / 16;            // ≥ 16 keys per CTA
+    long long max_split = (ap.span + 7) / 8;              // ≥ 8 keys per CTA (two per warp)
     long long nsplit = std::max<long long>(1, std::min<long long>(want, max_split));
     if (2 * queries > (long long)kCounterWords) nsplit = 1;
     nsplit = std::min<long long>(nsplit, 1024);
@@ -385,7 +388,7 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
 #define PTRS                                                                                                       \
     {{&ap.q, qsrc}, {&ap.pk, present_k.buf}, {&ap.pv, present_v.buf}, {&ap.seqlens, seqlens.buf},                  \
      {&ap.bias, bias ? bias->buf : null}, {&ap.scores, scores}, {&ap.stats, stats}, {&ap.part, part},              \
-     {&ap.counters, Buf{kSlotCounters, 0}}, {&ap.out, out.buf}}
+     {&ap.counters, Buf{kSlotCounters, 0}}, {&ap.out, out.buf}, {&ap.dyn_t, dyn_t}}
 #define GO(K, LABEL, DPL, GTT) em.launch(K<DT, DPL, GTT>, g, blk, 0, ap, PTRS, LABEL)
 #define GO_D(K, LABEL, GTT)                  \
     switch (D / 32) {                        \

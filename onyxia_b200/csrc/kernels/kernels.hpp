@@ -53,6 +53,13 @@ constexpr uint32_t kSlotNull = 0xFFFFFFF2u;     // resolves to nullptr
 // kernels that use it leave every word zero again when they finish.
 constexpr uint32_t kSlotCounters = 0xFFFFFFF3u;
 constexpr size_t kCounterWords = 1 << 16;
+// The plan's block of per-run scalars (int64 each; offset = byte position).
+// Values that change from run to run without changing the launch geometry —
+// the KV length of a decode step — are read from here by the kernels, so the
+// parameter bytes of their launches stay identical and a CUDA graph replays
+// unmodified. The session refreshes the block before every run.
+constexpr uint32_t kSlotDyn = 0xFFFFFFF4u;
+constexpr int kDynPerNode = 4;
 
 struct Reloc {
     uint32_t field_off;  // byte offset of a pointer field inside the parameter struct
@@ -85,6 +92,15 @@ public:
     void begin_node(int n) {
         node = n;
         scratch_cursor_ = 0;
+        dyn_vals.clear();
+    }
+    // Register a per-run scalar of the current node; kernels read it through
+    // the returned address instead of from their parameter bytes.
+    std::vector<int64_t> dyn_vals;
+    Buf dyn(int64_t value) {
+        if ((int)dyn_vals.size() >= kDynPerNode) throw std::runtime_error("too many per-run scalars for one node");
+        dyn_vals.push_back(value);
+        return Buf{kSlotDyn, (int64_t)((node * kDynPerNode + (int)dyn_vals.size() - 1) * 8)};
     }
 
     template <class P>
@@ -174,6 +190,10 @@ struct GqaDesc {
     bool has_bias;
     int64_t bias_b, bias_h;  // bias batch/head extents (1 = broadcast)
     bool in_place;         // present aliases past: only new rows are written
+    // > 0: size the key split for this many rows (a bucket ≥ past + seq) and let
+    // the kernels read the true length from the plan's per-run scalars, so a
+    // decode step changes no launch parameter until the bucket is outgrown.
+    int64_t t_bucket;
 };
 void emit_gqa(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef& v, const TRef& past_k,
               const TRef& past_v, const TRef& seqlens, const TRef* cos, const TRef* sin, const TRef* bias,
@@ -199,7 +219,10 @@ void emit_matmul_nbits_mma(Emitter&, const NBitsDesc&, const TRef& a, const TRef
 void emit_nbits_interleave(Emitter&, Buf src, Buf dst, long long bytes);
 
 // argmax over the last axis, highest index among equal maxima → i64.
-void emit_argmax_last(Emitter&, const TRef& x, const TRef& y);
+// `part` is scratch of argmax_scratch_bytes(rows) bytes, `counters` the zeroed arrival counters.
+constexpr int kArgmaxMaxBlocks = 128;
+inline size_t argmax_scratch_bytes(int64_t rows) { return (size_t)rows * kArgmaxMaxBlocks * 12 + 64; }
+void emit_argmax_last(Emitter&, const TRef& x, const TRef& y, Buf part, Buf counters);
 
 // Clear the error word (one tiny launch at the head of a plan is not needed:
 // the session clears it with a memset when it reads it).

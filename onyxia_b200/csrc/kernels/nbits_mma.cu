@@ -23,6 +23,8 @@
 //    order, so the result does not depend on scheduling.
 //
 // Algorithmic bytes: N·⌈K/32⌉·(16 + 2) + zero points + activations in/out.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.hpp"
 
@@ -107,22 +109,44 @@ __global__ void __launch_bounds__(128) nbits_gemv(const NBitsMmaP p) {
     int kt_end = kt_begin + p.tiles_per_split;
     if (kt_end > p.k_tiles) kt_end = p.k_tiles;
 
-    for (int kt = kt_begin + warp; kt < kt_end; kt += 4) {
+    // One tile of weights (two 16-byte blocks, their scales and zero points) per
+    // lane, fetched one iteration ahead so the loads of tile i+1 are in flight
+    // while tile i is widened and multiplied.
+    struct Tile {
+        uint4 wl, wh;
+        __half sl, sh;
+        int zl, zh;
+    };
+    auto fetch = [&](int kt) {
+        Tile tl;
+        tl.wl = make_uint4(0, 0, 0, 0);
+        tl.wh = tl.wl;
+        tl.sl = __float2half(0.f);
+        tl.sh = tl.sl;
+        tl.zl = 8;
+        tl.zh = 8;
         const long long kb = (long long)kt * 4 + t;
-        uint4 wl = make_uint4(0, 0, 0, 0), wh = wl;
-        __half sl = __float2half(0.f), sh = sl;
-        int zl = 8, zh = 8;
-        if (kb < nb) {
-            wl = __ldg(p.w + rl * nb + kb);
-            wh = __ldg(p.w + rh * nb + kb);
-            sl = p.scales[rl * nb + kb];
-            sh = p.scales[rh * nb + kb];
+        if (kt < kt_end && kb < nb) {
+            tl.wl = __ldg(p.w + rl * nb + kb);
+            tl.wh = __ldg(p.w + rh * nb + kb);
+            tl.sl = p.scales[rl * nb + kb];
+            tl.sh = p.scales[rh * nb + kb];
             if (p.zp) {
                 long long il = rl * nb + kb, ih = rh * nb + kb;
-                zl = (p.zp[il >> 1] >> ((il & 1) * 4)) & 0xF;
-                zh = (p.zp[ih >> 1] >> ((ih & 1) * 4)) & 0xF;
+                tl.zl = (p.zp[il >> 1] >> ((il & 1) * 4)) & 0xF;
+                tl.zh = (p.zp[ih >> 1] >> ((ih & 1) * 4)) & 0xF;
             }
         }
+        return tl;
+    };
+    Tile next = fetch(kt_begin + warp);
+    for (int kt = kt_begin + warp; kt < kt_end; kt += 4) {
+        const long long kb = (long long)kt * 4 + t;
+        const Tile cur = next;
+        next = fetch(kt + 4);
+        const uint4 wl = cur.wl, wh = cur.wh;
+        const __half sl = cur.sl, sh = cur.sh;
+        const int zl = cur.zl, zh = cur.zh;
         // activations of batch row g for block kb: 32 halves = four 16-byte words
         uint4 av[4];
 #pragma unroll
@@ -207,7 +231,12 @@ void emit_matmul_nbits_mma(Emitter& em, const NBitsDesc& d, const TRef& a, const
     p.row_tiles = (int)((d.n + 15) / 16);
     p.k_tiles = (int)((d.n_blocks + 3) / 4);
     // enough CTAs for ~4 per SM, at least one k-tile per warp
-    long long want = (148 * 4 + p.row_tiles - 1) / p.row_tiles;
+    static const int ctas_per_sm = [] {
+        const char* e = std::getenv("ONYXIA_GEMV_CTAS_PER_SM");  // tuning knob
+        int v = e ? std::atoi(e) : 4;
+        return v < 1 ? 1 : v;
+    }();
+    long long want = (148 * ctas_per_sm + p.row_tiles - 1) / p.row_tiles;
     long long max_split = (p.k_tiles + 3) / 4;
     p.ksplit = (int)std::max<long long>(1, std::min<long long>(want, max_split));
     p.tiles_per_split = (p.k_tiles + p.ksplit - 1) / p.ksplit;
