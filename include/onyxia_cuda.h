@@ -257,6 +257,23 @@ void ox_session_plan_stats(const ox_session*, uint64_t out[9]);
  * crates/onyxia-cli/src/sampling.rs:71-80, which keeps the last maximum).
  * Returns an I64 tensor shaped like `logits` without its last axis. */
 ox_status ox_session_argmax_last(ox_session*, const ox_tensor* logits, ox_tensor** out);
+/* The same argmax written into a tensor the caller already holds, without
+ * allocating anything: no device allocation, no buffer from the session's pool,
+ * no new tensor handle. One kernel is enqueued on the session's stream; its
+ * scratch is a fixed array inside the library's device image. This entry point
+ * has no counterpart in the reference; it exists for callers that must not
+ * allocate at the point where they sample (a serving loop running against a
+ * device-memory budget it has already committed in full, or a section that
+ * cannot tolerate the device-wide synchronisation an allocation may cause).
+ *   - `logits`: F32 or F16, densely packed, at most 64 rows (the product of all
+ *     axes but the last); more rows fail with OX_ERR_RUNTIME and a message that
+ *     names the limit. `out`: an I64 tensor with exactly one element per row.
+ *   - The first call on a device looks up the scratch array's address while that
+ *     device is current; make it before starting any stream capture.
+ *   - All calls on one device share the scratch array: calls that could execute
+ *     concurrently (other sessions, other host threads) race and must be ordered
+ *     by the caller. Calls on one session are ordered by its stream. */
+ox_status ox_session_argmax_last_into(ox_session*, const ox_tensor* logits, ox_tensor* out);
 
 #ifdef __cplusplus
 }

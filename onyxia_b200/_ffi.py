@@ -118,6 +118,7 @@ SIGNATURES = {
     "ox_session_launch_count": (C.c_uint64, [_P]),
     "ox_session_plan_stats": (None, [_P, _u64p]),
     "ox_session_argmax_last": (C.c_int32, [_P, _P, C.POINTER(_P)]),
+    "ox_session_argmax_last_into": (C.c_int32, [_P, _P, _P]),
 }
 
 # Symbols implemented by the host-only IR library (the rest need the CUDA one).

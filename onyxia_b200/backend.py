@@ -98,6 +98,10 @@ class CudaSession:
         check(self._lib.ox_session_argmax_last(self._h, t.handle, C.byref(out)))
         return DeviceTensor(out)
 
+    def argmax_last_into(self, t: DeviceTensor, out: DeviceTensor) -> None:
+        """Argmax over the last axis written into `out` (I64, one element per row); allocates nothing."""
+        check(self._lib.ox_session_argmax_last_into(self._h, t.handle, out.handle))
+
     # inherent methods of the reference session (session.rs:280-340)
     def wait_idle(self) -> None:
         check(self._lib.ox_session_wait_idle(self._h))

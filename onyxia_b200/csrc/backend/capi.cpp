@@ -211,4 +211,11 @@ ox_status ox_session_argmax_last(ox_session* s, const ox_tensor* logits, ox_tens
     OX_CATCH
 }
 
+ox_status ox_session_argmax_last_into(ox_session* s, const ox_tensor* logits, ox_tensor* out) {
+    OX_TRY
+    s->s->argmax_last_into(logits->t, out->t);
+    return OX_OK;
+    OX_CATCH
+}
+
 }  // extern "C"

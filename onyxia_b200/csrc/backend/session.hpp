@@ -79,6 +79,7 @@ public:
     std::vector<std::pair<std::string, DTensor>> run(const std::vector<std::pair<std::string, DTensor>>& inputs);
     void download(const DTensor& t, void* dst, size_t cap, size_t* written);
     DTensor argmax_last(const DTensor& logits);
+    void argmax_last_into(const DTensor& logits, const DTensor& out);
     void wait_idle();
     void timer_start();
     float timer_stop();

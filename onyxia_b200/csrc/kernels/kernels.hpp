@@ -224,6 +224,14 @@ constexpr int kArgmaxMaxBlocks = 128;
 inline size_t argmax_scratch_bytes(int64_t rows) { return (size_t)rows * kArgmaxMaxBlocks * 12 + 64; }
 void emit_argmax_last(Emitter&, const TRef& x, const TRef& y, Buf part, Buf counters);
 
+// The same argmax with its scratch in a fixed array of the module's global
+// data: launches one kernel on `stream` and allocates nothing. At most
+// kStaticArgmaxMaxRows rows per call; calls on one device share the array and
+// must not overlap. Returns nullptr, or a message describing the failure.
+constexpr int kStaticArgmaxMaxRows = 64;
+const char* argmax_last_static(int device, cudaStream_t stream, const void* x, int dtype, long long rows,
+                               long long cols, long long* y);
+
 // Clear the error word (one tiny launch at the head of a plan is not needed:
 // the session clears it with a memset when it reads it).
 }  // namespace oxk
