@@ -209,7 +209,8 @@ void nbits_lower(FusedCtx& c) {
     d.act_dtype = c.ins[0].dtype;
     d.scale_dtype = c.ins[2].dtype;
     d.has_zp = c.ins.size() > 3;
-    d.interleaved = c.weights_interleaved;
+    d.interleaved = c.weights_layout == 1;
+    d.tiled = c.weights_layout == 2;
     oxk::emit_matmul_nbits(c.em, d, c.ins[0], c.ins[1], c.ins[2], d.has_zp ? &c.ins[3] : nullptr, c.outs[0]);
 }
 

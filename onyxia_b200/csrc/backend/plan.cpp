@@ -260,7 +260,7 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
                 lower_prim(em, node, bindings, ins, outs);
             } else {
                 FusedCtx fc{em, node, ins, outs, (bool)kv_in_place[nid], false};
-                if (node.inputs.size() > 1) fc.weights_interleaved = interleaved_[node.inputs[1]] != 0;
+                if (node.inputs.size() > 1) fc.weights_layout = interleaved_[node.inputs[1]];
                 info_[nid].fused->lower(fc);
                 plan.node_bucket[nid] = fc.bucket;
                 plan.node_bucket_step[nid] = fc.bucket_step;
@@ -470,29 +470,54 @@ std::vector<Timing> Session::take_timings() {
     return out;
 }
 
+// One launch of a record with its parameter bytes. Kernels written for
+// programmatic dependent launch get the stream-serialisation attribute, so they
+// may begin while the launch before them is still running.
+void Session::launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_pdl) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = r.grid;
+    cfg.blockDim = r.block;
+    cfg.dynamicSmemBytes = r.smem;
+    cfg.stream = stream_;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (allow_pdl && r.pdl) ? 1 : 0;
+    void* args[1] = {param_bytes};
+    OX_CUDA(cudaLaunchKernelExC(&cfg, r.func, args));
+}
+
+// The plan's launch list as a CUDA graph, recorded by capturing the launches so
+// that programmatic-dependent-launch edges are kept. The node created by each
+// launch is remembered for later parameter updates.
 void Session::build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& params) {
     if (plan.exec) cudaGraphExecDestroy(plan.exec);
     if (plan.graph) cudaGraphDestroy(plan.graph);
     plan.exec = nullptr;
     plan.graph = nullptr;
     plan.graph_nodes.clear();
-    OX_CUDA(cudaGraphCreate(&plan.graph, 0));
-    cudaGraphNode_t prev = nullptr;
-    for (size_t i = 0; i < plan.recs.size(); i++) {
-        const oxk::LaunchRec& r = plan.recs[i];
-        cudaKernelNodeParams kp{};
-        void* args[1] = {const_cast<uint8_t*>(params[i].data())};
-        kp.func = const_cast<void*>(r.func);
-        kp.gridDim = r.grid;
-        kp.blockDim = r.block;
-        kp.sharedMemBytes = r.smem;
-        kp.kernelParams = args;
-        kp.extra = nullptr;
-        cudaGraphNode_t node;
-        OX_CUDA(cudaGraphAddKernelNode(&node, plan.graph, prev ? &prev : nullptr, prev ? 1 : 0, &kp));
-        plan.graph_nodes.push_back(node);
-        prev = node;
+    OX_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed));
+    try {
+        for (size_t i = 0; i < plan.recs.size(); i++) {
+            launch_rec(plan.recs[i], const_cast<uint8_t*>(params[i].data()), !opt_.disable_pdl);
+            cudaStreamCaptureStatus status;
+            const cudaGraphNode_t* deps = nullptr;
+            size_t n_deps = 0;
+            OX_CUDA(cudaStreamGetCaptureInfo_v3(stream_, &status, nullptr, nullptr, &deps, nullptr, &n_deps));
+            if (status != cudaStreamCaptureStatusActive || n_deps != 1)
+                fail(ErrKind::Runtime, "internal: stream capture lost track of a launch");
+            plan.graph_nodes.push_back(deps[0]);
+        }
+    } catch (...) {
+        cudaGraph_t dead = nullptr;
+        cudaStreamEndCapture(stream_, &dead);
+        if (dead) cudaGraphDestroy(dead);
+        cudaGetLastError();
+        plan.graph_nodes.clear();
+        throw;
     }
+    OX_CUDA(cudaStreamEndCapture(stream_, &plan.graph));
     OX_CUDA(cudaGraphInstantiate(&plan.exec, plan.graph, 0));
     plan.graph_params = params;
     plan.graph_grids.clear();
@@ -614,7 +639,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
                 pr.node = r.node;
                 OX_CUDA(cudaEventRecord(pr.a, stream_));
             }
-            OX_CUDA(cudaLaunchKernel(r.func, r.grid, r.block, args, r.smem, stream_));
+            launch_rec(r, args[0], !profiling && !opt_.disable_pdl);
             launch_count++;
             if (profiling) {
                 OX_CUDA(cudaEventRecord(pr.b, stream_));

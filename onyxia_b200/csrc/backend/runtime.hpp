@@ -89,6 +89,7 @@ struct Options {
     bool without_fused = false;
     bool disable_graphs = false;
     bool disable_pattern_fusion = false;
+    bool disable_pdl = false;  // launch every kernel fully serialised
 };
 
 class Session;
@@ -100,8 +101,9 @@ struct FusedCtx {
     const std::vector<oxk::TRef>& ins;
     const std::vector<oxk::TRef>& outs;
     bool kv_in_place = false;
-    // MatMulNBits: the weight constant (input 1) holds the interleaved layout.
-    bool weights_interleaved = false;
+    // MatMulNBits: layout of the weight constant (input 1): 0 as uploaded,
+    // 1 nibble-interleaved, 2 tile records with scales and zero points inside.
+    int weights_layout = 0;
     // Set by a kernel that sized its launch for a bucket of a growing dimension
     // and reads the true value from the per-run scalars: the launch stays valid
     // while the value stays in (bucket − bucket_step, bucket].

@@ -120,6 +120,7 @@ Session::Session(Backend& backend, Module legalized)
     : backend_(backend), opt_(backend.options()), device_(backend.device()), pool_(std::make_shared<Pool>(backend.device())),
       module_(std::move(legalized)) {
     OX_CUDA(cudaSetDevice(device_));
+    if (const char* e = std::getenv("ONYXIA_DISABLE_PDL")) opt_.disable_pdl = opt_.disable_pdl || std::atoi(e) != 0;  // diagnostics
     OX_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     OX_CUDA(cudaMalloc((void**)&d_err_, sizeof(oxk::ErrWord)));
     OX_CUDA(cudaMemset(d_err_, 0, sizeof(oxk::ErrWord)));
@@ -356,14 +357,20 @@ void Session::launch_now(const oxk::Emitter& em, const std::vector<void*>& slots
     }
 }
 
-// Weight constants read only by f16 MatMulNBits nodes get the interleaved
-// nibble layout of the tensor-core GEMV (a backend-private layout; the
-// caller's bytes were consumed by prepare).
+// Weight constants read only by f16 MatMulNBits nodes are re-laid out for the
+// decode kernels (backend-private layouts; the caller's bytes were consumed by
+// prepare). Preferred: tile records that hold a tile's nibbles, scales and zero
+// points together, which needs every reader of the weight to use the same
+// constant scales and zero points. Otherwise: nibbles interleaved in place.
 void Session::interleave_weights() {
     const Module& m = module_;
     interleaved_.assign(m.values.size(), 0);
     if (opt_.without_fused) return;
+    const char* layout_env = std::getenv("ONYXIA_GEMV_LAYOUT");  // "interleaved" forces the older layout
+    const bool allow_tiled = !(layout_env && std::string(layout_env) == "interleaved");
     std::vector<int> total(m.values.size(), 0), eligible(m.values.size(), 0);
+    // per weight: the scales / zero-point values its readers use (−1 none yet, −2 readers disagree)
+    std::vector<long long> w_scales(m.values.size(), -1), w_zp(m.values.size(), -1);
     for (auto& n : m.nodes)
         for (auto v : n.inputs) total[v]++;
     for (auto& o : m.outputs) total[o.second]++;
@@ -371,12 +378,36 @@ void Session::interleave_weights() {
         const Node& n = m.nodes[i];
         if (n.is_prim || n.composite.name != "com.microsoft.MatMulNBits" || !info_[i].fused) continue;
         if (m.values[n.inputs[0]].ty.dtype != DType::F16 || m.values[n.inputs[2]].ty.dtype != DType::F16) continue;
-        eligible[n.inputs[1]]++;
+        ValueId w = n.inputs[1];
+        eligible[w]++;
+        long long sc = m.values[n.inputs[2]].origin.kind == Origin::Const ? (long long)n.inputs[2] : -2;
+        long long zp = n.inputs.size() > 3 ? (m.values[n.inputs[3]].origin.kind == Origin::Const ? (long long)n.inputs[3] : -2) : -3;
+        w_scales[w] = w_scales[w] == -1 || w_scales[w] == sc ? sc : -2;
+        w_zp[w] = w_zp[w] == -1 || w_zp[w] == zp ? zp : -2;
     }
     std::unordered_map<void*, char> done;
     for (ValueId v = 0; v < m.values.size(); v++) {
         if (!eligible[v] || eligible[v] != total[v] || !consts_[v].buf) continue;
         // constants sharing one pool entry share one device buffer
+        bool shared = false;
+        for (ValueId u = 0; u < m.values.size(); u++)
+            if (u != v && consts_[u].buf == consts_[v].buf) shared = true;
+        auto wd = shape_as_static(m.values[v].ty.shape);
+        const bool tiled = allow_tiled && !shared && w_scales[v] >= 0 && w_zp[v] != -2 && wd && wd->size() == 3 &&
+                           consts_[(ValueId)w_scales[v]].buf && (w_zp[v] < 0 || consts_[(ValueId)w_zp[v]].buf);
+        if (tiled) {
+            const long long n_rows = (long long)(*wd)[0], nb = (long long)(*wd)[1];
+            const bool has_zp = w_zp[v] >= 0;
+            BufferRef dst = pool_->alloc(std::max<size_t>(oxk::nbits_tiled_bytes(n_rows, nb, has_zp), 16));
+            oxk::Emitter em;
+            oxk::emit_nbits_pack_tiles(em, oxk::Buf{0, 0}, oxk::Buf{1, 0}, oxk::Buf{2, 0}, oxk::Buf{3, 0}, n_rows, nb, has_zp);
+            launch_now(em, {consts_[v].buf->ptr, consts_[(ValueId)w_scales[v]].ptr(),
+                            has_zp ? consts_[(ValueId)w_zp[v]].ptr() : nullptr, dst->ptr});
+            OX_CUDA(cudaStreamSynchronize(stream_));  // the source buffer may be released below
+            consts_[v].buf = dst;
+            interleaved_[v] = 2;
+            continue;
+        }
         bool shared_ok = true;
         for (ValueId u = 0; u < m.values.size(); u++)
             if (u != v && consts_[u].buf == consts_[v].buf && (eligible[u] != total[u] || !eligible[u])) shared_ok = false;

@@ -132,6 +132,7 @@ private:
     void finish_outputs(Plan& plan);
     void execute(Plan& plan, const std::vector<DTensor>& inputs, std::vector<BufferRef>& out_bufs);
     void build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& params);
+    void launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_pdl);
     void check_device_error();
     DTensor dense_copy(const DTensor& t);
 
@@ -148,7 +149,7 @@ private:
     std::vector<int> last_use_;             // per root value: last step reading it
     std::vector<std::vector<ValueId>> deaths_;  // per step: roots that die after it
     std::vector<DTensor> consts_;           // per value (empty unless Origin::Const)
-    std::vector<char> interleaved_;         // per value: u4 weight constant re-laid out for the tensor-core GEMV
+    std::vector<char> interleaved_;         // per value: layout of a u4 weight constant (0 as uploaded, 1 interleaved, 2 tiled)
     unsigned* d_counters_ = nullptr;        // kCounterWords zeroed arrival counters
     std::vector<int> input_index_;          // per value: position in module.inputs or −1
     std::vector<char> is_output_root_;      // per value

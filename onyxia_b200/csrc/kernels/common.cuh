@@ -93,6 +93,17 @@ __device__ __forceinline__ long long nd_offset(long long linear, const NdShape& 
     return off;
 }
 
+// Programmatic dependent launch. `pdl_trigger` lets the next kernel in the
+// stream start its prologue once every CTA of this grid has called it;
+// `pdl_wait` returns when all earlier grids have completed and their writes are
+// visible. Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+    pdl_trigger();
+    pdl_wait();
+}
+
 __device__ __forceinline__ long long global_tid() {
     return (long long)blockIdx.x * blockDim.x + threadIdx.x;
 }

@@ -93,6 +93,7 @@ struct RmsNormP {
 // stays in registers (one DRAM latency instead of three).
 template <int DT, int EPT> __global__ void __launch_bounds__(1024) fused_rmsnorm(const RmsNormP p) {
     __shared__ double redd[32];
+    pdl_enter();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
     for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const long long base = row * p.cols;
@@ -161,7 +162,7 @@ void emit_rmsnorm(Emitter& em, const TRef& x, const TRef& w, const TRef& y, doub
     dim3 g((unsigned)std::min<long long>(p.rows, 148 * 32)), b((unsigned)threads);
     Buf rb = res ? res->buf : Buf{kSlotNull, 0}, sb = sum_out ? sum_out->buf : Buf{kSlotNull, 0};
 #define GO(DT, E) \
-    em.launch(fused_rmsnorm<DT, E>, g, b, 0, p, {{&p.x, x.buf}, {&p.res, rb}, {&p.w, w.buf}, {&p.y, y.buf}, {&p.sum_out, sb}}, "fused_rmsnorm")
+    em.launch(fused_rmsnorm<DT, E>, g, b, 0, p, {{&p.x, x.buf}, {&p.res, rb}, {&p.w, w.buf}, {&p.y, y.buf}, {&p.sum_out, sb}}, "fused_rmsnorm", /*pdl=*/true)
 #define GO_E(DT)                    \
     if (ept <= 1) GO(DT, 1);        \
     else if (ept <= 2) GO(DT, 2);   \
@@ -194,6 +195,7 @@ __device__ __forceinline__ double erf_as_f(float xf) {  // Abramowitz–Stegun 7
 }
 
 template <int DT> __global__ void fused_gelu(const GeluP p) {
+    pdl_enter();
     for (long long i = global_tid(); i < p.n; i += global_threads()) {
         float x = ld<DT>(p.x, i);
         float inner;
@@ -230,8 +232,8 @@ void emit_gelu(Emitter& em, const TRef& x, const TRef& y, bool tanh_approx, cons
     dim3 g(grid_for(p.n, 256)), b(256);
     Buf mb = mul ? mul->buf : Buf{kSlotNull, 0};
     const char* label = mul ? "fused_geglu" : "fused_gelu";
-    if (x.dtype == DT_F32) em.launch(fused_gelu<DT_F32>, g, b, 0, p, {{&p.x, x.buf}, {&p.mul, mb}, {&p.y, y.buf}}, label);
-    else em.launch(fused_gelu<DT_F16>, g, b, 0, p, {{&p.x, x.buf}, {&p.mul, mb}, {&p.y, y.buf}}, label);
+    if (x.dtype == DT_F32) em.launch(fused_gelu<DT_F32>, g, b, 0, p, {{&p.x, x.buf}, {&p.mul, mb}, {&p.y, y.buf}}, label, /*pdl=*/true);
+    else em.launch(fused_gelu<DT_F16>, g, b, 0, p, {{&p.x, x.buf}, {&p.mul, mb}, {&p.y, y.buf}}, label, /*pdl=*/true);
 }
 
 // ───────────────────────────── RotaryEmbedding ──────────────────────────

@@ -79,6 +79,7 @@ __device__ __forceinline__ float rope_elem(const void* x, long long base, long l
 }
 
 template <int DT> __global__ void gqa_prepare(const GqaPrepP p) {
+    pdl_enter();
     const long long total = p.nq + p.nkv;
     const long long T = p.dyn_t ? *p.dyn_t : p.T;
     for (long long i = global_tid(); i < total; i += global_threads()) {
@@ -202,6 +203,7 @@ __device__ __forceinline__ bool last_cta(unsigned* counter, int expected) {
 // DPL = head-dim elements per lane (D = 32·DPL), GT = query heads per CTA.
 template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_scores(const GqaAttnP p) {
     constexpr int NW = 4;
+    pdl_enter();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long split = blockIdx.x;
     const GqaWho w = gqa_who(p, GT);
@@ -264,6 +266,7 @@ template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_sc
 
 template <int DT, int DPL, int GT> __global__ void __launch_bounds__(128) gqa_pv(const GqaAttnP p) {
     constexpr int NW = 4;
+    pdl_enter();
     constexpr int D = 32 * DPL;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long split = blockIdx.x;
@@ -354,7 +357,7 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
                {&pp.seqlens, seqlens.buf}, {&pp.cos, cos ? cos->buf : null}, {&pp.sin, sin ? sin->buf : null},
                {&pp.q_rot, qrot}, {&pp.present_k, present_k.buf}, {&pp.present_v, present_v.buf}, {&pp.err, Buf{kSlotErr, 0}},
                {&pp.dyn_t, dyn_t}},
-              "gqa_prepare");
+              "gqa_prepare", /*pdl=*/true);
 
     GqaAttnP ap{};
     ap.B = B; ap.S = S; ap.H = H; ap.KV = KV; ap.D = D; ap.T = dyn ? 0 : T;
@@ -389,7 +392,7 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
     {{&ap.q, qsrc}, {&ap.pk, present_k.buf}, {&ap.pv, present_v.buf}, {&ap.seqlens, seqlens.buf},                  \
      {&ap.bias, bias ? bias->buf : null}, {&ap.scores, scores}, {&ap.stats, stats}, {&ap.part, part},              \
      {&ap.counters, Buf{kSlotCounters, 0}}, {&ap.out, out.buf}, {&ap.dyn_t, dyn_t}}
-#define GO(K, LABEL, DPL, GTT) em.launch(K<DT, DPL, GTT>, g, blk, 0, ap, PTRS, LABEL)
+#define GO(K, LABEL, DPL, GTT) em.launch(K<DT, DPL, GTT>, g, blk, 0, ap, PTRS, LABEL, /*pdl=*/true)
 #define GO_D(K, LABEL, GTT)                  \
     switch (D / 32) {                        \
         case 1: GO(K, LABEL, 1, GTT); break; \

@@ -74,6 +74,12 @@ struct LaunchRec {
     std::vector<Reloc> relocs;
     const char* label = "";
     int node = -1;  // IR node index, for error messages and profiling
+    // The kernel executes `griddepcontrol.wait` before it reads anything an
+    // earlier launch wrote and before it writes anything at all, on every path
+    // to its exit. Such a kernel may be launched while its predecessor in the
+    // stream is still running (programmatic dependent launch): its prologue —
+    // barrier set-up, prefetch of constant weights — overlaps the predecessor.
+    bool pdl = false;
 };
 
 class Emitter {
@@ -105,7 +111,7 @@ public:
 
     template <class P>
     void launch(void (*kernel)(const P), dim3 grid, dim3 block, unsigned smem, const P& p,
-                std::initializer_list<std::pair<const void*, Buf>> ptrs, const char* label) {
+                std::initializer_list<std::pair<const void*, Buf>> ptrs, const char* label, bool pdl = false) {
         static_assert(sizeof(P) <= 4000, "kernel parameter struct too large");
         LaunchRec r;
         r.func = (const void*)kernel;
@@ -122,6 +128,7 @@ public:
         }
         r.label = label;
         r.node = node;
+        r.pdl = pdl;
         recs.push_back(std::move(r));
     }
 
@@ -206,6 +213,10 @@ struct NBitsDesc {
     // The weight constant was re-laid out by emit_nbits_interleave (backend-
     // private layout for the tensor-core decode kernel).
     bool interleaved;
+    // The weight constant was replaced by tile records holding nibbles, scales
+    // and zero points together (emit_nbits_pack_tiles); `scales` and `zp` are
+    // not read by the kernel.
+    bool tiled;
 };
 // y[m, n] = a[m, :] · dequant(w)[n, :]ᵀ for packed u4 weights [N, n_blocks, bs].
 void emit_matmul_nbits(Emitter&, const NBitsDesc&, const TRef& a, const TRef& w, const TRef& scales,
@@ -217,6 +228,13 @@ void emit_matmul_nbits_mma(Emitter&, const NBitsDesc&, const TRef& a, const TRef
 // One-time re-layout of a packed u4 weight constant: within each 32-bit word,
 // nibble j moves to position (j >> 1) + 4·(j & 1).
 void emit_nbits_interleave(Emitter&, Buf src, Buf dst, long long bytes);
+
+// Streaming decode kernel over tile-major weight records (f16 activations and scales).
+void emit_matmul_nbits_stream(Emitter&, const NBitsDesc&, const TRef& a, const TRef& tiles, const TRef& y);
+// One-time gathering of a packed u4 weight [N, n_blocks, 32], its f16 scales
+// and optional u4 zero points into tile records; `dst` needs nbits_tiled_bytes.
+size_t nbits_tiled_bytes(long long n, long long n_blocks, bool has_zp);
+void emit_nbits_pack_tiles(Emitter&, Buf w, Buf scales, Buf zp, Buf dst, long long n, long long n_blocks, bool has_zp);
 
 // argmax over the last axis, highest index among equal maxima → i64.
 // `part` is scratch of argmax_scratch_bytes(rows) bytes, `counters` the zeroed arrival counters.

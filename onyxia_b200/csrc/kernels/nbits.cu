@@ -115,6 +115,10 @@ void emit_matmul_nbits(Emitter& em, const NBitsDesc& d, const TRef& a, const TRe
                        const TRef* zp, const TRef& y) {
     if (d.block_size != 32) throw std::runtime_error("nbits kernels need block_size 32");
     if (d.m == 0 || d.n == 0) return;
+    if (d.tiled) {
+        emit_matmul_nbits_stream(em, d, a, w, y);
+        return;
+    }
     if (d.interleaved) {
         emit_matmul_nbits_mma(em, d, a, w, scales, zp, y);
         return;

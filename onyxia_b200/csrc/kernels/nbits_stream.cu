@@ -1,0 +1,456 @@
+// Streaming MatMulNBits for the decode path (f16 activations, f16 scales, up
+// to 8 activation rows per pass):
+//   y[m, n] = Σ_k a[m, k] · round_f16((q[n, k] − zp[n, k/32]) · s[n, k/32])
+//
+// The kernel is bound by the HBM read of the weights, so everything is built
+// around keeping that read a long, contiguous, deeply pipelined stream.
+//
+//  * Tile-major weights. At prepare time the packed nibbles, the scales and the
+//    zero points of every 16-row × 128-column tile are gathered into one
+//    contiguous record (`nbits_pack_tiles`): 1024 B of nibbles in the order the
+//    lanes consume them, 128 B of scales (a lane's two rows side by side), 64 B
+//    of zero points when the matrix has them. Records follow each other row tile by row tile, k tile by k tile;
+//    rows and blocks beyond the matrix are stored as zero weights with zero
+//    scale, so the inner loop has no bounds checks.
+//  * One stream per warp. The records are numbered 0 … row_tiles·k_tiles − 1
+//    and cut into equal contiguous ranges, one per warp of the grid. A warp
+//    moves its range through a private ring of shared-memory stages with bulk
+//    asynchronous copies (`cp.async.bulk`, completion counted on an mbarrier per
+//    stage), so each warp keeps several kilobytes in flight without holding
+//    them in registers, and no block-wide barrier sits in the loop.
+//  * Tensor-core inner product. Lane (g, t) widens the 32 nibbles of rows g and
+//    g + 8 at block t of the tile (0x6400 trick, exact (q − zp)·s rounding) and
+//    feeds them to m16n8k16 MMAs as the A operand; the B operand holds up to 8
+//    activation rows, staged once per CTA in shared memory in fragment order.
+//    Tiles are summed in f32 on two independent MMA chains; every few tiles
+//    the f32 sums move to an f64 accumulator.
+//  * Ranges ignore row-tile boundaries. A warp that covers all k tiles of a row
+//    tile stores the result directly; the pieces of a row tile shared between
+//    neighbouring warps go to scratch, and the last warp to arrive (one counter
+//    per row tile) adds the pieces in range order, so results do not depend on
+//    scheduling.
+//
+// Algorithmic bytes: N·⌈K/32⌉·(16 + 2) (+ N·⌈K/32⌉/2 zero points) + activations.
+#include <cstdlib>
+
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace oxk {
+
+namespace {
+
+constexpr int kWarps = 8;           // warps per CTA, each with its own stream
+constexpr int kTileW = 1024;        // nibble bytes per tile record
+constexpr int kTileS = 128;         // scale bytes per tile record
+constexpr int kTileZ = 64;          // zero-point bytes per tile record (when present)
+constexpr int kStageTiles = 3;      // tile records per pipeline stage
+constexpr int kStages = 3;          // pipeline depth per warp
+constexpr int kFoldTiles = 4;       // tiles summed in f32 before the sum moves to the f64 accumulator
+constexpr long long kWaitCycles = 2000000000LL;  // ≈ 1 s: how long a stage may take to land before giving up
+
+// ── prepare-time packing ────────────────────────────────────────────────
+struct PackP {
+    const unsigned* w;           // [N][nb][4] words, natural nibble order
+    const __half* scales;        // [N][nb]
+    const unsigned char* zp;     // packed nibbles over [N][nb], or null
+    unsigned char* dst;
+    long long n, nb, row_tiles, k_tiles;
+    int tile_bytes;
+};
+
+__device__ __forceinline__ unsigned interleave_word(unsigned w) {
+    unsigned o = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) o |= ((w >> (4 * j)) & 0xFu) << (4 * ((j >> 1) + 4 * (j & 1)));
+    return o;
+}
+
+// One thread per (tile, half h, row g, block t): 16 B of nibbles, one scale, one zero point.
+__global__ void nbits_pack_tiles(const PackP p) {
+    const long long units = p.row_tiles * p.k_tiles * 64;
+    for (long long u = global_tid(); u < units; u += global_threads()) {
+        const int slot = (int)(u & 63);  // h·32 + g·4 + t
+        const long long tile = u >> 6;
+        const long long rt = tile / p.k_tiles, kt = tile % p.k_tiles;
+        const long long row = rt * 16 + (slot >> 5) * 8 + ((slot >> 2) & 7), kb = kt * 4 + (slot & 3);
+        unsigned char* rec = p.dst + tile * p.tile_bytes;
+        uint4 q = make_uint4(0, 0, 0, 0);
+        __half s = __float2half(0.f);
+        unsigned char z = 8;
+        if (row < p.n && kb < p.nb) {
+            const unsigned* src = p.w + (row * p.nb + kb) * 4;
+            q = make_uint4(interleave_word(src[0]), interleave_word(src[1]), interleave_word(src[2]), interleave_word(src[3]));
+            s = p.scales[row * p.nb + kb];
+            if (p.zp) {
+                long long i = row * p.nb + kb;
+                z = (p.zp[i >> 1] >> ((i & 1) * 4)) & 0xF;
+            }
+        }
+        reinterpret_cast<uint4*>(rec)[slot] = q;
+        // scales and zero points: the values of rows g and g + 8 side by side per lane
+        const int pair = (slot & 31) * 2 + (slot >> 5);
+        reinterpret_cast<__half*>(rec + kTileW)[pair] = s;
+        if (p.zp) rec[kTileW + kTileS + pair] = z;
+    }
+}
+
+// ── PTX helpers ─────────────────────────────────────────────────────────
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the barrier did not complete within kWaitCycles.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (clock64() - t0 < kWaitCycles)
+        if (mbar_try(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mma16816s(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                          unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned hu(__half2 h) { return *reinterpret_cast<unsigned*>(&h); }
+__device__ __forceinline__ __half2 uh(unsigned u) { return *reinterpret_cast<__half2*>(&u); }
+
+// (a & b) | c in one instruction.
+__device__ __forceinline__ unsigned and_or(unsigned a, unsigned b, unsigned c) {
+    unsigned d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// One 32-bit word (8 interleaved nibbles) → four scaled f16 pairs {k0,k1} {k2,k3} {k4,k5} {k6,k7}.
+// The low nibble of each half-word becomes the f16 1024 + q, the next one 1024 + 16·q.
+__device__ __forceinline__ void widen_word(unsigned w, __half2 sub_lo, __half2 add_hi, __half2 s2, unsigned (&out)[4]) {
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    const unsigned magic = 0x64006400u, m_lo = 0x000F000Fu, m_hi = 0x00F000F0u;
+    const unsigned lo = and_or(w, m_lo, magic), hi = and_or(w, m_hi, magic);
+    const unsigned w8 = w >> 8;
+    const unsigned lo2 = and_or(w8, m_lo, magic), hi2 = and_or(w8, m_hi, magic);
+    out[0] = hu(__hmul2(__hsub2(uh(lo), sub_lo), s2));
+    out[1] = hu(__hmul2(__hfma2(uh(hi), sixteenth, add_hi), s2));
+    out[2] = hu(__hmul2(__hsub2(uh(lo2), sub_lo), s2));
+    out[3] = hu(__hmul2(__hfma2(uh(hi2), sixteenth, add_hi), s2));
+}
+
+}  // namespace
+
+struct StreamP {
+    const __half* a;
+    const unsigned char* tiles;
+    __half* y;
+    ErrWord* err;
+    long long m0, m_total, k, n;
+    int k_tiles, row_tiles, rts_per_cta, act_bytes, node;
+};
+
+// Result fragment of one row tile → y. c0:(row g, col 2t) c1:(row g, col 2t+1)
+// c2:(row g+8, col 2t) c3:(row g+8, col 2t+1); col = activation row.
+template <int MR> __device__ __forceinline__ void stream_store(const StreamP& p, const double (&acc)[4], long long rt, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const long long row = rt * 16 + g + (q >= 2 ? 8 : 0), col = p.m0 + 2 * t + (q & 1);
+        if (row < p.n && col < p.m_total && 2 * t + (q & 1) < MR) p.y[col * p.n + row] = __double2half(acc[q]);
+    }
+}
+
+template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2) nbits_stream(const StreamP p) {
+    constexpr int kTileBytes = kTileW + kTileS + (HAS_ZP ? kTileZ : 0);
+    constexpr int kStageBytes = kStageTiles * kTileBytes;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    unsigned char* ring = smem + p.act_bytes + warp * (kStages * kStageBytes);
+    const unsigned bars = smem_addr(smem + p.act_bytes + kWarps * kStages * kStageBytes) + warp * kStages * 8;
+
+    // pieces of row tiles shared between warps of this CTA: [warp][first / last piece][128]
+    double* pieces = reinterpret_cast<double*>(smem + p.act_bytes + kWarps * kStages * kStageBytes + kWarps * kStages * 8);
+
+    // This CTA owns `cta_rts` consecutive row tiles = cta_tiles consecutive tile
+    // records, cut into equal ranges for its warps.
+    const int cta_rt0 = blockIdx.x * p.rts_per_cta;
+    const int cta_rts = p.row_tiles - cta_rt0 < p.rts_per_cta ? p.row_tiles - cta_rt0 : p.rts_per_cta;
+    const int cta_tiles = cta_rts * p.k_tiles;
+    const int per = (cta_tiles + kWarps - 1) / kWarps;
+    const int beg = warp * per;
+    const int n_tiles = beg >= cta_tiles ? 0 : (cta_tiles - beg < per ? cta_tiles - beg : per);
+    const int n_stages = (n_tiles + kStageTiles - 1) / kStageTiles;
+    const unsigned char* src = p.tiles + ((long long)cta_rt0 * p.k_tiles + beg) * kTileBytes;
+
+    auto issue = [&](int st, int slot) {  // lane 0 only
+        int cnt = n_tiles - st * kStageTiles;
+        if (cnt > kStageTiles) cnt = kStageTiles;
+        const unsigned bytes = (unsigned)cnt * kTileBytes;
+        mbar_expect(bars + slot * 8, bytes);
+        bulk_load(smem_addr(ring + slot * kStageBytes), src + (size_t)st * kStageBytes, bytes, bars + slot * 8);
+    };
+
+    // The weights do not depend on the kernels before this one: start streaming
+    // them before waiting for the producer of the activations.
+    if (lane == 0) {
+        for (int s = 0; s < kStages; s++) mbar_init(bars + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int s = 0; s < kStages && s < n_stages; s++) issue(s, s);
+    }
+    __syncwarp();
+    pdl_trigger();
+    pdl_wait();
+
+    // Activations → shared memory in B-fragment order: chunk (kt·4 + m)·4·MR + g·4 + t
+    // holds a[m0 + g][kt·128 + t·32 + m·8 … + 8], zero beyond the matrix.
+    {
+        uint4* as = reinterpret_cast<uint4*>(smem);
+        const int chunks = p.k_tiles * 16 * MR;
+        const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.a) & 15) == 0;
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            const int ct = c & 3, cg = (c >> 2) % MR, cm = (c / (4 * MR)) & 3, ckt = c / (16 * MR);
+            const long long row = p.m0 + cg, k0 = (long long)ckt * 128 + ct * 32 + cm * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < p.m_total) {
+                const __half* s = p.a + row * p.k + k0;
+                if (vec && k0 + 8 <= p.k) {
+                    v = *reinterpret_cast<const uint4*>(s);
+                } else {
+                    __half tmp[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) tmp[e] = k0 + e < p.k ? s[e] : __float2half(0.f);
+                    v = *reinterpret_cast<uint4*>(tmp);
+                }
+            }
+            as[c] = v;
+        }
+    }
+    __syncthreads();
+
+    // lanes without an activation row read chunk 0 and ignore it
+    const bool has_b = g < MR;
+    const uint4* as_lane = reinterpret_cast<const uint4*>(smem) + (has_b ? g * 4 + t : 0);
+    int rt = beg / p.k_tiles;  // row tile within the CTA
+    const int kt0 = beg - rt * p.k_tiles;
+    const uint4* ap = as_lane + kt0 * (16 * MR);
+    int seg_left = p.k_tiles - kt0 < n_tiles ? p.k_tiles - kt0 : n_tiles;  // tiles to the end of this row tile's piece
+    int seg_len = seg_left, consumed = 0;
+    bool first_seg = true;
+    int remaining = n_tiles, group = 0;
+    float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};
+    const __half2 sub_c = __float2half2_rn(1032.f), add_c = __float2half2_rn(-72.f);  // zero point 8
+
+    bool ok = true;
+    int st = 0, slot = 0;
+    unsigned parity = 0;
+    for (; st < n_stages; st++) {
+        if (!mbar_wait(bars + slot * 8, parity)) {
+            ok = false;
+            break;
+        }
+        const unsigned char* rec = ring + slot * kStageBytes;
+#pragma unroll
+        for (int j = 0; j < kStageTiles; j++) {
+            if (j < remaining) {
+                const uint4* wq = reinterpret_cast<const uint4*>(rec + j * kTileBytes);
+                const uint4 wl = wq[lane], wh = wq[32 + lane];
+                const __half2 s2 = reinterpret_cast<const __half2*>(rec + j * kTileBytes + kTileW)[lane];  // {row g, row g+8}
+                const __half2 s2l = __low2half2(s2), s2h = __high2half2(s2);
+                __half2 subl = sub_c, subh = sub_c, addl = add_c, addh = add_c;
+                if (HAS_ZP) {
+                    const uchar2 z = reinterpret_cast<const uchar2*>(rec + j * kTileBytes + kTileW + kTileS)[lane];
+                    subl = __float2half2_rn(1024.f + (float)z.x);
+                    subh = __float2half2_rn(1024.f + (float)z.y);
+                    addl = __float2half2_rn(-64.f - (float)z.x);
+                    addh = __float2half2_rn(-64.f - (float)z.y);
+                }
+                const uint4 av0 = ap[0], av1 = ap[4 * MR], av2 = ap[8 * MR], av3 = ap[12 * MR];
+                unsigned al[4], ah[4];
+                widen_word(wl.x, subl, addl, s2l, al);
+                widen_word(wh.x, subh, addh, s2h, ah);
+                mma16816s(ca, al[0], ah[0], al[1], ah[1], av0.x, av0.y);
+                mma16816s(cb, al[2], ah[2], al[3], ah[3], av0.z, av0.w);
+                widen_word(wl.y, subl, addl, s2l, al);
+                widen_word(wh.y, subh, addh, s2h, ah);
+                mma16816s(ca, al[0], ah[0], al[1], ah[1], av1.x, av1.y);
+                mma16816s(cb, al[2], ah[2], al[3], ah[3], av1.z, av1.w);
+                widen_word(wl.z, subl, addl, s2l, al);
+                widen_word(wh.z, subh, addh, s2h, ah);
+                mma16816s(ca, al[0], ah[0], al[1], ah[1], av2.x, av2.y);
+                mma16816s(cb, al[2], ah[2], al[3], ah[3], av2.z, av2.w);
+                widen_word(wl.w, subl, addl, s2l, al);
+                widen_word(wh.w, subh, addh, s2h, ah);
+                mma16816s(ca, al[0], ah[0], al[1], ah[1], av3.x, av3.y);
+                mma16816s(cb, al[2], ah[2], al[3], ah[3], av3.z, av3.w);
+                ap += 16 * MR;
+                group++;
+                seg_left--;
+                if (group == kFoldTiles || seg_left == 0) {
+                    // f32 tile sums → f64 running sum
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        acc[q] += (double)(ca[q] + cb[q]);
+                        ca[q] = 0.f;
+                        cb[q] = 0.f;
+                    }
+                    group = 0;
+                }
+                consumed++;
+                if (seg_left == 0) {
+                    if (seg_len == p.k_tiles) {
+                        stream_store<MR>(p, acc, cta_rt0 + rt, lane);
+                    } else {
+                        double2* mine = reinterpret_cast<double2*>(pieces + (warp * 2 + (first_seg ? 0 : 1)) * 128) + 2 * lane;
+                        mine[0] = make_double2(acc[0], acc[1]);
+                        mine[1] = make_double2(acc[2], acc[3]);
+                    }
+                    acc[0] = acc[1] = acc[2] = acc[3] = 0.0;
+                    rt++;
+                    ap = as_lane;
+                    first_seg = false;
+                    const int rest = n_tiles - consumed;
+                    seg_left = p.k_tiles < rest ? p.k_tiles : rest;
+                    seg_len = seg_left;
+                }
+            }
+        }
+        remaining -= kStageTiles;
+        __syncwarp();  // every lane is done with this stage before it is refilled
+        if (lane == 0 && st + kStages < n_stages) issue(st + kStages, slot);
+        if (++slot == kStages) {
+            slot = 0;
+            parity ^= 1;
+        }
+    }
+    if (!ok) {
+        // A copy did not land in time. Record it, then give the copies still in
+        // flight a last bounded chance to land before this warp's ring goes away.
+        if (lane == 0) report(p.err, ERR_WAIT_TIMEOUT, p.node, (long long)blockIdx.x, (long long)st);
+        const int issued = st + kStages < n_stages ? st + kStages : n_stages;
+        for (int s = st; s < issued; s++) mbar_wait(bars + (s % kStages) * 8, (s / kStages) & 1);
+    }
+
+    // Row tiles cut by a boundary between two warps' ranges: the warp after the
+    // first boundary inside the row tile adds the pieces in range order.
+    __syncthreads();
+    const int b = warp * per;  // boundary before this warp's range
+    if (warp > 0 && b < cta_tiles && b % p.k_tiles != 0) {
+        const int r = b / p.k_tiles, t0 = r * p.k_tiles;
+        if ((warp - 1) * per <= t0) {
+            const int j0 = t0 / per, j1 = (t0 + p.k_tiles - 1) / per;
+            double sum[4] = {0.0, 0.0, 0.0, 0.0};
+            for (int w = j0; w <= j1; w++) {
+                // a warp's first piece lies in the row tile its range starts in
+                const double2* src2 = reinterpret_cast<const double2*>(pieces + (w * 2 + (w * per >= t0 ? 0 : 1)) * 128) + 2 * lane;
+                const double2 v0 = src2[0], v1 = src2[1];
+                sum[0] += v0.x;
+                sum[1] += v0.y;
+                sum[2] += v1.x;
+                sum[3] += v1.y;
+            }
+            stream_store<MR>(p, sum, cta_rt0 + r, lane);
+        }
+    }
+}
+
+size_t nbits_tiled_bytes(long long n, long long n_blocks, bool has_zp) {
+    const long long row_tiles = (n + 15) / 16, k_tiles = (n_blocks + 3) / 4;
+    return (size_t)(row_tiles * k_tiles) * (size_t)(kTileW + kTileS + (has_zp ? kTileZ : 0));
+}
+
+void emit_nbits_pack_tiles(Emitter& em, Buf w, Buf scales, Buf zp, Buf dst, long long n, long long n_blocks, bool has_zp) {
+    PackP p{};
+    p.n = n;
+    p.nb = n_blocks;
+    p.row_tiles = (n + 15) / 16;
+    p.k_tiles = (n_blocks + 3) / 4;
+    p.tile_bytes = kTileW + kTileS + (has_zp ? kTileZ : 0);
+    em.launch(nbits_pack_tiles, dim3(grid_for(p.row_tiles * p.k_tiles * 64, 256)), dim3(256), 0, p,
+              {{&p.w, w}, {&p.scales, scales}, {&p.zp, has_zp ? zp : Buf{kSlotNull, 0}}, {&p.dst, dst}}, "nbits_pack_tiles");
+}
+
+namespace {
+
+int env_int(const char* name, int dflt, int lo, int hi) {
+    const char* e = std::getenv(name);
+    int v = e ? std::atoi(e) : dflt;
+    return v < lo ? lo : (v > hi ? hi : v);
+}
+
+using StreamFn = void (*)(const StreamP);
+template <bool Z> StreamFn stream_fn(int mr) {
+    switch (mr) {
+        case 1: return nbits_stream<1, Z>;
+        case 2: return nbits_stream<2, Z>;
+        case 4: return nbits_stream<4, Z>;
+        default: return nbits_stream<8, Z>;
+    }
+}
+
+constexpr size_t kSmemBudget = 200 * 1024;
+
+}  // namespace
+
+void emit_matmul_nbits_stream(Emitter& em, const NBitsDesc& d, const TRef& a, const TRef& tiles, const TRef& y) {
+    StreamP p{};
+    p.m_total = d.m;
+    p.k = d.k;
+    p.n = d.n;
+    p.row_tiles = (int)((d.n + 15) / 16);
+    p.k_tiles = (int)((d.n_blocks + 3) / 4);
+    const int tile_bytes = kTileW + kTileS + (d.has_zp ? kTileZ : 0);
+    p.node = em.node;
+
+    // tuning knob: resident CTAs per SM the grid should fill
+    static const int ctas_per_sm = env_int("ONYXIA_GEMV_CTAS_PER_SM", 2, 1, 8);
+    p.rts_per_cta = (int)((p.row_tiles + 148LL * ctas_per_sm - 1) / (148LL * ctas_per_sm));
+    const long long grid = (p.row_tiles + p.rts_per_cta - 1) / p.rts_per_cta;
+
+    const size_t fixed = (size_t)kWarps * kStages * kStageTiles * tile_bytes + (size_t)kWarps * kStages * 8 +
+                         (size_t)kWarps * 2 * 128 * sizeof(double);
+    // activation rows per pass: as many (≤ 8) as fit beside the rings
+    int rows_per_pass = 8;
+    while (rows_per_pass > 1 && (size_t)p.k_tiles * 256 * rows_per_pass + fixed > kSmemBudget) rows_per_pass /= 2;
+    if ((size_t)p.k_tiles * 256 + fixed > kSmemBudget) throw std::runtime_error("MatMulNBits: K too large for the streaming kernel");
+
+    for (long long m0 = 0; m0 < d.m; m0 += rows_per_pass) {
+        const long long rows = std::min<long long>(rows_per_pass, d.m - m0);
+        const int mr = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
+        p.m0 = m0;
+        p.act_bytes = (p.k_tiles * 256 * mr + 127) / 128 * 128;
+        const size_t smem = (size_t)p.act_bytes + fixed;
+        StreamFn fn = d.has_zp ? stream_fn<true>(mr) : stream_fn<false>(mr);
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+            if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+        }
+        em.launch(fn, dim3((unsigned)grid), dim3(kWarps * 32), (unsigned)smem, p,
+                  {{&p.a, a.buf}, {&p.tiles, tiles.buf}, {&p.y, y.buf}, {&p.err, Buf{kSlotErr, 0}}}, "nbits_stream", /*pdl=*/true);
+    }
+}
+
+}  // namespace oxk
