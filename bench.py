@@ -138,6 +138,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -218,10 +220,14 @@ def main():
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     sampler.start()
+    if args.profiler_range:
+        torch.cuda.cudart().cudaProfilerStart()
     sess.timer_start()
     for i in range(W, W + K):
         tok = device_step(i, tok, kv)
     ms = sess.timer_stop()
+    if args.profiler_range:
+        torch.cuda.cudart().cudaProfilerStop()
     clocks = sampler.stop()
     torch.cuda.synchronize()
     if world > 1:
@@ -261,14 +267,15 @@ def main():
         a[0] += 1
         a[1] += ns
     peak, peak_kind = load_peaks()
-    gemv = by_kernel.get("nbits_gemv", [0, 0])
+    gemv_name = max((k for k in by_kernel if k.startswith("nbits_")), key=lambda k: by_kernel[k][1], default="nbits_stream")
+    gemv = by_kernel.get(gemv_name, [0, 0])
     weight_bytes = cfg.weight_bytes_per_token()
     # activations in and out of the 7 matrices per layer + lm_head, fp16
     act_bytes = 2 * (cfg.layers * (cfg.hidden * 4 + cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim +
                                    3 * cfg.ffn + cfg.hidden * 2) + cfg.hidden + cfg.vocab)
     alg_bytes_per_step = weight_bytes + act_bytes
     roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
-                "kernel": "nbits_gemv", "peak_source": peak_kind}
+                "kernel": gemv_name, "peak_source": peak_kind}
     if gemv[0]:
         gemv_s_per_step = gemv[1] / 1e9 / prof_steps
         roofline["achieved"] = alg_bytes_per_step / gemv_s_per_step / 1e9

@@ -73,7 +73,7 @@ def ir_sources():
 
 
 def cuda_sources():
-    pats = ["backend/*.cpp", "backend/*.hpp", "backend/*.cu", "backend/*.cuh", "kernels/*.cu", "kernels/*.cuh"]
+    pats = ["backend/*.cpp", "backend/*.hpp", "backend/*.cu", "backend/*.cuh", "kernels/*.cu", "kernels/*.cuh", "kernels/*.hpp"]
     out = []
     for p in pats:
         out += glob.glob(os.path.join(CSRC, p))

@@ -479,11 +479,22 @@ void Session::launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_
     cfg.blockDim = r.block;
     cfg.dynamicSmemBytes = r.smem;
     cfg.stream = stream_;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (allow_pdl && r.pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
+    if (r.cluster.x) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = r.cluster.x;
+        attr[n_attr].val.clusterDim.y = r.cluster.y;
+        attr[n_attr].val.clusterDim.z = r.cluster.z;
+        n_attr++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = (allow_pdl && r.pdl) ? 1 : 0;
+    cfg.numAttrs = n_attr;
     void* args[1] = {param_bytes};
     OX_CUDA(cudaLaunchKernelExC(&cfg, r.func, args));
 }

@@ -344,6 +344,7 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
     const bool dyn = d.t_bucket > 0 && d.in_place && !bias;
     const long long Tsz = dyn ? d.t_bucket : T;
     Buf dyn_t = dyn ? em.dyn(T) : null;
+    if (dyn && S == 1 && emit_gqa_decode(em, d, q, k, v, seqlens, cos, sin, out, present_k, present_v, dyn_t, Tsz)) return;
     if (dyn) pp.P = pp.T = 0;
     pp.half = d.rot_half;
     pp.cache_rows = d.cache_rows;

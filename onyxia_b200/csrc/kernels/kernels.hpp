@@ -69,6 +69,7 @@ struct Reloc {
 struct LaunchRec {
     const void* func = nullptr;
     dim3 grid{1, 1, 1}, block{1, 1, 1};
+    dim3 cluster{0, 0, 0};  // thread-block cluster shape; x = 0 launches without clusters
     unsigned smem = 0;
     std::vector<uint8_t> params;
     std::vector<Reloc> relocs;
@@ -205,6 +206,14 @@ struct GqaDesc {
 void emit_gqa(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef& v, const TRef& past_k,
               const TRef& past_v, const TRef& seqlens, const TRef* cos, const TRef* sin, const TRef* bias,
               const TRef& out, const TRef& present_k, const TRef& present_v);
+
+// The decode step (S = 1) over an in-place cache as one launch of thread-block
+// clusters; false when the shape is outside what that kernel handles. `t_size`
+// bounds the present length the launch is sized for; the true length is read
+// from `dyn_t` at run time.
+bool emit_gqa_decode(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef& v, const TRef& seqlens,
+                     const TRef* cos, const TRef* sin, const TRef& out, const TRef& present_k, const TRef& present_v,
+                     Buf dyn_t, long long t_size);
 
 struct NBitsDesc {
     int64_t m, k, n, block_size, n_blocks;
