@@ -20,9 +20,10 @@
 //   4. V rows stream through the same ring; p = round(e / Σ) and Σ p·v in f64 per
 //      CTA; the partial outputs are added across the cluster in rank order by the
 //      CTA that owns a slice of the head dimension, rounded and stored.
-// Nothing spins on memory: CTAs meet at hardware cluster barriers, and waits on
-// copy completion are bounded (an expired wait sets the error word and the CTA
-// carries on to the barriers, so the cluster always drains).
+// Nothing spins on memory: CTAs meet at hardware cluster barriers; the generic
+// kernel's waits on bulk-copy completion are bounded (an expired wait sets the
+// error word and the CTA carries on to the barriers, so the cluster always
+// drains), and the f16 kernel waits only on its own asynchronous copies.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -357,6 +358,323 @@ template <int DT, int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1
     cluster.sync();  // nobody leaves while its shared memory may still be read
 }
 
+
+// ── f16 variant: the two contractions run on the tensor cores ────────────
+// Scores: per 16 keys, m16n8k16 MMAs with the K rows as A (keys × head dim) and
+// the rotated q rows as B (head dim × heads, up to 8 heads). P·V: the rounded
+// probabilities as A (heads × keys) and V rows as B (keys × 8 dims, read
+// transposed). Products of two f16 values are exact; sums are f32. K/V rows are
+// copied one row per bulk copy into rows padded by 16 bytes, so that the 8×8
+// matrix loads touch every bank once.
+constexpr int kRowPad = 8;  // f16 elements
+
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_decode_h(const GqaDecP p) {
+    constexpr int DT = DT_F16;
+    constexpr int D = 32 * DPL, RS = D + kRowPad;      // row stride in elements
+    constexpr int kBlockBytes = kKeyBlock * RS * 2;
+    constexpr int NW = kThreads / 32;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CX = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int kpad = (p.chunk_max + 15) & ~15;  // keys per CTA rounded up to whole MMA tiles
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* ring = smem;                                             // kRing blocks of kKeyBlock padded rows
+    __half* q_h = reinterpret_cast<__half*>(ring + kRing * kBlockBytes);    // [8][RS] rotated q, zero rows beyond the group
+    float* sc = reinterpret_cast<float*>(q_h + 8 * RS);                     // [GT][kpad] scores → exponentials
+    __half* p_h = reinterpret_cast<__half*>(sc + GT * kpad);                // [8][kpad + 8] probabilities (A operand of P·V)
+    float* part = reinterpret_cast<float*>(p_h + 8 * (kpad + 8));           // [GT][D] this CTA's partial output (read by the cluster)
+    double* red = reinterpret_cast<double*>(part + GT * D);                 // [GT][NW]
+    float* xmax = reinterpret_cast<float*>(red + GT * NW);                  // [8 ranks][GT] maxima, written by every CTA of the cluster
+    double* xsum = reinterpret_cast<double*>(xmax + 8 * GT);                // [8 ranks][GT] sums,   written by every CTA of the cluster
+    float* xpart = reinterpret_cast<float*>(xsum + 8 * GT);                 // [8 ranks][GT][slice] partial outputs of this CTA's slice
+
+    pdl_enter();
+
+    const long long b = blockIdx.z;
+    const long long kvh = blockIdx.y / p.groups, gc = blockIdx.y % p.groups;
+    const long long G = p.H / p.KV, h0 = kvh * G + gc * GT;
+    const int live = (int)(G - gc * GT < GT ? G - gc * GT : GT);
+    const long long T = *p.dyn_t;
+    const long long tot = (long long)p.seqlens[b] + 1, qpos = tot - 1 > 0 ? tot - 1 : 0;
+    const long long hi = qpos < T - 1 ? qpos : T - 1;
+    const long long lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;
+    const int n = (int)(hi >= lo ? hi - lo + 1 : 0);
+    const int chunk = (n + CX - 1) / CX;
+    const long long my_lo = lo + (long long)rank * chunk;
+    int my_n = n - rank * chunk;
+    my_n = my_n < 0 ? 0 : (my_n > chunk ? chunk : my_n);
+    if (my_n > p.chunk_max) {
+        if (tid == 0) report(p.err, ERR_SLICE_OOB, p.node, my_n, p.chunk_max);
+        my_n = p.chunk_max;
+    }
+    const int n_blocks = (my_n + kKeyBlock - 1) / kKeyBlock;
+    const long long head_base = (b * p.KV + kvh) * p.cap * D;
+    __half* ck = reinterpret_cast<__half*>(p.cache_k) + head_base;
+    __half* cv = reinterpret_cast<__half*>(p.cache_v) + head_base;
+    const bool owns_new = qpos <= T - 1 && n > 0 && (int)((hi - lo) / chunk) == rank;
+
+    long long rope_row = qpos;
+    if (p.half && rope_row >= p.cache_rows) {
+        if (tid == 0 && rank == 0) report(p.err, ERR_GATHER_OOB, p.node, rope_row, p.cache_rows);
+        rope_row = 0;
+    }
+    auto rope = [&](const void* x, long long base, int e) -> float {
+        if (e >= 2 * p.half) return ld<DT>(x, base + e);
+        const bool first = e < p.half;
+        const long long j = first ? e : e - p.half;
+        const float c = ld<DT>(p.cos, rope_row * p.half + j), s = ld<DT>(p.sin, rope_row * p.half + j);
+        const float x1 = ld<DT>(x, base + j), x2 = ld<DT>(x, base + j + p.half);
+        return first ? rndf<DT>(x1 * c) - rndf<DT>(x2 * s) : rndf<DT>(x2 * c) + rndf<DT>(x1 * s);
+    };
+
+    // Block i of 2·n_blocks (K blocks, then V blocks) → ring slot i % kRing, as 16-byte asynchronous
+    // copies into padded rows; every thread commits one group per block (empty beyond the last block).
+    // The newest key's row is not fetched: its owner writes it into the slot directly.
+    auto fetch = [&](int i) {
+        if (i < 2 * n_blocks) {
+            const bool is_v = i >= n_blocks;
+            const int blk = is_v ? i - n_blocks : i;
+            int rows = my_n - blk * kKeyBlock;
+            rows = rows > kKeyBlock ? kKeyBlock : rows;
+            const __half* src = (is_v ? cv : ck) + (my_lo + (long long)blk * kKeyBlock) * D;
+            const unsigned dst = sm_addr(ring + (i % kRing) * kBlockBytes);
+            const long long skip = owns_new ? qpos - (my_lo + (long long)blk * kKeyBlock) : -1;
+            for (int c = tid; c < rows * (D / 8); c += kThreads) {
+                const int r = c / (D / 8), col = c % (D / 8);
+                if (r == skip) continue;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (r * RS + col * 8) * 2), "l"(src + (long long)r * D + col * 8)
+                             : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int i = 0; i < kRing; i++) fetch(i);
+
+    // 1. rotated q for the heads of the group (zero rows up to 8), the new k / v rows, zeroed padding.
+    // Thread e owns element e of every row, so all its loads are independent and issued together.
+    float new_k = 0.f, new_v = 0.f;  // element tid of the new rows (D ≤ kThreads)
+    if (tid < D) {
+        const int e = tid;
+        const bool rot = e < 2 * p.half, first = e < p.half;
+        const int j = first ? e : e - (int)p.half, e2 = first ? e + (int)p.half : e - (int)p.half;  // partner element
+        float c = 1.f, s = 0.f;
+        if (rot) {
+            c = ld<DT>(p.cos, rope_row * p.half + j);
+            s = ld<DT>(p.sin, rope_row * p.half + j);
+        }
+        float x[GT + 1], y[GT + 1];  // rows: the group's q heads, then the new k
+        const long long kbase = (b * p.KV + kvh) * D;
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) {
+            const long long base = (b * p.H + h0 + (hh < live ? hh : 0)) * D;
+            x[hh] = ld<DT>(p.q, base + e);
+            y[hh] = rot ? ld<DT>(p.q, base + e2) : 0.f;
+        }
+        x[GT] = owns_new ? ld<DT>(p.k, kbase + e) : 0.f;
+        y[GT] = owns_new && rot ? ld<DT>(p.k, kbase + e2) : 0.f;
+        if (owns_new) new_v = ld<DT>(p.v, kbase + e);
+        // first half: x1·cos − x2·sin; second half: x2·cos + x1·sin, with x the own element and y the partner
+        auto turn = [&](float own, float partner) {
+            if (!rot) return own;
+            return first ? rndf<DT>(own * c) - rndf<DT>(partner * s) : rndf<DT>(own * c) + rndf<DT>(partner * s);
+        };
+#pragma unroll
+        for (int hh = 0; hh < 8; hh++) q_h[hh * RS + e] = __float2half_rn(hh < GT && hh < live ? turn(x[hh < GT ? hh : 0], y[hh < GT ? hh : 0]) : 0.f);
+        new_k = turn(x[GT], y[GT]);
+        if (owns_new && gc == 0) {
+            st<DT>(ck, qpos * D + e, new_k);
+            st<DT>(cv, qpos * D + e, new_v);
+            for (long long z = qpos + 1; z < T; z++) {  // a row shorter than the batch's longest
+                st<DT>(ck, z * D + e, 0.f);
+                st<DT>(cv, z * D + e, 0.f);
+            }
+        }
+    }
+    for (int i = tid; i < 8 * (kpad + 8); i += kThreads) p_h[i] = __float2half(0.f);
+    cluster.sync();  // also: every CTA of the cluster has started, so its shared memory may be written remotely
+
+    // 2. scores: q as the B operand (head dim × heads), kept in registers
+    unsigned qb[D / 16][2];
+#pragma unroll
+    for (int j = 0; j < D / 16; j++) {
+        qb[j][0] = *reinterpret_cast<const unsigned*>(q_h + g * RS + 16 * j + 2 * t);
+        qb[j][1] = *reinterpret_cast<const unsigned*>(q_h + g * RS + 16 * j + 2 * t + 8);
+    }
+    for (int blk = 0; blk < n_blocks; blk++) {
+        const int slot = blk % kRing;
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");  // this thread's copies of the oldest block landed
+        __half* rows = reinterpret_cast<__half*>(ring + slot * kBlockBytes);
+        const int first = blk * kKeyBlock;  // index within this CTA's keys
+        const long long first_pos = my_lo + first;
+        if (owns_new && qpos >= first_pos && qpos < first_pos + kKeyBlock && tid < D)
+            rows[(qpos - first_pos) * RS + tid] = __float2half_rn(new_k);
+        __syncthreads();
+        int here = my_n - first;
+        here = here > kKeyBlock ? kKeyBlock : here;
+        for (int kt = warp; kt * 16 < here; kt += NW) {  // 16 keys per MMA tile
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const int m = lane >> 3, r = lane & 7;
+            const unsigned a_addr = sm_addr(rows + (kt * 16 + (m & 1) * 8 + r) * RS + (m >> 1) * 8);
+#pragma unroll
+            for (int j = 0; j < D / 16; j++) {
+                unsigned a[4];
+                ldsm_x4(a, a_addr + j * 32);
+                mma_f16(c, a[0], a[1], a[2], a[3], qb[j][0], qb[j][1]);
+            }
+            // c0: (key g, head 2t)  c1: (key g, head 2t+1)  c2: (key g+8, head 2t)  c3: (key g+8, head 2t+1)
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int key = first + kt * 16 + g + (q >= 2 ? 8 : 0), head = 2 * t + (q & 1);
+                if (head < GT && key < my_n) sc[head * kpad + key] = rndf<DT>(rndf<DT>(c[q]) * p.scale);
+            }
+        }
+        __syncthreads();  // the block is consumed: its slot takes the next one
+        fetch(blk + kRing);
+    }
+
+    // 3. softmax statistics: every CTA stores its maxima (then its sums) into slot `rank` of every
+    // CTA's exchange area through distributed shared memory; after the cluster barrier each reads its own copy.
+    for (int hh = warp; hh < GT; hh += NW) {
+        float m = -INFINITY;
+        for (int i = lane; i < my_n; i += 32) m = fmaxf(m, sc[hh * kpad + i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane < CX) cluster.map_shared_rank(xmax, lane)[rank * GT + hh] = m;
+    }
+    cluster.sync();
+    float gmax[GT];
+#pragma unroll
+    for (int hh = 0; hh < GT; hh++) {
+        float m = -INFINITY;
+        for (int r = 0; r < CX; r++) m = fmaxf(m, xmax[r * GT + hh]);
+        gmax[hh] = m;
+    }
+    {
+        double local[GT];
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) local[hh] = 0.0;
+        for (int i = tid; i < my_n; i += kThreads) {
+#pragma unroll
+            for (int hh = 0; hh < GT; hh++) {
+                const float e = rndd<DT>(exp((double)rndd<DT>((double)sc[hh * kpad + i] - (double)gmax[hh])));
+                sc[hh * kpad + i] = e;
+                local[hh] += (double)e;
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) {
+            double v = local[hh];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) red[hh * NW + warp] = v;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            for (int hh = 0; hh < GT; hh++) {
+                double v = 0.0;
+                for (int w = 0; w < NW; w++) v += red[hh * NW + w];
+                if (lane < CX) cluster.map_shared_rank(xsum, lane)[rank * GT + hh] = v;
+            }
+        }
+    }
+    cluster.sync();
+    float total[GT];
+#pragma unroll
+    for (int hh = 0; hh < GT; hh++) {
+        double v = 0.0;
+        for (int r = 0; r < CX; r++) v += xsum[r * GT + hh];
+        total[hh] = rndd<DT>(v);
+    }
+    for (int i = tid; i < my_n; i += kThreads)
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) p_h[hh * (kpad + 8) + i] = __double2half((double)sc[hh * kpad + i] / (double)total[hh]);
+    __syncthreads();
+
+    // 4. P·V: warp w owns dims [w·D/NW, (w+1)·D/NW) in n-tiles of 8; A = probabilities (heads × keys)
+    constexpr int NT = D / 8 / NW;  // n-tiles per warp
+    float o[NT > 0 ? NT : 1][4];
+#pragma unroll
+    for (int i = 0; i < (NT > 0 ? NT : 1); i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int blk = 0; blk < n_blocks; blk++) {
+        const int i = n_blocks + blk, slot = i % kRing;
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
+        __half* rows = reinterpret_cast<__half*>(ring + slot * kBlockBytes);
+        const int first = blk * kKeyBlock;
+        const long long first_pos = my_lo + first;
+        int here = my_n - first;
+        here = here > kKeyBlock ? kKeyBlock : here;
+        if (owns_new && qpos >= first_pos && qpos < first_pos + kKeyBlock && tid < D)
+            rows[(qpos - first_pos) * RS + tid] = __float2half_rn(new_v);
+        // rows beyond the last key of a partly filled tile hold stale bytes: clear them (their p is 0, but 0·NaN is NaN)
+        for (int z = here * D + tid; z < ((here + 15) & ~15) * D; z += kThreads) rows[(z / D) * RS + z % D] = __float2half(0.f);
+        __syncthreads();
+        if (NT > 0) {
+            for (int kt = 0; kt * 16 < here; kt++) {
+                const unsigned a0 = *reinterpret_cast<const unsigned*>(p_h + g * (kpad + 8) + first + kt * 16 + 2 * t);
+                const unsigned a2 = *reinterpret_cast<const unsigned*>(p_h + g * (kpad + 8) + first + kt * 16 + 2 * t + 8);
+                const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt += 2) {
+                    // matrices: (keys 0-7, dims n0..), (keys 8-15, dims n0..), (keys 0-7, dims n0+8..), (keys 8-15, dims n0+8..)
+                    const int n0 = (warp * NT + nt) * 8;
+                    unsigned bm[4];
+                    ldsm_x4_t(bm, sm_addr(rows + (kt * 16 + (m & 1) * 8 + r) * RS + n0 + (m >> 1) * 8));
+                    mma_f16(o[nt], a0, 0u, a2, 0u, bm[0], bm[1]);
+                    if (nt + 1 < NT) mma_f16(o[nt + 1], a0, 0u, a2, 0u, bm[2], bm[3]);
+                }
+            }
+        }
+        __syncthreads();
+        fetch(i + kRing);
+    }
+    // c0: (head g, dim n0 + 2t)  c1: (head g, dim n0 + 2t + 1); rows 8-15 of the tile are padding.
+    // Dim c belongs to the CTA c / slice, which adds the CX partial values in rank order.
+    const int slice = (D + CX - 1) / CX;
+    if (NT > 0 && g < GT)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const int c = (warp * NT + nt) * 8 + 2 * t + q, owner = c / slice;
+                cluster.map_shared_rank(xpart, owner)[(rank * GT + g) * slice + c - owner * slice] = o[nt][q];
+            }
+    cluster.sync();
+    for (int i = tid; i < GT * slice; i += kThreads) {
+        const int hh = i / slice, c = rank * slice + i % slice;
+        if (hh >= live || c >= D) continue;
+        float v = 0.f;
+        for (int r = 0; r < CX; r++) v += xpart[(r * GT + hh) * slice + i % slice];
+        st<DT>(p.out, (b * p.H + h0 + hh) * D + c, v);
+    }
+}
+
+template <int DPL, int GT> size_t decode_h_smem(int chunk_max) {
+    constexpr int D = 32 * DPL, RS = D + kRowPad;
+    const int kpad = (chunk_max + 15) & ~15;
+    return (size_t)kRing * kKeyBlock * RS * 2 + (size_t)8 * RS * 2 + (size_t)GT * kpad * 4 + (size_t)8 * (kpad + 8) * 2 +
+           (size_t)GT * D * 4 + (size_t)GT * (kThreads / 32) * 8 + (size_t)8 * GT * 4 + (size_t)8 * GT * 8 +
+           (size_t)8 * GT * D * 4 + 128;
+}
+
 }  // namespace
 
 namespace {
@@ -370,9 +688,13 @@ template <int DT, int DPL, int GT> size_t decode_smem(int chunk_max) {
 
 template <int DT, int DPL, int GT>
 bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf (&bufs)[11]) {
-    const size_t smem = decode_smem<DT, DPL, GT>(p0.chunk_max);
+    size_t smem = decode_smem<DT, DPL, GT>(p0.chunk_max);
+    void (*fn)(const GqaDecP) = gqa_decode<DT, DPL, GT>;
+    if constexpr (DT == DT_F16 && DPL >= 2) {  // D ≥ 64: whole n-tiles per warp
+        smem = decode_h_smem<DPL, GT>(p0.chunk_max);
+        fn = gqa_decode_h<DPL, GT>;
+    }
     if (smem > 200 * 1024) return false;
-    auto fn = gqa_decode<DT, DPL, GT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
