@@ -115,6 +115,12 @@ void Session::collect_node_syms() {
         of_node(i, s);
         if (info_[i].fuse_with >= 0) of_node((size_t)info_[i].fuse_with, s);
         if (info_[i].absorbed_by >= 0) of_node((size_t)info_[i].absorbed_by, s);
+        if (group_of_leader_[i] >= 0) {
+            const GemvGroup& g = groups_[group_of_leader_[i]];
+            for (auto mem : g.members) of_node(mem, s);
+            for (int extra : {g.gelu_node, g.mul_node, g.norm2, g.add, g.norm1})
+                if (extra >= 0) of_node((size_t)extra, s);
+        }
         std::sort(s.begin(), s.end());
         s.erase(std::unique(s.begin(), s.end()), s.end());
         info_[i].syms = std::move(s);
@@ -245,7 +251,9 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
             std::vector<TRef> ins, outs;
             for (auto v : node.inputs) ins.push_back(plan.trefs[v]);
             for (auto v : node.outputs) outs.push_back(plan.trefs[v]);
-            if (node.is_prim && node.prim.kind == PrimKind::Reshape) {
+            if (group_of_leader_[nid] >= 0) {
+                lower_group(em, groups_[group_of_leader_[nid]], plan);
+            } else if (node.is_prim && node.prim.kind == PrimKind::Reshape) {
                 // a view: nothing to launch
             } else if (info_[nid].fuse_kind == FUSE_GEGLU) {
                 const Node& g = m.nodes[info_[nid].fuse_with];
@@ -282,6 +290,42 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
         for (auto v : deaths_[step])
             if (plan.loc[v].kind == ValueLoc::Arena) arena->release(plan.loc[v].offset, plan.arena_size[v]);
     return true;
+}
+
+// One launch for a group of MatMulNBits nodes with its prologue and epilogue.
+void Session::lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan) {
+    const Module& m = module_;
+    oxk::NBitsGroup gr{};
+    gr.k = g.k;
+    gr.has_zp = g.has_zp;
+    gr.m = plan.trefs[g.src].numel() / g.k;
+    gr.n_seg = (int)g.members.size();
+    for (size_t i = 0; i < g.members.size(); i++) {
+        const Node& n = m.nodes[g.members[i]];
+        gr.seg_n[i] = n.composite.attrs.int_("N");
+        gr.y[i] = plan.trefs[n.outputs[0]];
+    }
+    gr.geglu = g.geglu;
+    if (g.geglu) gr.y[0] = plan.trefs[m.nodes[g.mul_node].outputs[0]];
+    TRef w1, w2, res, sum;
+    if (g.norm1 >= 0) {
+        w1 = plan.trefs[m.nodes[g.norm1].inputs[1]];
+        gr.w1 = &w1;
+        gr.eps1 = m.nodes[g.norm1].composite.attrs.float_or("epsilon", 1e-5);
+    }
+    if (g.add >= 0) {
+        res = plan.trefs[g.res];
+        sum = plan.trefs[m.nodes[g.add].outputs[0]];
+        gr.res = &res;
+        gr.sum_out = &sum;
+    }
+    if (g.norm2 >= 0) {
+        w2 = plan.trefs[m.nodes[g.norm2].inputs[1]];
+        gr.w2 = &w2;
+        gr.eps2 = m.nodes[g.norm2].composite.attrs.float_or("epsilon", 1e-5);
+    }
+    // the group's tile stream lives in the slot of the first member's weight constant
+    oxk::emit_nbits_group(em, gr, plan.trefs[g.src], plan.trefs[m.nodes[g.members[0]].inputs[1]]);
 }
 
 void Session::finish_outputs(Plan& plan) {

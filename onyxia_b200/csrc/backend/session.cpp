@@ -206,6 +206,7 @@ void Session::analyse() {
         output_names_.push_back(o.first);
     }
 
+    find_gemv_groups();
     if (!opt_.disable_pattern_fusion && !opt_.without_fused) find_pattern_fusions();
     collect_node_syms();
 
@@ -261,6 +262,161 @@ void Session::analyse() {
         for (size_t n = 0; n < nn; n++)
             if (gqa_past_input_[0][n] == (int)i || gqa_past_input_[1][n] == (int)i) kv_only = true;
         input_needs_dense_[i] = kv_only && is_kv_slot[v] ? 0 : 1;
+    }
+}
+
+// Groups MatMulNBits nodes that read the same f16 activations (and whose
+// constant weights nobody else reads) into single launches, and attaches to a
+// group the norm/add/norm chain that feeds it and the Gelu·Mul pair it feeds
+// when these touch nothing else. The arithmetic and its rounding points are the
+// ones of the separate kernels.
+void Session::find_gemv_groups() {
+    const Module& m = module_;
+    const size_t nn = m.nodes.size(), nv = m.values.size();
+    groups_.clear();
+    group_of_leader_.assign(nn, -1);
+    if (opt_.without_fused || opt_.disable_pattern_fusion) return;
+    if (const char* e = std::getenv("ONYXIA_DISABLE_GEMV_GROUPS"))  // diagnostics
+        if (std::atoi(e) != 0) return;
+    const char* layout_env = std::getenv("ONYXIA_GEMV_LAYOUT");
+    if (layout_env && std::string(layout_env) == "interleaved") return;
+
+    std::vector<int> uses(nv, 0);
+    std::vector<std::vector<int>> readers(nv);
+    for (size_t i = 0; i < nn; i++)
+        for (auto v : m.nodes[i].inputs) {
+            uses[v]++;
+            readers[v].push_back((int)i);
+        }
+    std::vector<int> out_uses(nv, 0);
+    for (auto& o : m.outputs) out_uses[o.second]++;
+
+    auto is_norm = [&](int i) {
+        const Node& n = m.nodes[i];
+        return !n.is_prim && n.composite.name == "SimplifiedLayerNormalization" && info_[i].fused && info_[i].absorbed_by < 0 &&
+               info_[i].fuse_with < 0 && m.values[n.inputs[0]].ty.dtype == DType::F16 && m.values[n.inputs[1]].ty.dtype == DType::F16 &&
+               m.values[n.outputs[0]].ty == m.values[n.inputs[0]].ty && m.values[n.inputs[1]].origin.kind == Origin::Const;
+    };
+    auto producer = [&](ValueId v) { return m.values[v].origin.kind == Origin::Node ? (int)m.values[v].origin.id : -1; };
+
+    // eligible members, keyed by the activations they read
+    auto eligible = [&](size_t i) {
+        const Node& n = m.nodes[i];
+        if (n.is_prim || n.composite.name != "com.microsoft.MatMulNBits" || !info_[i].fused || info_[i].absorbed_by >= 0) return false;
+        if (m.values[n.inputs[0]].ty.dtype != DType::F16 || m.values[n.inputs[2]].ty.dtype != DType::F16) return false;
+        if (m.values[n.outputs[0]].ty.dtype != DType::F16) return false;
+        for (size_t j = 1; j < n.inputs.size(); j++) {
+            ValueId c = n.inputs[j];
+            if (m.values[c].origin.kind != Origin::Const || uses[c] != 1 || out_uses[c]) return false;
+            // constants sharing one pool entry would share one device buffer
+            for (ValueId u = 0; u < nv; u++)
+                if (u != c && m.values[u].origin.kind == Origin::Const && m.values[u].origin.id == m.values[c].origin.id) return false;
+        }
+        auto wd = shape_as_static(m.values[n.inputs[1]].ty.shape);
+        return wd && wd->size() == 3;
+    };
+    std::vector<char> taken(nn, 0);
+    for (size_t s = 0; s < order_.size(); s++) {
+        const size_t i = order_[s];
+        if (taken[i] || !eligible(i)) continue;
+        const Node& n0 = m.nodes[i];
+        GemvGroup g;
+        g.k = n0.composite.attrs.int_("K");
+        g.has_zp = n0.inputs.size() > 3;
+        g.members.push_back((ox::NodeId)i);
+        const ValueId a = n0.inputs[0];
+        for (size_t s2 = s + 1; s2 < order_.size() && g.members.size() < 3; s2++) {
+            const size_t j = order_[s2];
+            if (taken[j] || !eligible(j)) continue;
+            const Node& nj = m.nodes[j];
+            if (nj.inputs[0] != a || nj.composite.attrs.int_("K") != g.k || (nj.inputs.size() > 3) != g.has_zp) continue;
+            g.members.push_back((ox::NodeId)j);
+        }
+        // every reader of a member's output must run after the launch
+        auto readers_after = [&](int leader) {
+            for (auto mem : g.members)
+                for (int r : readers[m.nodes[mem].outputs[0]])
+                    if (r != leader && step_of_node_[r] <= step_of_node_[leader]) return false;
+            return true;
+        };
+        g.leader = (int)g.members.back();
+        // Gelu(member 0) · member 1 with nothing else reading either
+        if (g.members.size() == 2) {
+            const ValueId o0 = m.nodes[g.members[0]].outputs[0], o1 = m.nodes[g.members[1]].outputs[0];
+            if (uses[o0] == 1 && uses[o1] == 1 && !out_uses[o0] && !out_uses[o1] && m.values[o0].ty == m.values[o1].ty) {
+                const int gi = readers[o0][0], mi = readers[o1][0];
+                const Node &gn = m.nodes[gi], &mn = m.nodes[mi];
+                if (!gn.is_prim && gn.composite.name == "Gelu" && info_[gi].fused && info_[gi].absorbed_by < 0 && mn.is_prim &&
+                    mn.prim.kind == PrimKind::Binary && (BinaryOp)mn.prim.op == BinaryOp::Mul && info_[mi].absorbed_by < 0 &&
+                    info_[mi].fuse_with < 0 && mn.inputs[0] == gn.outputs[0] && mn.inputs[1] == o1 &&
+                    uses[gn.outputs[0]] == 1 && !out_uses[gn.outputs[0]] && m.values[mn.outputs[0]].ty == m.values[o0].ty &&
+                    alias_root_[mn.outputs[0]] == mn.outputs[0]) {
+                    g.geglu = gn.composite.attrs.str_or("approximate", "none") == "tanh" ? 1 : 2;
+                    g.gelu_node = gi;
+                    g.mul_node = mi;
+                    g.leader = mi;
+                }
+            }
+        }
+        while (!g.geglu && !readers_after(g.leader) && g.members.size() > 1) {
+            g.members.pop_back();  // fall back to a smaller group
+            g.leader = (int)g.members.back();
+        }
+        // the chain that produces the activations
+        g.src = a;
+        const int pn = producer(a);
+        if (pn >= 0 && is_norm(pn) && uses[a] == (int)g.members.size() && !out_uses[a] && alias_root_[a] == a) {
+            const Node& n2 = m.nodes[pn];
+            bool ok = true;
+            GemvGroup c = g;
+            c.norm2 = pn;
+            c.src = n2.inputs[0];
+            const int an = producer(n2.inputs[0]);
+            if (an >= 0 && m.nodes[an].is_prim && m.nodes[an].prim.kind == PrimKind::Binary &&
+                (BinaryOp)m.nodes[an].prim.op == BinaryOp::Add && info_[an].absorbed_by < 0 && info_[an].fuse_with < 0 &&
+                alias_root_[n2.inputs[0]] == n2.inputs[0]) {
+                const Node& ad = m.nodes[an];
+                const TensorType& ts = m.values[ad.outputs[0]].ty;
+                if (m.values[ad.inputs[0]].ty == ts && m.values[ad.inputs[1]].ty == ts && ts.dtype == DType::F16) {
+                    // every other reader of the sum must run after the launch
+                    for (int r : readers[ad.outputs[0]])
+                        if (r != pn && step_of_node_[r] <= step_of_node_[g.leader]) ok = false;
+                    if (ok) {
+                        c.add = an;
+                        int which = -1;  // the operand that is itself a norm nothing else reads
+                        for (int side = 1; side >= 0 && which < 0; side--) {
+                            const ValueId ov = ad.inputs[side];
+                            const int p1 = producer(ov);
+                            if (p1 >= 0 && is_norm(p1) && uses[ov] == 1 && !out_uses[ov] && alias_root_[ov] == ov) which = side;
+                        }
+                        if (which >= 0) {
+                            c.norm1 = producer(ad.inputs[which]);
+                            c.src = m.nodes[c.norm1].inputs[0];
+                            c.res = ad.inputs[1 - which];
+                        } else {
+                            c.src = ad.inputs[1];
+                            c.res = ad.inputs[0];
+                        }
+                    }
+                }
+            }
+            if (ok) g = c;
+        }
+        // record
+        const int gid = (int)groups_.size();
+        auto absorb = [&](int node) {
+            if (node >= 0 && node != g.leader) info_[node].absorbed_by = g.leader;
+        };
+        for (auto mem : g.members) {
+            taken[mem] = 1;
+            absorb((int)mem);
+        }
+        absorb(g.gelu_node);
+        absorb(g.norm2);
+        absorb(g.add);
+        absorb(g.norm1);
+        group_of_leader_[g.leader] = gid;
+        groups_.push_back(std::move(g));
     }
 }
 
@@ -385,8 +541,40 @@ void Session::interleave_weights() {
         w_scales[w] = w_scales[w] == -1 || w_scales[w] == sc ? sc : -2;
         w_zp[w] = w_zp[w] == -1 || w_zp[w] == zp ? zp : -2;
     }
+    // groups first: one tile stream per group, kept in the slot of the first member's weight
+    for (auto& g : groups_) {
+        const long long nb = (g.k + 31) / 32;
+        std::vector<long long> rts;
+        long long total_rt = 0;
+        for (auto mem : g.members) {
+            rts.push_back((m.nodes[mem].composite.attrs.int_("N") + 15) / 16);
+            total_rt += rts.back();
+        }
+        const size_t tile_bytes = oxk::nbits_tiled_bytes(16, nb, g.has_zp);  // bytes of one row tile (all its k tiles)
+        BufferRef dst = pool_->alloc(std::max<size_t>((size_t)total_rt * tile_bytes, 16));
+        long long rt_add = 0;
+        for (size_t i = 0; i < g.members.size(); i++) {
+            const Node& n = m.nodes[g.members[i]];
+            oxk::Emitter em;
+            // GeGLU: row tiles of gate and up alternate; otherwise one matrix after the other
+            oxk::emit_nbits_pack_tiles(em, oxk::Buf{0, 0}, oxk::Buf{1, 0}, oxk::Buf{2, 0}, oxk::Buf{3, 0},
+                                       n.composite.attrs.int_("N"), nb, g.has_zp, g.geglu ? 2 : 1, g.geglu ? (long long)i : rt_add);
+            launch_now(em, {consts_[n.inputs[1]].ptr(), consts_[n.inputs[2]].ptr(), g.has_zp ? consts_[n.inputs[3]].ptr() : nullptr,
+                            dst->ptr});
+            rt_add += rts[i];
+        }
+        OX_CUDA(cudaStreamSynchronize(stream_));
+        for (size_t i = 0; i < g.members.size(); i++) {
+            const Node& n = m.nodes[g.members[i]];
+            interleaved_[n.inputs[1]] = 3;  // part of a group's stream; not usable on its own
+            consts_[n.inputs[1]].buf = i == 0 ? dst : BufferRef();
+            consts_[n.inputs[2]].buf = BufferRef();  // the scales (and zero points) live inside the tile records
+            if (g.has_zp) consts_[n.inputs[3]].buf = BufferRef();
+        }
+    }
     std::unordered_map<void*, char> done;
     for (ValueId v = 0; v < m.values.size(); v++) {
+        if (interleaved_[v] == 3) continue;
         if (!eligible[v] || eligible[v] != total[v] || !consts_[v].buf) continue;
         // constants sharing one pool entry share one device buffer
         bool shared = false;

@@ -110,6 +110,27 @@ private:
     };
     enum { FUSE_NONE = 0, FUSE_GEGLU = 1, FUSE_ADD_NORM = 2 };
 
+    // MatMulNBits nodes that read the same activations run as one launch of the
+    // streaming kernel over one tile stream. The launch may also cover the RMS
+    // norm / residual add / RMS norm chain that produces the activations (as the
+    // kernel's prologue) and a Gelu·Mul pair that consumes two members (as its
+    // epilogue). All covered nodes are absorbed by the leader, the node at whose
+    // step the launch is issued.
+    struct GemvGroup {
+        std::vector<ox::NodeId> members;  // in stream order
+        int leader = -1;
+        int geglu = 0;                    // 0 none, 1 tanh form, 2 erf form
+        int gelu_node = -1, mul_node = -1;
+        int norm2 = -1, add = -1, norm1 = -1;  // prologue chain, −1 = absent
+        ValueId src = 0, res = 0;         // what the prologue reads (src = the members' input without a prologue)
+        bool has_zp = false;
+        int64_t k = 0;
+    };
+    std::vector<GemvGroup> groups_;
+    std::vector<int> group_of_leader_;    // per node: index into groups_ or −1
+    void find_gemv_groups();
+    void lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan);
+
     void upload_constants();
     void interleave_weights();
     void launch_now(const oxk::Emitter& em, const std::vector<void*>& slots);

@@ -242,8 +242,34 @@ void emit_nbits_interleave(Emitter&, Buf src, Buf dst, long long bytes);
 void emit_matmul_nbits_stream(Emitter&, const NBitsDesc&, const TRef& a, const TRef& tiles, const TRef& y);
 // One-time gathering of a packed u4 weight [N, n_blocks, 32], its f16 scales
 // and optional u4 zero points into tile records; `dst` needs nbits_tiled_bytes.
+// Row tile rt of the matrix becomes row tile rt·rt_mul + rt_add of the
+// destination stream, so several matrices can share one stream (one after the
+// other, or interleaved row tile by row tile).
 size_t nbits_tiled_bytes(long long n, long long n_blocks, bool has_zp);
-void emit_nbits_pack_tiles(Emitter&, Buf w, Buf scales, Buf zp, Buf dst, long long n, long long n_blocks, bool has_zp);
+void emit_nbits_pack_tiles(Emitter&, Buf w, Buf scales, Buf zp, Buf dst, long long n, long long n_blocks, bool has_zp,
+                           long long rt_mul = 1, long long rt_add = 0);
+
+// Several MatMulNBits over the same activations as one launch of the streaming
+// kernel, optionally with a prologue on the activations and a GeGLU epilogue:
+//   v = a;  [v = rmsnorm(v, eps1)·w1;]  [v = res + v, also stored to sum_out;]  [v = rmsnorm(v, eps2)·w2;]
+//   plain:  y[i] = v · W_iᵀ for each segment i (the stream holds W_0's row tiles, then W_1's, …)
+//   geglu:  y[0] = gelu(v · W_0ᵀ) · (v · W_1ᵀ), the stream alternating row tiles of W_0 and W_1
+// Every step rounds where the primitives of the corresponding decompositions store a tensor.
+struct NBitsGroup {
+    long long m, k;
+    bool has_zp;
+    int n_seg;            // 1..3
+    long long seg_n[3];
+    TRef y[3];
+    int geglu;            // 0 none, 1 tanh form, 2 erf form
+    const TRef* w1;
+    double eps1;
+    const TRef* res;
+    const TRef* sum_out;
+    const TRef* w2;
+    double eps2;
+};
+void emit_nbits_group(Emitter&, const NBitsGroup&, const TRef& a, const TRef& tiles);
 
 // argmax over the last axis, highest index among equal maxima → i64.
 // `part` is scratch of argmax_scratch_bytes(rows) bytes, `counters` the zeroed arrival counters.

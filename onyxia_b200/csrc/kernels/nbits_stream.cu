@@ -56,6 +56,7 @@ struct PackP {
     const unsigned char* zp;     // packed nibbles over [N][nb], or null
     unsigned char* dst;
     long long n, nb, row_tiles, k_tiles;
+    long long rt_mul, rt_add;    // row tile rt of this matrix is row tile rt·rt_mul + rt_add of the destination stream
     int tile_bytes;
 };
 
@@ -74,7 +75,7 @@ __global__ void nbits_pack_tiles(const PackP p) {
         const long long tile = u >> 6;
         const long long rt = tile / p.k_tiles, kt = tile % p.k_tiles;
         const long long row = rt * 16 + (slot >> 5) * 8 + ((slot >> 2) & 7), kb = kt * 4 + (slot & 3);
-        unsigned char* rec = p.dst + tile * p.tile_bytes;
+        unsigned char* rec = p.dst + ((rt * p.rt_mul + p.rt_add) * p.k_tiles + kt) * p.tile_bytes;
         uint4 q = make_uint4(0, 0, 0, 0);
         __half s = __float2half(0.f);
         unsigned char z = 8;
@@ -162,23 +163,58 @@ __device__ __forceinline__ void widen_word(unsigned w, __half2 sub_lo, __half2 a
 }  // namespace
 
 struct StreamP {
-    const __half* a;
-    const unsigned char* tiles;
-    __half* y;
+    const __half* a;            // activations [M, K] (before the prologue)
+    const unsigned char* tiles; // tile records of all segments, row tile by row tile
     ErrWord* err;
-    long long m0, m_total, k, n;
-    int k_tiles, row_tiles, rts_per_cta, act_bytes, node;
+    __half* y[3];               // one output [M, seg_n] per segment (GeGLU: only y[0], [M, seg_n[0]])
+    // Prologue on the activations, each step optional:
+    //   v = a;  v = rmsnorm(v)·w1;  v = res + v (also stored to sum_out);  v = rmsnorm(v)·w2
+    const __half* w1;
+    const __half* res;
+    __half* sum_out;
+    const __half* w2;
+    float eps1, eps2;           // rounded to f16
+    float c_half, c_one, c_coef, c_k, c_inv_sqrt2;  // Gelu constants rounded to f16
+    long long m0, m_total, k;
+    long long seg_n[3];
+    int seg_rt0[4];             // first row tile of each segment, then the total
+    int n_seg;
+    int geglu;                  // 0: plain outputs; 1 / 2: out = gelu_tanh / gelu_erf(segment 0)·segment 1, row tiles interleaved
+    int k_tiles, row_tiles, rts_per_cta, act_bytes, aux_bytes, node;
 };
 
-// Result fragment of one row tile → y. c0:(row g, col 2t) c1:(row g, col 2t+1)
-// c2:(row g+8, col 2t) c3:(row g+8, col 2t+1); col = activation row.
-template <int MR> __device__ __forceinline__ void stream_store(const StreamP& p, const double (&acc)[4], long long rt, int lane) {
+// Result fragment of one row tile → the CTA's staging area [row tile][16 rows][MR], rounded to f16.
+// c0:(row g, col 2t) c1:(row g, col 2t+1) c2:(row g+8, col 2t) c3:(row g+8, col 2t+1); col = activation row.
+template <int MR> __device__ __forceinline__ void stream_stage(float* ystage, const double (&acc)[4], int rt_local, int lane) {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int q = 0; q < 4; q++) {
-        const long long row = rt * 16 + g + (q >= 2 ? 8 : 0), col = p.m0 + 2 * t + (q & 1);
-        if (row < p.n && col < p.m_total && 2 * t + (q & 1) < MR) p.y[col * p.n + row] = __double2half(acc[q]);
+        const int row = g + (q >= 2 ? 8 : 0), col = 2 * t + (q & 1);
+        if (col < MR) ystage[(rt_local * 16 + row) * MR + col] = __half2float(__double2half(acc[q]));
     }
+}
+
+__device__ __forceinline__ float r16(float v) { return __half2float(__float2half_rn(v)); }
+__device__ __forceinline__ float r16d(double v) { return __half2float(__double2half(v)); }
+
+// gelu(gate)·up with the rounding points of the Gelu decomposition followed by Mul
+// (crates/onyxia-ir/src/decomp.rs:185-213); the caller rounds the product when it stores it.
+__device__ __forceinline__ float geglu_value(const StreamP& p, float x, float up) {
+    float inner;
+    if (p.geglu == 1) {
+        const float x2 = r16(x * x), x3 = r16(x2 * x), cx3 = r16(p.c_coef * x3), s = r16(x + cx3), sc = r16(p.c_k * s);
+        inner = r16d(tanh((double)sc));
+    } else {
+        // erf by Abramowitz–Stegun 7.1.26, as the interpreter evaluates it (interp.rs:860-872)
+        double z = (double)r16(x * p.c_inv_sqrt2);
+        const double sign = z < 0.0 ? -1.0 : 1.0;
+        z = fabs(z);
+        const double tt = 1.0 / (1.0 + 0.3275911 * z);
+        const double e = 1.0 - (((((1.061405429 * tt - 1.453152027) * tt) + 1.421413741) * tt - 0.284496736) * tt + 0.254829592) * tt * exp(-z * z);
+        inner = r16d(sign * e);
+    }
+    const float one_plus = r16(p.c_one + inner), hx = r16(p.c_half * x);
+    return r16(hx * one_plus) * up;
 }
 
 template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2) nbits_stream(const StreamP p) {
@@ -187,11 +223,14 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
     extern __shared__ __align__(128) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    unsigned char* ring = smem + p.act_bytes + warp * (kStages * kStageBytes);
-    const unsigned bars = smem_addr(smem + p.act_bytes + kWarps * kStages * kStageBytes) + warp * kStages * 8;
+    // activations | aux: scratch of the prologue, later the output staging | rings | barriers | pieces
+    float* aux = reinterpret_cast<float*>(smem + p.act_bytes);
+    unsigned char* ring_base = smem + p.act_bytes + p.aux_bytes;
+    unsigned char* ring = ring_base + warp * (kStages * kStageBytes);
+    const unsigned bars = smem_addr(ring_base + kWarps * kStages * kStageBytes) + warp * kStages * 8;
 
     // pieces of row tiles shared between warps of this CTA: [warp][first / last piece][128]
-    double* pieces = reinterpret_cast<double*>(smem + p.act_bytes + kWarps * kStages * kStageBytes + kWarps * kStages * 8);
+    double* pieces = reinterpret_cast<double*>(ring_base + kWarps * kStages * kStageBytes + kWarps * kStages * 8);
 
     // This CTA owns `cta_rts` consecutive row tiles = cta_tiles consecutive tile
     // records, cut into equal ranges for its warps.
@@ -225,8 +264,8 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
     pdl_wait();
 
     // Activations → shared memory in B-fragment order: chunk (kt·4 + m)·4·MR + g·4 + t
-    // holds a[m0 + g][kt·128 + t·32 + m·8 … + 8], zero beyond the matrix.
-    {
+    // holds v[m0 + g][kt·128 + t·32 + m·8 … + 8], zero beyond the matrix.
+    if (!p.w1 && !p.res && !p.w2) {
         uint4* as = reinterpret_cast<uint4*>(smem);
         const int chunks = p.k_tiles * 16 * MR;
         const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.a) & 15) == 0;
@@ -235,20 +274,122 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
             const long long row = p.m0 + cg, k0 = (long long)ckt * 128 + ct * 32 + cm * 8;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (row < p.m_total) {
-                const __half* s = p.a + row * p.k + k0;
+                const __half* src_a = p.a + row * p.k + k0;
                 if (vec && k0 + 8 <= p.k) {
-                    v = *reinterpret_cast<const uint4*>(s);
+                    v = *reinterpret_cast<const uint4*>(src_a);
                 } else {
                     __half tmp[8];
 #pragma unroll
-                    for (int e = 0; e < 8; e++) tmp[e] = k0 + e < p.k ? s[e] : __float2half(0.f);
+                    for (int e = 0; e < 8; e++) tmp[e] = k0 + e < p.k ? src_a[e] : __float2half(0.f);
                     v = *reinterpret_cast<uint4*>(tmp);
                 }
             }
             as[c] = v;
         }
+        __syncthreads();
+    } else {
+        // The prologue: RMS norm, residual add, RMS norm — the primitive sequence and rounding
+        // points of SimplifiedLayerNormalization (decomp.rs:241-257) and Add. Every CTA does it
+        // for the MR rows of this pass; CTA 0 also stores the residual sum.
+        __half* ah = reinterpret_cast<__half*>(smem);
+        float* v = aux;                                                // [MR][K]
+        double* red = reinterpret_cast<double*>(aux + (((size_t)MR * p.k + 1) & ~(size_t)1));  // [MR][kWarps], then [MR] totals
+        const int K = (int)p.k;
+        auto block_sums = [&](double (&part)[MR]) {  // per-row sums over the CTA, result in red[MR·kWarps + m]
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                double x = part[m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+                if (lane == 0) red[m * kWarps + warp] = x;
+            }
+            __syncthreads();
+            if (threadIdx.x < MR) {
+                double tot = 0.0;
+                for (int w = 0; w < kWarps; w++) tot += red[threadIdx.x * kWarps + w];
+                red[MR * kWarps + threadIdx.x] = tot;
+            }
+            __syncthreads();
+        };
+        auto inv_rms = [&](int m, float eps) {
+            const float ms = r16d(red[MR * kWarps + m] / (double)K), denom = r16(ms + eps);
+            return r16d(1.0 / sqrt((double)denom));
+        };
+        double part[MR];
+#pragma unroll
+        for (int m = 0; m < MR; m++) part[m] = 0.0;
+        // pass A: fetch (with the residual already added when there is no first norm)
+        for (int i = threadIdx.x; i < MR * K; i += blockDim.x) {
+            const int m = i / K, kk = i - m * K;
+            float x = 0.f;
+            if (p.m0 + m < p.m_total) {
+                x = __half2float(p.a[(p.m0 + m) * p.k + kk]);
+                if (!p.w1 && p.res) {
+                    x = r16(x + __half2float(p.res[(p.m0 + m) * p.k + kk]));
+                    if (p.sum_out && blockIdx.x == 0) p.sum_out[(p.m0 + m) * p.k + kk] = __float2half_rn(x);
+                }
+            }
+            v[i] = x;
+#pragma unroll
+            for (int mm = 0; mm < MR; mm++)
+                if (mm == m) part[mm] += (double)r16(x * x);
+        }
+        if (p.w1) {
+            block_sums(part);
+            float inv[MR];
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                inv[m] = inv_rms(m, p.eps1);
+                part[m] = 0.0;
+            }
+            // pass B: first norm, residual add
+            for (int i = threadIdx.x; i < MR * K; i += blockDim.x) {
+                const int m = i / K, kk = i - m * K;
+                float iv = 0.f;
+#pragma unroll
+                for (int mm = 0; mm < MR; mm++)
+                    if (mm == m) iv = inv[mm];
+                float x = r16(r16(v[i] * iv) * __half2float(p.w1[kk]));
+                if (p.res && p.m0 + m < p.m_total) {
+                    x = r16(x + __half2float(p.res[(p.m0 + m) * p.k + kk]));
+                    if (p.sum_out && blockIdx.x == 0) p.sum_out[(p.m0 + m) * p.k + kk] = __float2half_rn(x);
+                }
+                v[i] = x;
+#pragma unroll
+                for (int mm = 0; mm < MR; mm++)
+                    if (mm == m) part[mm] += (double)r16(x * x);
+            }
+        }
+        float inv2[MR];
+#pragma unroll
+        for (int m = 0; m < MR; m++) inv2[m] = 0.f;
+        if (p.w2) {
+            block_sums(part);
+#pragma unroll
+            for (int m = 0; m < MR; m++) inv2[m] = inv_rms(m, p.eps2);
+        } else {
+            __syncthreads();  // pass C reads what other threads wrote to v
+        }
+        // pass C: second norm, f16, fragment order (zero beyond K)
+        const int kpad = p.k_tiles * 128;
+        for (int i = threadIdx.x; i < MR * kpad; i += blockDim.x) {
+            const int m = i / kpad, kk = i - m * kpad;
+            float x = 0.f;
+            if (kk < K) {
+                x = v[m * K + kk];
+                if (p.w2) {
+                    float iv = 0.f;
+#pragma unroll
+                    for (int mm = 0; mm < MR; mm++)
+                        if (mm == m) iv = inv2[mm];
+                    x = r16(x * iv) * __half2float(p.w2[kk]);
+                }
+            }
+            const int kt = kk >> 7, ct = (kk >> 5) & 3, cm = (kk >> 3) & 3, e = kk & 7;
+            ah[(((kt * 4 + cm) * MR + m) * 4 + ct) * 8 + e] = __float2half_rn(x);
+        }
+        __syncthreads();  // the scratch becomes the output staging from here on
     }
-    __syncthreads();
 
     // lanes without an activation row read chunk 0 and ignore it
     const bool has_b = g < MR;
@@ -322,7 +463,7 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
                 consumed++;
                 if (seg_left == 0) {
                     if (seg_len == p.k_tiles) {
-                        stream_store<MR>(p, acc, cta_rt0 + rt, lane);
+                        stream_stage<MR>(aux, acc, rt, lane);
                     } else {
                         double2* mine = reinterpret_cast<double2*>(pieces + (warp * 2 + (first_seg ? 0 : 1)) * 128) + 2 * lane;
                         mine[0] = make_double2(acc[0], acc[1]);
@@ -372,7 +513,33 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
                 sum[2] += v1.x;
                 sum[3] += v1.y;
             }
-            stream_store<MR>(p, sum, cta_rt0 + r, lane);
+            stream_stage<MR>(aux, sum, r, lane);
+        }
+    }
+    __syncthreads();
+
+    // Staged results → global memory, consecutive threads on consecutive rows.
+    if (p.geglu == 0) {
+        for (int i = threadIdx.x; i < cta_rts * 16 * MR; i += blockDim.x) {
+            const int col = i / (cta_rts * 16), rr = i - col * (cta_rts * 16);  // rr = row within the CTA
+            const int rtg = cta_rt0 + (rr >> 4);
+            int seg = 0;
+            if (p.n_seg > 1 && rtg >= p.seg_rt0[1]) seg = 1;
+            if (p.n_seg > 2 && rtg >= p.seg_rt0[2]) seg = 2;
+            const long long row = (long long)(rtg - p.seg_rt0[seg]) * 16 + (rr & 15), mrow = p.m0 + col;
+            if (row < p.seg_n[seg] && mrow < p.m_total) p.y[seg][mrow * p.seg_n[seg] + row] = __float2half_rn(aux[rr * MR + col]);
+        }
+    } else {
+        // row tiles alternate gate, up: pair j of the CTA holds rows 16·(cta_rt0/2 + j) … of both
+        const int pairs = cta_rts / 2;
+        for (int i = threadIdx.x; i < pairs * 16 * MR; i += blockDim.x) {
+            const int col = i / (pairs * 16), rr = i - col * (pairs * 16);
+            const int pj = rr >> 4, r = rr & 15;
+            const long long row = (long long)(cta_rt0 / 2 + pj) * 16 + r, mrow = p.m0 + col;
+            if (row < p.seg_n[0] && mrow < p.m_total) {
+                const float gate = aux[((2 * pj) * 16 + r) * MR + col], up = aux[((2 * pj + 1) * 16 + r) * MR + col];
+                p.y[0][mrow * p.seg_n[0] + row] = __float2half_rn(geglu_value(p, gate, up));
+            }
         }
     }
 }
@@ -382,12 +549,15 @@ size_t nbits_tiled_bytes(long long n, long long n_blocks, bool has_zp) {
     return (size_t)(row_tiles * k_tiles) * (size_t)(kTileW + kTileS + (has_zp ? kTileZ : 0));
 }
 
-void emit_nbits_pack_tiles(Emitter& em, Buf w, Buf scales, Buf zp, Buf dst, long long n, long long n_blocks, bool has_zp) {
+void emit_nbits_pack_tiles(Emitter& em, Buf w, Buf scales, Buf zp, Buf dst, long long n, long long n_blocks, bool has_zp,
+                           long long rt_mul, long long rt_add) {
     PackP p{};
     p.n = n;
     p.nb = n_blocks;
     p.row_tiles = (n + 15) / 16;
     p.k_tiles = (n_blocks + 3) / 4;
+    p.rt_mul = rt_mul;
+    p.rt_add = rt_add;
     p.tile_bytes = kTileW + kTileS + (has_zp ? kTileZ : 0);
     em.launch(nbits_pack_tiles, dim3(grid_for(p.row_tiles * p.k_tiles * 64, 256)), dim3(256), 0, p,
               {{&p.w, w}, {&p.scales, scales}, {&p.zp, has_zp ? zp : Buf{kSlotNull, 0}}, {&p.dst, dst}}, "nbits_pack_tiles");
@@ -413,44 +583,87 @@ template <bool Z> StreamFn stream_fn(int mr) {
 
 constexpr size_t kSmemBudget = 200 * 1024;
 
+float to_f16(double v) { return __half2float(__double2half(v)); }
+
 }  // namespace
 
-void emit_matmul_nbits_stream(Emitter& em, const NBitsDesc& d, const TRef& a, const TRef& tiles, const TRef& y) {
+void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TRef& tiles) {
+    if (gr.m == 0) return;
     StreamP p{};
-    p.m_total = d.m;
-    p.k = d.k;
-    p.n = d.n;
-    p.row_tiles = (int)((d.n + 15) / 16);
-    p.k_tiles = (int)((d.n_blocks + 3) / 4);
-    const int tile_bytes = kTileW + kTileS + (d.has_zp ? kTileZ : 0);
+    p.m_total = gr.m;
+    p.k = gr.k;
+    p.k_tiles = (int)(((gr.k + 31) / 32 + 3) / 4);
+    p.n_seg = gr.n_seg;
+    p.geglu = gr.geglu;
+    int rt = 0;
+    for (int i = 0; i < gr.n_seg; i++) {
+        p.seg_n[i] = gr.seg_n[i];
+        p.seg_rt0[i] = rt;
+        rt += (int)((gr.seg_n[i] + 15) / 16);
+    }
+    p.seg_rt0[gr.n_seg] = rt;
+    p.row_tiles = rt;  // GeGLU: gate and up row tiles interleaved, the same count
+    if (gr.geglu && (gr.n_seg != 2 || gr.seg_n[0] != gr.seg_n[1])) throw std::runtime_error("GeGLU epilogue needs two equal segments");
+    const int tile_bytes = kTileW + kTileS + (gr.has_zp ? kTileZ : 0);
     p.node = em.node;
+    p.eps1 = to_f16(gr.eps1);
+    p.eps2 = to_f16(gr.eps2);
+    p.c_half = to_f16(0.5);
+    p.c_one = to_f16(1.0);
+    p.c_coef = to_f16(0.044715);
+    p.c_k = to_f16(std::sqrt(2.0 / 3.14159265358979323846));
+    p.c_inv_sqrt2 = to_f16(0.70710678118654752440);
 
     // tuning knob: resident CTAs per SM the grid should fill
     static const int ctas_per_sm = env_int("ONYXIA_GEMV_CTAS_PER_SM", 2, 1, 8);
     p.rts_per_cta = (int)((p.row_tiles + 148LL * ctas_per_sm - 1) / (148LL * ctas_per_sm));
+    if (gr.geglu) p.rts_per_cta = (p.rts_per_cta + 1) & ~1;  // a CTA holds whole gate/up pairs
     const long long grid = (p.row_tiles + p.rts_per_cta - 1) / p.rts_per_cta;
 
+    const bool prologue = gr.w1 || gr.res || gr.w2;
     const size_t fixed = (size_t)kWarps * kStages * kStageTiles * tile_bytes + (size_t)kWarps * kStages * 8 +
                          (size_t)kWarps * 2 * 128 * sizeof(double);
+    auto aux_bytes = [&](int mr) {
+        size_t stage = (size_t)p.rts_per_cta * 16 * mr * 4;
+        size_t pro = prologue ? (((size_t)mr * gr.k + 1) & ~(size_t)1) * 4 + (size_t)(mr * kWarps + mr) * 8 : 0;
+        return (std::max(stage, pro) + 127) / 128 * 128;
+    };
     // activation rows per pass: as many (≤ 8) as fit beside the rings
     int rows_per_pass = 8;
-    while (rows_per_pass > 1 && (size_t)p.k_tiles * 256 * rows_per_pass + fixed > kSmemBudget) rows_per_pass /= 2;
-    if ((size_t)p.k_tiles * 256 + fixed > kSmemBudget) throw std::runtime_error("MatMulNBits: K too large for the streaming kernel");
+    while (rows_per_pass > 1 && (size_t)p.k_tiles * 256 * rows_per_pass + aux_bytes(rows_per_pass) + fixed > kSmemBudget) rows_per_pass /= 2;
+    if ((size_t)p.k_tiles * 256 + aux_bytes(1) + fixed > kSmemBudget) throw std::runtime_error("MatMulNBits: K too large for the streaming kernel");
 
-    for (long long m0 = 0; m0 < d.m; m0 += rows_per_pass) {
-        const long long rows = std::min<long long>(rows_per_pass, d.m - m0);
+    const Buf null{kSlotNull, 0};
+    for (long long m0 = 0; m0 < gr.m; m0 += rows_per_pass) {
+        const long long rows = std::min<long long>(rows_per_pass, gr.m - m0);
         const int mr = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
         p.m0 = m0;
         p.act_bytes = (p.k_tiles * 256 * mr + 127) / 128 * 128;
-        const size_t smem = (size_t)p.act_bytes + fixed;
-        StreamFn fn = d.has_zp ? stream_fn<true>(mr) : stream_fn<false>(mr);
+        p.aux_bytes = (int)aux_bytes(mr);
+        const size_t smem = (size_t)p.act_bytes + p.aux_bytes + fixed;
+        StreamFn fn = gr.has_zp ? stream_fn<true>(mr) : stream_fn<false>(mr);
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
             if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
         }
         em.launch(fn, dim3((unsigned)grid), dim3(kWarps * 32), (unsigned)smem, p,
-                  {{&p.a, a.buf}, {&p.tiles, tiles.buf}, {&p.y, y.buf}, {&p.err, Buf{kSlotErr, 0}}}, "nbits_stream", /*pdl=*/true);
+                  {{&p.a, a.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.y[0], gr.y[0].buf},
+                   {&p.y[1], gr.n_seg > 1 && !gr.geglu ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null},
+                   {&p.w1, gr.w1 ? gr.w1->buf : null}, {&p.res, gr.res ? gr.res->buf : null},
+                   {&p.sum_out, gr.sum_out ? gr.sum_out->buf : null}, {&p.w2, gr.w2 ? gr.w2->buf : null}},
+                  "nbits_stream", /*pdl=*/true);
     }
+}
+
+void emit_matmul_nbits_stream(Emitter& em, const NBitsDesc& d, const TRef& a, const TRef& tiles, const TRef& y) {
+    NBitsGroup gr{};
+    gr.m = d.m;
+    gr.k = d.k;
+    gr.has_zp = d.has_zp;
+    gr.n_seg = 1;
+    gr.seg_n[0] = d.n;
+    gr.y[0] = y;
+    emit_nbits_group(em, gr, a, tiles);
 }
 
 }  // namespace oxk
