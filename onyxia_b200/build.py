@@ -31,6 +31,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # fast-math stays off: parity with the f64 interpreter needs IEEE division, sqrt and exp.
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall",
               "--expt-relaxed-constexpr", "-diag-suppress", "20012"]
+NVCC_FLAGS += os.environ.get("ONYXIA_EXTRA_NVCC_FLAGS", "").split()  # developer builds, e.g. -DOX_TRACE
 CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wextra"]
 
 
@@ -118,7 +119,7 @@ def build_cuda(force=False, verbose=False) -> str:
 
     def compile_one(path):
         obj = os.path.join(OBJ, os.path.relpath(path, CSRC).replace(os.sep, "_") + ".o")
-        key = hdr_hash + _hash([path])
+        key = hdr_hash + _hash([path]) + " ".join(NVCC_FLAGS)
         stamp = obj + ".stamp"
         if not force and os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == key:
             return obj

@@ -218,4 +218,15 @@ ox_status ox_session_argmax_last_into(ox_session* s, const ox_tensor* logits, ox
     OX_CATCH
 }
 
+#ifdef OX_TRACE
+// Developer builds only: copy the kernels' trace log (count, then entries) to the host and clear it.
+int32_t ox_debug_trace(ox_session* s, uint64_t* out, int32_t cap) {
+    s->s->wait_idle();
+    char* base = (char*)s->s->error_area() + 256;
+    cudaMemcpy(out, base, sizeof(uint64_t) * (size_t)cap, cudaMemcpyDeviceToHost);
+    cudaMemset(base, 0, 8);
+    return (int32_t)(out[0] & 0xffffffffu);
+}
+#endif
+
 }  // extern "C"

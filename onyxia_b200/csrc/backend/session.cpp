@@ -122,8 +122,8 @@ Session::Session(Backend& backend, Module legalized)
     OX_CUDA(cudaSetDevice(device_));
     if (const char* e = std::getenv("ONYXIA_DISABLE_PDL")) opt_.disable_pdl = opt_.disable_pdl || std::atoi(e) != 0;  // diagnostics
     OX_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
-    OX_CUDA(cudaMalloc((void**)&d_err_, sizeof(oxk::ErrWord)));
-    OX_CUDA(cudaMemset(d_err_, 0, sizeof(oxk::ErrWord)));
+    OX_CUDA(cudaMalloc((void**)&d_err_, kErrAreaBytes));  // the error word, then room for a developer trace log
+    OX_CUDA(cudaMemset(d_err_, 0, kErrAreaBytes));
     OX_CUDA(cudaMallocHost((void**)&h_err_, sizeof(oxk::ErrWord)));
     std::memset(h_err_, 0, sizeof(oxk::ErrWord));
     OX_CUDA(cudaEventCreate(&ev_t0_));

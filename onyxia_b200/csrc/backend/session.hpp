@@ -96,6 +96,7 @@ public:
     double host_us[3] = {0, 0, 0};
     uint64_t host_runs = 0;
     const Module& module() const { return module_; }
+    void* error_area() const { return d_err_; }
     const std::vector<std::string>& output_names() const { return output_names_; }
 
 private:
@@ -177,6 +178,7 @@ private:
     std::vector<char> input_needs_dense_;   // per module input
     std::vector<int> gqa_past_input_[2];    // per node: module-input index feeding past_k / past_v in place, or −1
     std::vector<std::string> output_names_;
+    static constexpr size_t kErrAreaBytes = 256 + 8 * 8192;
     oxk::ErrWord* d_err_ = nullptr;
     oxk::ErrWord* h_err_ = nullptr;
     bool err_pending_ = false;

@@ -93,6 +93,24 @@ __device__ __forceinline__ long long nd_offset(long long linear, const NdShape& 
     return off;
 }
 
+// Developer tracing, compiled in with -DOX_TRACE only: thread 0 of block 0 appends
+// (id, global timer) to a log that follows the error word in device memory.
+#ifdef OX_TRACE
+__device__ __forceinline__ void ox_trace(ErrWord* e, int id) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long* t = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(e) + 256);
+        const unsigned i = atomicAdd(reinterpret_cast<unsigned*>(t), 1u);
+        if (i < 8000) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            t[1 + i] = ((unsigned long long)id << 56) | (now & 0x00FFFFFFFFFFFFFFull);
+        }
+    }
+}
+#else
+#define ox_trace(e, id) ((void)0)
+#endif
+
 // Programmatic dependent launch. `pdl_trigger` lets the next kernel in the
 // stream start its prologue once every CTA of this grid has called it;
 // `pdl_wait` returns when all earlier grids have completed and their writes are

@@ -407,7 +407,9 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
     double* xsum = reinterpret_cast<double*>(xmax + 8 * GT);                // [8 ranks][GT] sums,   written by every CTA of the cluster
     float* xpart = reinterpret_cast<float*>(xsum + 8 * GT);                 // [8 ranks][GT][slice] partial outputs of this CTA's slice
 
+    ox_trace(p.err, 11);
     pdl_enter();
+    ox_trace(p.err, 12);
 
     const long long b = blockIdx.z;
     const long long kvh = blockIdx.y / p.groups, gc = blockIdx.y % p.groups;
@@ -468,6 +470,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     for (int i = 0; i < kRing; i++) fetch(i);
+    ox_trace(p.err, 13);
 
     // 1. rotated q for the heads of the group (zero rows up to 8), the new k / v rows, zeroed padding.
     // Thread e owns element e of every row, so all its loads are independent and issued together.
@@ -476,22 +479,33 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         const int e = tid;
         const bool rot = e < 2 * p.half, first = e < p.half;
         const int j = first ? e : e - (int)p.half, e2 = first ? e + (int)p.half : e - (int)p.half;  // partner element
-        float c = 1.f, s = 0.f;
-        if (rot) {
-            c = ld<DT>(p.cos, rope_row * p.half + j);
-            s = ld<DT>(p.sin, rope_row * p.half + j);
-        }
-        float x[GT + 1], y[GT + 1];  // rows: the group's q heads, then the new k
+        // unconditional loads from clamped addresses, all issued before any is used
+        const int jc = rot ? j : 0;
         const long long kbase = (b * p.KV + kvh) * D;
+        const __half* hq = reinterpret_cast<const __half*>(p.q);
+        const __half* hk = reinterpret_cast<const __half*>(p.k);
+        const __half* hv = reinterpret_cast<const __half*>(p.v);
+        const __half* hcos = p.half ? reinterpret_cast<const __half*>(p.cos) : hq;
+        const __half* hsin = p.half ? reinterpret_cast<const __half*>(p.sin) : hq;
+        const __half rc = hcos[p.half ? rope_row * p.half + jc : 0], rsn = hsin[p.half ? rope_row * p.half + jc : 0];
+        __half rx[GT + 1], ry[GT + 1];
 #pragma unroll
         for (int hh = 0; hh < GT; hh++) {
             const long long base = (b * p.H + h0 + (hh < live ? hh : 0)) * D;
-            x[hh] = ld<DT>(p.q, base + e);
-            y[hh] = rot ? ld<DT>(p.q, base + e2) : 0.f;
+            rx[hh] = hq[base + e];
+            ry[hh] = hq[base + (rot ? e2 : e)];
         }
-        x[GT] = owns_new ? ld<DT>(p.k, kbase + e) : 0.f;
-        y[GT] = owns_new && rot ? ld<DT>(p.k, kbase + e2) : 0.f;
-        if (owns_new) new_v = ld<DT>(p.v, kbase + e);
+        rx[GT] = hk[kbase + e];
+        ry[GT] = hk[kbase + (rot ? e2 : e)];
+        const __half rv = hv[kbase + e];
+        const float c = rot ? __half2float(rc) : 1.f, s = rot ? __half2float(rsn) : 0.f;
+        float x[GT + 1], y[GT + 1];  // rows: the group's q heads, then the new k
+#pragma unroll
+        for (int hh = 0; hh <= GT; hh++) {
+            x[hh] = __half2float(rx[hh]);
+            y[hh] = rot ? __half2float(ry[hh]) : 0.f;
+        }
+        if (owns_new) new_v = __half2float(rv);
         // first half: x1·cos − x2·sin; second half: x2·cos + x1·sin, with x the own element and y the partner
         auto turn = [&](float own, float partner) {
             if (!rot) return own;
@@ -511,6 +525,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
     }
     for (int i = tid; i < 8 * (kpad + 8); i += kThreads) p_h[i] = __float2half(0.f);
     cluster.sync();  // also: every CTA of the cluster has started, so its shared memory may be written remotely
+    ox_trace(p.err, 14);
 
     // 2. scores: q as the B operand (head dim × heads), kept in registers
     unsigned qb[D / 16][2];
@@ -551,6 +566,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         fetch(blk + kRing);
     }
 
+    ox_trace(p.err, 15);
     // 3. softmax statistics: every CTA stores its maxima (then its sums) into slot `rank` of every
     // CTA's exchange area through distributed shared memory; after the cluster barrier each reads its own copy.
     for (int hh = warp; hh < GT; hh += NW) {
@@ -561,6 +577,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         if (lane < CX) cluster.map_shared_rank(xmax, lane)[rank * GT + hh] = m;
     }
     cluster.sync();
+    ox_trace(p.err, 16);
     float gmax[GT];
 #pragma unroll
     for (int hh = 0; hh < GT; hh++) {
@@ -597,6 +614,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         }
     }
     cluster.sync();
+    ox_trace(p.err, 17);
     float total[GT];
 #pragma unroll
     for (int hh = 0; hh < GT; hh++) {
@@ -606,9 +624,12 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
     }
     for (int i = tid; i < my_n; i += kThreads)
 #pragma unroll
-        for (int hh = 0; hh < GT; hh++) p_h[hh * (kpad + 8) + i] = __double2half((double)sc[hh * kpad + i] / (double)total[hh]);
+        // e and Σ are f16 values: their f32 quotient rounds to the same f16 as the exact one would
+        // (a quotient of two 11-bit integers is never within 2⁻²⁴ of a 12-bit rounding boundary unless it is on it)
+        for (int hh = 0; hh < GT; hh++) p_h[hh * (kpad + 8) + i] = __float2half_rn(sc[hh * kpad + i] / total[hh]);
     __syncthreads();
 
+    ox_trace(p.err, 18);
     // 4. P·V: warp w owns dims [w·D/NW, (w+1)·D/NW) in n-tiles of 8; A = probabilities (heads × keys)
     constexpr int NT = D / 8 / NW;  // n-tiles per warp
     float o[NT > 0 ? NT : 1][4];
@@ -646,6 +667,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         __syncthreads();
         fetch(i + kRing);
     }
+    ox_trace(p.err, 19);
     // c0: (head g, dim n0 + 2t)  c1: (head g, dim n0 + 2t + 1); rows 8-15 of the tile are padding.
     // Dim c belongs to the CTA c / slice, which adds the CX partial values in rank order.
     const int slice = (D + CX - 1) / CX;
@@ -665,6 +687,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
         for (int r = 0; r < CX; r++) v += xpart[(r * GT + hh) * slice + i % slice];
         st<DT>(p.out, (b * p.H + h0 + hh) * D + c, v);
     }
+    ox_trace(p.err, 20);
 }
 
 template <int DPL, int GT> size_t decode_h_smem(int chunk_max) {

@@ -260,8 +260,10 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
         for (int s = 0; s < kStages && s < n_stages; s++) issue(s, s);
     }
     __syncwarp();
+    ox_trace(p.err, 1);
     pdl_trigger();
     pdl_wait();
+    ox_trace(p.err, 2);
 
     // Activations → shared memory in B-fragment order: chunk (kt·4 + m)·4·MR + g·4 + t
     // holds v[m0 + g][kt·128 + t·32 + m·8 … + 8], zero beyond the matrix.
@@ -315,6 +317,111 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
             const float ms = r16d(red[MR * kWarps + m] / (double)K), denom = r16(ms + eps);
             return r16d(1.0 / sqrt((double)denom));
         };
+        const int kpad = p.k_tiles * 128;
+        constexpr int EPT = 8;  // elements per thread the fast path keeps in registers
+        if (MR * K <= EPT * kWarps * 32) {
+            // Fast path: every operand of the chain is fetched in one round of loads.
+            // The loads are unconditional, from clamped (always valid) addresses, and nothing uses a
+            // loaded value before all of them are issued: a use inside a branch would make each load
+            // wait for the one before it.
+            float xs[EPT], rs[EPT], w1s[EPT], w2s[EPT];
+            int ms[EPT], ks[EPT];
+            __half hx[EPT], hr[EPT], h1[EPT], h2[EPT];
+            const __half* res_p = p.res ? p.res : p.a;
+            const __half* w1_p = p.w1 ? p.w1 : p.a;
+            const __half* w2_p = p.w2 ? p.w2 : p.a;
+            const long long last_row = p.m_total - 1;
+#pragma unroll
+            for (int e = 0; e < EPT; e++) {
+                const int i = threadIdx.x + e * (kWarps * 32);
+                const bool in = i < MR * K;
+                const int ic = in ? i : MR * K - 1;
+                const int m = ic / K, kk = ic - m * K;
+                const long long row = p.m0 + m < last_row ? p.m0 + m : last_row;
+                ms[e] = in ? m : -1;
+                ks[e] = kk;
+                hx[e] = p.a[row * p.k + kk];
+                hr[e] = res_p[row * p.k + kk];
+                h1[e] = w1_p[kk];
+                h2[e] = w2_p[kk];
+            }
+#pragma unroll
+            for (int e = 0; e < EPT; e++) {
+                const bool row_ok = ms[e] >= 0 && p.m0 + ms[e] < p.m_total;
+                xs[e] = row_ok ? __half2float(hx[e]) : 0.f;
+                rs[e] = row_ok && p.res ? __half2float(hr[e]) : 0.f;
+                w1s[e] = __half2float(h1[e]);
+                w2s[e] = __half2float(h2[e]);
+            }
+            double* red_a = red;
+            double* red_b = red + MR * kWarps;
+            auto sums = [&](double* buf, float (&inv)[MR], float eps) {  // Σ r16(x²) per row over the CTA → 1/rms
+                double part[MR];
+#pragma unroll
+                for (int m = 0; m < MR; m++) part[m] = 0.0;
+#pragma unroll
+                for (int e = 0; e < EPT; e++)
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (ms[e] == m) part[m] += (double)r16(xs[e] * xs[e]);
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    double x = part[m];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+                    if (lane == 0) buf[m * kWarps + warp] = x;
+                }
+                __syncthreads();
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    double tot = 0.0;
+#pragma unroll
+                    for (int w = 0; w < kWarps; w++) tot += buf[m * kWarps + w];
+                    const float msq = r16d(tot / (double)K), denom = r16(msq + eps);
+                    inv[m] = r16d(1.0 / sqrt((double)denom));
+                }
+            };
+            auto add_res = [&]() {
+#pragma unroll
+                for (int e = 0; e < EPT; e++) {
+                    if (ms[e] < 0 || p.m0 + ms[e] >= p.m_total) continue;
+                    xs[e] = r16(xs[e] + rs[e]);
+                    if (p.sum_out && blockIdx.x == 0) p.sum_out[(p.m0 + ms[e]) * p.k + ks[e]] = __float2half_rn(xs[e]);
+                }
+            };
+            if (p.w1) {
+                float inv[MR];
+                sums(red_a, inv, p.eps1);
+#pragma unroll
+                for (int e = 0; e < EPT; e++)
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (ms[e] == m) xs[e] = r16(r16(xs[e] * inv[m]) * w1s[e]);
+            }
+            if (p.res) add_res();
+            if (p.w2) {
+                float inv[MR];
+                sums(red_b, inv, p.eps2);
+#pragma unroll
+                for (int e = 0; e < EPT; e++)
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (ms[e] == m) xs[e] = r16(xs[e] * inv[m]) * w2s[e];
+            }
+            // f16, fragment order; the tail of the last k tile is cleared first
+            for (int i = K + threadIdx.x; i < kpad; i += blockDim.x) {
+                const int kt = i >> 7, ct = (i >> 5) & 3, cm = (i >> 3) & 3, e8 = i & 7;
+#pragma unroll
+                for (int m = 0; m < MR; m++) ah[(((kt * 4 + cm) * MR + m) * 4 + ct) * 8 + e8] = __float2half(0.f);
+            }
+#pragma unroll
+            for (int e = 0; e < EPT; e++) {
+                if (ms[e] < 0) continue;
+                const int kk = ks[e], kt = kk >> 7, ct = (kk >> 5) & 3, cm = (kk >> 3) & 3, e8 = kk & 7;
+                ah[(((kt * 4 + cm) * MR + ms[e]) * 4 + ct) * 8 + e8] = __float2half_rn(xs[e]);
+            }
+            __syncthreads();  // the scratch becomes the output staging from here on
+        } else {
         double part[MR];
 #pragma unroll
         for (int m = 0; m < MR; m++) part[m] = 0.0;
@@ -371,7 +478,6 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
             __syncthreads();  // pass C reads what other threads wrote to v
         }
         // pass C: second norm, f16, fragment order (zero beyond K)
-        const int kpad = p.k_tiles * 128;
         for (int i = threadIdx.x; i < MR * kpad; i += blockDim.x) {
             const int m = i / kpad, kk = i - m * kpad;
             float x = 0.f;
@@ -389,8 +495,10 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
             ah[(((kt * 4 + cm) * MR + m) * 4 + ct) * 8 + e] = __float2half_rn(x);
         }
         __syncthreads();  // the scratch becomes the output staging from here on
+        }
     }
 
+    ox_trace(p.err, 3);
     // lanes without an activation row read chunk 0 and ignore it
     const bool has_b = g < MR;
     const uint4* as_lane = reinterpret_cast<const uint4*>(smem) + (has_b ? g * 4 + t : 0);
@@ -495,6 +603,7 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
         for (int s = st; s < issued; s++) mbar_wait(bars + (s % kStages) * 8, (s / kStages) & 1);
     }
 
+    ox_trace(p.err, 4);
     // Row tiles cut by a boundary between two warps' ranges: the warp after the
     // first boundary inside the row tile adds the pieces in range order.
     __syncthreads();
@@ -518,6 +627,7 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
     }
     __syncthreads();
 
+    ox_trace(p.err, 5);
     // Staged results → global memory, consecutive threads on consecutive rows.
     if (p.geglu == 0) {
         for (int i = threadIdx.x; i < cta_rts * 16 * MR; i += blockDim.x) {
@@ -542,6 +652,7 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
             }
         }
     }
+    ox_trace(p.err, 6);
 }
 
 size_t nbits_tiled_bytes(long long n, long long n_blocks, bool has_zp) {
@@ -625,7 +736,7 @@ void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TR
                          (size_t)kWarps * 2 * 128 * sizeof(double);
     auto aux_bytes = [&](int mr) {
         size_t stage = (size_t)p.rts_per_cta * 16 * mr * 4;
-        size_t pro = prologue ? (((size_t)mr * gr.k + 1) & ~(size_t)1) * 4 + (size_t)(mr * kWarps + mr) * 8 : 0;
+        size_t pro = prologue ? (((size_t)mr * gr.k + 1) & ~(size_t)1) * 4 + (size_t)(2 * mr * kWarps + mr) * 8 : 0;
         return (std::max(stage, pro) + 127) / 128 * 128;
     };
     // activation rows per pass: as many (≤ 8) as fit beside the rings
