@@ -135,6 +135,17 @@ ox_module* ox_module_new(void);
 void ox_module_free(ox_module*);
 /* Deep copy of the graph; constant bytes are shared, not copied. */
 ox_module* ox_module_clone(const ox_module*);
+/* Tensor-parallel partition (no counterpart in the reference, which executes on one
+ * device): a new module holding what rank `rank` of `tp` ranks executes. Pairs of
+ * MatMulNBits nodes are split along N then K (column-split Q/K/V/gate/up, row-split
+ * O/down), attention runs on the rank's heads and its share of the KV cache (the
+ * declared shapes of the cache inputs and outputs shrink by `tp` along the head axis),
+ * and an `onyxia.AllReduce` composite follows every K-split node; a backend created
+ * with ox_backend_create_tp executes it as a sum over the ranks. The source module is
+ * left untouched. `ox_module_tp_stats` reports how many nodes would be split along N
+ * (out[0]), along K (out[1]) and how many attention nodes (out[2]). */
+ox_status ox_module_tp_partition(const ox_module*, int32_t tp, int32_t rank, ox_module** out);
+void ox_module_tp_stats(const ox_module*, int32_t tp, uint64_t out[3]);
 /* ≙ GraphBuilder::sym (builder.rs:69-71). */
 int32_t ox_module_intern_symbol(ox_module*, const char* name);
 /* ≙ GraphBuilder::constant (builder.rs:127-135). With borrow != 0 the bytes

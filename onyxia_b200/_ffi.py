@@ -72,6 +72,8 @@ SIGNATURES = {
     "ox_module_new": (_P, []),
     "ox_module_free": (None, [_P]),
     "ox_module_clone": (_P, [_P]),
+    "ox_module_tp_partition": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(_P)]),
+    "ox_module_tp_stats": (None, [_P, C.c_int32, C.POINTER(C.c_uint64)]),
     "ox_module_intern_symbol": (C.c_int32, [_P, C.c_char_p]),
     "ox_module_add_const": (C.c_int32, [_P, C.c_int32, _u64p, C.c_int32, _P, C.c_size_t, C.c_int32, _i32p]),
     "ox_module_add_input": (C.c_int32, [_P, C.c_char_p, C.c_int32, C.POINTER(DimExprC), C.c_int32, _i32p]),

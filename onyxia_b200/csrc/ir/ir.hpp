@@ -319,6 +319,13 @@ struct Module {
     void remove_nodes(const std::unordered_set<NodeId>& dead);
 };
 
+// The part of `m` that rank `rank` of `tp` tensor-parallel ranks executes:
+// MatMulNBits pairs split along N then K with an `onyxia.AllReduce` composite
+// after every K-split node, attention on the rank's heads and its share of the
+// KV cache, everything else replicated (see tp.cpp).
+Module tp_partition(const Module& m, int tp, int rank);
+void tp_partition_stats(const Module& m, int tp, size_t* col, size_t* row, size_t* attn);
+
 // Remove nodes none of whose outputs are consumed; returns how many.
 size_t eliminate_dead(Module& m);
 

@@ -100,6 +100,31 @@ ox_module* ox_module_clone(const ox_module* m) {
     return c;
 }
 
+ox_status ox_module_tp_partition(const ox_module* m, int32_t tp, int32_t rank, ox_module** out) {
+    OX_TRY
+    auto* c = new ox_module();
+    try {
+        c->b.module() = tp_partition(const_cast<ox_module*>(m)->b.module(), tp, rank);
+    } catch (...) {
+        delete c;
+        throw;
+    }
+    *out = c;
+    return OX_OK;
+    OX_CATCH
+}
+
+void ox_module_tp_stats(const ox_module* m, int32_t tp, uint64_t out[3]) {
+    size_t c = 0, r = 0, a = 0;
+    try {
+        tp_partition_stats(const_cast<ox_module*>(m)->b.module(), tp, &c, &r, &a);
+    } catch (...) {
+    }
+    out[0] = c;
+    out[1] = r;
+    out[2] = a;
+}
+
 int32_t ox_module_intern_symbol(ox_module* m, const char* name) {
     return (int32_t)m->b.module().symbols.intern(name);
 }

@@ -196,6 +196,18 @@ class Module:
     def clone(self) -> "Module":
         return Module(_ffi.ir_lib().ox_module_clone(self.handle), self._keep)
 
+    def tp_partition(self, tp: int, rank: int) -> "Module":
+        """The module rank `rank` of `tp` tensor-parallel ranks executes (this module is left untouched)."""
+        out = C.c_void_p()
+        check(_ffi.ir_lib().ox_module_tp_partition(self.handle, tp, rank, C.byref(out)))
+        return Module(out, self._keep)
+
+    def tp_stats(self, tp: int) -> tuple:
+        """(MatMulNBits nodes split along N, split along K, attention nodes split) for `tp` ranks."""
+        out = (C.c_uint64 * 3)()
+        _ffi.ir_lib().ox_module_tp_stats(self.handle, tp, out)
+        return out[0], out[1], out[2]
+
     def validate(self) -> None:
         check(_ffi.ir_lib().ox_module_validate(self.handle))
 

@@ -937,6 +937,21 @@ static std::vector<std::pair<std::string, Tensor>> eval_with(const Module& m, co
     }
     for (size_t step = 0; step < order.size(); step++) {
         const Node& node = m.nodes[order[step]];
+        if (!node.is_prim && node.composite.name == "onyxia.AllReduce") {
+            // The sum over tensor-parallel ranks: the test harness supplies it (another thread or process
+            // holds the other ranks' interpreters). Element type and count travel with the call.
+            if (!allreduce_hook()) fail(ErrKind::Interp, "onyxia.AllReduce needs an all-reduce hook");
+            if (!have[node.inputs[0]]) fail(ErrKind::Interp, "input value not yet materialized");
+            Tensor t = slots[node.inputs[0]];
+            materialize(t);
+            Tensor out = Tensor::from_bytes(t.dtype, t.shape, t.data, t.nbytes());
+            allreduce_hook()(out.mut(), (uint64_t)out.numel(), (int32_t)out.dtype);
+            slots[node.outputs[0]] = std::move(out);
+            have[node.outputs[0]] = 1;
+            if (deaths)
+                for (auto v : (*deaths)[step]) slots[v] = Tensor();
+            continue;
+        }
         if (!node.is_prim)
             fail(ErrKind::Interp, "composite '" + node.composite.name + "' must be inlined before interpretation");
         std::vector<const Tensor*> ins;
@@ -972,13 +987,19 @@ static std::vector<std::pair<std::string, Tensor>> eval_with(const Module& m, co
     return outs;
 }
 
+AllReduceHook& allreduce_hook() {
+    static AllReduceHook hook = nullptr;
+    return hook;
+}
+
 std::vector<std::pair<std::string, Tensor>> eval(const Module& m, const std::vector<std::pair<std::string, Tensor>>& inputs) {
     return eval_with(m, m.topo_order(), nullptr, inputs);
 }
 
 RefSession prepare(Module m) {
     RefSession s;
-    s.module = inline_composites(std::move(m), standard_decompositions(), [](const Module&, const Node&) { return false; });
+    s.module = inline_composites(std::move(m), standard_decompositions(),
+                                 [](const Module&, const Node& n) { return !n.is_prim && n.composite.name == "onyxia.AllReduce"; });
     validate(s.module);
     s.order = s.module.topo_order();
     // Values are dropped after their last reader so big models fit in host

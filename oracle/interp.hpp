@@ -62,6 +62,11 @@ struct LazyDequant {
     size_t block_size = 0;
 };
 
+// Called for every `onyxia.AllReduce` node: sum `count` elements of dtype code `dtype` in place
+// with the other tensor-parallel ranks (supplied by the test that runs the ranks).
+using AllReduceHook = void (*)(void* data, uint64_t count, int32_t dtype);
+AllReduceHook& allreduce_hook();
+
 // Evaluate one primitive (interp.rs:511-799). May bind late symbols.
 Tensor eval_prim(const ox::Prim& p, const std::vector<const Tensor*>& ins, ox::Bindings& bindings);
 // Write out a lazily dequantised tensor.

@@ -26,6 +26,7 @@ struct oxref_result {
 extern "C" {
 
 void oxref_set_threads(int n) { oxref::set_threads(n); }
+void oxref_set_allreduce_hook(oxref::AllReduceHook hook) { oxref::allreduce_hook() = hook; }
 int oxref_get_threads(void) { return oxref::get_threads(); }
 
 // Inline every composite and validate; consumes the module.

@@ -53,6 +53,35 @@ def lib():
     return _lib
 
 
+ALLREDUCE_HOOK = C.CFUNCTYPE(None, C.c_void_p, C.c_uint64, C.c_int32)
+_hook_keepalive = None
+
+
+def set_allreduce_hook(fn) -> None:
+    """Install the function the interpreter calls at every ``onyxia.AllReduce`` node:
+    ``fn(numpy_view)`` must replace the view's content by its sum over the tensor-parallel
+    ranks (the test that runs the ranks — as threads or as processes — supplies it).
+    ``None`` removes the hook."""
+    global _hook_keepalive
+    if fn is None:
+        lib().oxref_set_allreduce_hook.argtypes = [C.c_void_p]
+        lib().oxref_set_allreduce_hook(None)
+        _hook_keepalive = None
+        return
+    import numpy as np
+    from onyxia_b200 import ir
+    np_of = {ir.F32: np.float32, ir.F16: np.float16, ir.I64: np.int64, ir.I32: np.int32}
+
+    def thunk(data, count, dtype):
+        arr = np.ctypeslib.as_array(C.cast(data, C.POINTER(C.c_uint8)), shape=(count * np.dtype(np_of[dtype]).itemsize,))
+        fn(arr.view(np_of[dtype]))
+
+    cb = ALLREDUCE_HOOK(thunk)
+    lib().oxref_set_allreduce_hook.argtypes = [ALLREDUCE_HOOK]
+    lib().oxref_set_allreduce_hook(cb)
+    _hook_keepalive = cb
+
+
 def set_threads(n: int) -> None:
     """1 = the reference's single-threaded behaviour; more threads split big
     loops over outputs without changing any accumulation order."""
