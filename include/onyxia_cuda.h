@@ -209,6 +209,15 @@ ox_status ox_backend_create(const int32_t* device_ordinals, int32_t n_devices, o
 ox_status ox_backend_create_ex(const int32_t* device_ordinals, int32_t n_devices,
                                const ox_backend_options* options, ox_backend** out);
 void ox_backend_free(ox_backend*);
+/* Tensor parallelism (no counterpart in the reference). One process per GPU: rank 0 obtains an
+ * id with ox_tp_unique_id and distributes its 128 bytes by whatever channel the host has; every
+ * rank then calls ox_backend_join_tp on its backend (a collective call: it returns when all
+ * `world` ranks have joined). A joined backend executes the `onyxia.AllReduce` composites that
+ * ox_module_tp_partition inserts as NCCL all-reduces on the session's stream.
+ * `nccl_library_path` names libnccl.so.2 when the process has not loaded NCCL yet (NULL: search
+ * the loader path); the library is opened at run time, so nothing here is needed on one GPU. */
+ox_status ox_tp_unique_id(const char* nccl_library_path, uint8_t out[128]);
+ox_status ox_backend_join_tp(ox_backend*, int32_t rank, int32_t world, const uint8_t id[128], const char* nccl_library_path);
 /* ≙ Backend::supports (backend.rs:28-31): 1 if a fused kernel is registered under this name. */
 int32_t ox_backend_supports(const ox_backend*, const char* composite_name);
 /* ≙ Backend::prepare (backend.rs:33-34). Consumes `module` (also on failure). */

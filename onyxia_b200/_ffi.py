@@ -121,6 +121,8 @@ SIGNATURES = {
     "ox_session_plan_stats": (None, [_P, _u64p]),
     "ox_session_argmax_last": (C.c_int32, [_P, _P, C.POINTER(_P)]),
     "ox_session_argmax_last_into": (C.c_int32, [_P, _P, _P]),
+    "ox_tp_unique_id": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint8)]),
+    "ox_backend_join_tp": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint8), C.c_char_p]),
 }
 
 # Symbols implemented by the host-only IR library (the rest need the CUDA one).

@@ -155,6 +155,20 @@ class CudaSession:
             pass
 
 
+def nccl_library_path():
+    """libnccl.so.2 as shipped beside torch (None if it cannot be found: the loader path is searched then)."""
+    try:
+        import nvidia.nccl  # type: ignore
+        import os
+        for d in nvidia.nccl.__path__:
+            p = os.path.join(d, "lib", "libnccl.so.2")
+            if os.path.exists(p):
+                return p
+    except Exception:  # noqa: BLE001 - optional
+        pass
+    return None
+
+
 class CudaBackend:
     """≙ ``impl Backend`` (session.rs:107-242)."""
 
@@ -177,6 +191,28 @@ class CudaBackend:
 
     def supports(self, composite: str) -> bool:
         return bool(self._lib.ox_backend_supports(self._h, composite.encode()))
+
+    # tensor parallelism: one process per GPU, the id travels by whatever channel the host has
+    @staticmethod
+    def tp_unique_id(nccl_path: str | None = None) -> bytes:
+        out = (C.c_uint8 * 128)()
+        check(_ffi.cuda_lib().ox_tp_unique_id(nccl_path.encode() if nccl_path else None, out))
+        return bytes(out)
+
+    def join_tp(self, rank: int, world: int, unique_id: bytes, nccl_path: str | None = None) -> None:
+        """Collective: returns when all `world` ranks have joined. Afterwards the backend executes
+        modules made by ``Module.tp_partition(world, rank)``."""
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        check(self._lib.ox_backend_join_tp(self._h, rank, world, buf, nccl_path.encode() if nccl_path else None))
+
+    def join_tp_torch(self, group=None) -> tuple:
+        """Join the group formed by a torch.distributed process group (used only to pass the id around)."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        box = [self.tp_unique_id(nccl_library_path()) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=group)
+        self.join_tp(rank, world, box[0], nccl_library_path())
+        return rank, world
 
     def prepare(self, module: Module) -> CudaSession:
         keep = module._keep

@@ -52,6 +52,20 @@ ox_status ox_backend_create(const int32_t* device_ordinals, int32_t n_devices, o
     return ox_backend_create_ex(device_ordinals, n_devices, nullptr, out);
 }
 
+ox_status ox_tp_unique_id(const char* nccl_library_path, uint8_t out[128]) {
+    OX_TRY
+    oxrt::tp_unique_id(nccl_library_path, out);
+    return OX_OK;
+    OX_CATCH
+}
+
+ox_status ox_backend_join_tp(ox_backend* b, int32_t rank, int32_t world, const uint8_t id[128], const char* nccl_library_path) {
+    OX_TRY
+    b->b->join(std::make_shared<oxrt::Communicator>(b->b->device(), rank, world, id, nccl_library_path));
+    return OX_OK;
+    OX_CATCH
+}
+
 void ox_backend_free(ox_backend* b) { delete b; }
 
 int32_t ox_backend_supports(const ox_backend* b, const char* name) { return b->b->supports(name) ? 1 : 0; }

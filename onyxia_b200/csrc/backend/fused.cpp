@@ -214,7 +214,37 @@ void nbits_lower(FusedCtx& c) {
     oxk::emit_matmul_nbits(c.em, d, c.ins[0], c.ins[1], c.ins[2], d.has_zp ? &c.ins[3] : nullptr, c.outs[0]);
 }
 
+// ── onyxia.AllReduce (tensor parallelism) ──
+bool allreduce_accepts(const Module& m, const Node& n) {
+    if (n.inputs.size() != 1 || n.outputs.size() != 1) return false;
+    const TensorType& t = ty(m, n.inputs[0]);
+    return (t.dtype == DType::F16 || t.dtype == DType::F32) && t == ty(m, n.outputs[0]);
+}
+void allreduce_lower(FusedCtx& c) { oxk::emit_allreduce(c.em, c.ins[0], c.outs[0]); }
+
 }  // namespace
+
+}  // namespace oxrt
+
+namespace oxk {
+void emit_allreduce(Emitter& em, const TRef& x, const TRef& y) {
+    if (x.numel() == 0) return;
+    CollP p{};
+    p.count = (unsigned long long)x.numel();
+    p.dtype = x.dtype;
+    LaunchRec r;
+    r.coll = 1;
+    r.params.resize(sizeof(CollP));
+    std::memcpy(r.params.data(), &p, sizeof(CollP));
+    r.relocs.push_back(Reloc{(uint32_t)offsetof(CollP, send), x.buf});
+    r.relocs.push_back(Reloc{(uint32_t)offsetof(CollP, recv), y.buf});
+    r.label = "allreduce";
+    r.node = em.node;
+    em.recs.push_back(std::move(r));
+}
+}  // namespace oxk
+
+namespace oxrt {
 
 const KernelRegistry& standard_kernels() {
     static const KernelRegistry reg = [] {
@@ -226,6 +256,7 @@ const KernelRegistry& standard_kernels() {
         r.add({"com.microsoft.GemmaRotaryEmbedding", rotary_accepts, rotary_lower});
         r.add({"com.microsoft.GroupQueryAttention", gqa_accepts, gqa_lower});
         r.add({"com.microsoft.MatMulNBits", nbits_accepts, nbits_lower});
+        r.add({"onyxia.AllReduce", allreduce_accepts, allreduce_lower});
         return r;
     }();
     return reg;

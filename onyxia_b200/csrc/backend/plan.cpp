@@ -518,6 +518,14 @@ std::vector<Timing> Session::take_timings() {
 // programmatic dependent launch get the stream-serialisation attribute, so they
 // may begin while the launch before them is still running.
 void Session::launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_pdl) {
+    if (r.coll) {
+        oxk::CollP c;
+        std::memcpy(&c, param_bytes, sizeof(c));
+        Communicator* comm = backend_.communicator();
+        if (!comm) fail(ErrKind::Runtime, "all-reduce without a tensor-parallel group");
+        comm->allreduce_sum(c.send, c.recv, (size_t)c.count, (DType)c.dtype, stream_);
+        return;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = r.grid;
     cfg.blockDim = r.block;
@@ -560,6 +568,10 @@ void Session::build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& p
             const cudaGraphNode_t* deps = nullptr;
             size_t n_deps = 0;
             OX_CUDA(cudaStreamGetCaptureInfo_v3(stream_, &status, nullptr, nullptr, &deps, nullptr, &n_deps));
+            if (plan.recs[i].coll) {  // a collective may record several nodes; it is never patched in place
+                plan.graph_nodes.push_back(nullptr);
+                continue;
+            }
             if (status != cudaStreamCaptureStatusActive || n_deps != 1)
                 fail(ErrKind::Runtime, "internal: stream capture lost track of a launch");
             plan.graph_nodes.push_back(deps[0]);
@@ -654,6 +666,10 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
                 const oxk::LaunchRec& r = plan.recs[i];
                 bool same_grid = plan.graph_grids[i].x == r.grid.x && plan.graph_grids[i].y == r.grid.y && plan.graph_grids[i].z == r.grid.z;
                 if (same_grid && params[i] == plan.graph_params[i]) continue;
+                if (r.coll) {  // the buffers of a captured collective moved: record the graph again
+                    rebuild = true;
+                    break;
+                }
                 cudaKernelNodeParams kp{};
                 void* args[1] = {params[i].data()};
                 kp.func = const_cast<void*>(r.func);

@@ -139,10 +139,34 @@ struct Timing {
     uint64_t time_ns;
 };
 
+// One rank's end of a tensor-parallel group (NCCL underneath, loaded on first use).
+class Communicator {
+public:
+    Communicator(int device, int rank, int world, const uint8_t id_bytes[128], const char* nccl_path);
+    ~Communicator();
+    Communicator(const Communicator&) = delete;
+    Communicator& operator=(const Communicator&) = delete;
+    int rank() const { return rank_; }
+    int world() const { return world_; }
+    // Enqueues the sum over all ranks on `stream` (capturable into a CUDA graph).
+    void allreduce_sum(const void* send, void* recv, size_t count, DType dtype, cudaStream_t stream);
+
+private:
+    void* comm_ = nullptr;
+    int rank_, world_;
+};
+// The id rank 0 creates and hands to every rank of a new group (by whatever channel the host has).
+void tp_unique_id(const char* nccl_path, uint8_t out[128]);
+
 class Backend {
 public:
     Backend(std::vector<int> devices, Options opt);
-    bool supports(const std::string& name) const { return !opt_.without_fused && standard_kernels().contains(name); }
+    bool supports(const std::string& name) const {
+        if (name == "onyxia.AllReduce") return comm_ != nullptr;
+        return !opt_.without_fused && standard_kernels().contains(name);
+    }
+    void join(std::shared_ptr<Communicator> c) { comm_ = std::move(c); }
+    Communicator* communicator() const { return comm_.get(); }
     std::unique_ptr<Session> prepare(Module m);
     const Options& options() const { return opt_; }
     int device() const { return devices_[0]; }
@@ -150,6 +174,7 @@ public:
 private:
     std::vector<int> devices_;
     Options opt_;
+    std::shared_ptr<Communicator> comm_;
 };
 
 }  // namespace oxrt

@@ -106,6 +106,10 @@ std::unique_ptr<Session> Backend::prepare(Module m) {
     // through their decompositions even though a kernel exists.
     std::string disabled = std::string(",") + (std::getenv("ONYXIA_DISABLE_FUSED") ? std::getenv("ONYXIA_DISABLE_FUSED") : "") + ",";
     Module legal = inline_composites(std::move(m), standard_decompositions(), [&](const Module& mod, const Node& n) {
+        if (n.composite.name == "onyxia.AllReduce") {
+            if (!comm_) fail(ErrKind::Unsupported, "the module was partitioned for tensor parallelism but this backend has not joined a group");
+            return true;
+        }
         if (!fused) return false;
         if (disabled.find("," + n.composite.name + ",") != std::string::npos) return false;
         const FusedKernel* k = reg.get(n.composite.name);

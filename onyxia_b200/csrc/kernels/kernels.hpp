@@ -81,6 +81,16 @@ struct LaunchRec {
     // stream is still running (programmatic dependent launch): its prologue —
     // barrier set-up, prefetch of constant weights — overlaps the predecessor.
     bool pdl = false;
+    // Not a kernel of this library: a collective the session enqueues itself. The parameter bytes
+    // are a CollP (with the usual pointer relocations); `func` is null.
+    int coll = 0;  // 1 = sum over the tensor-parallel ranks
+};
+
+struct CollP {
+    const void* send;
+    void* recv;
+    unsigned long long count;
+    int dtype;
 };
 
 class Emitter {
@@ -270,6 +280,9 @@ struct NBitsGroup {
     double eps2;
 };
 void emit_nbits_group(Emitter&, const NBitsGroup&, const TRef& a, const TRef& tiles);
+
+// y = Σ over the tensor-parallel ranks of x (executed by the session through its communicator).
+void emit_allreduce(Emitter&, const TRef& x, const TRef& y);
 
 // argmax over the last axis, highest index among equal maxima → i64.
 // `part` is scratch of argmax_scratch_bytes(rows) bytes, `counters` the zeroed arrival counters.

@@ -115,3 +115,22 @@ def test_gemma3_1b_arch_full_depth_prefill_decode_consistency():
     tok_dev = b.step_greedy([nxt], [b.sequence_length()])
     top2 = np.sort(logits_host)[-2:]
     assert tok_dev == llm.sample_greedy(logits_host) or top2[1] - top2[0] < 4e-2
+
+
+def test_tensor_parallel_two_gpus_match_one():
+    """Two ranks (torchrun, one GPU each, NCCL all-reduce) reproduce the single-GPU logits within the f16 bound."""
+    import os
+    import subprocess
+    import sys
+
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.path.join(root, "tests"), NCCL_NVLS_ENABLE="0",
+               GLOO_SOCKET_IFNAME="lo", PYTHONUNBUFFERED="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29541", os.path.join(root, "tests", "tp_gpu_worker.py")],
+                       env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-4000:]
+    assert "max abs diff vs one GPU" in r.stdout

@@ -1,0 +1,62 @@
+"""One tensor-parallel rank on its own GPU (launched by torchrun, one process per GPU). Every rank
+prepares its partition of a small f16 decoder, runs prefill + greedy decode, and rank 0 compares the
+logits with the unpartitioned model on its GPU. torch.distributed (gloo) only passes the group id."""
+import os
+import sys
+
+import numpy as np
+import torch.distributed as dist
+
+from onyxia_b200 import backend as be
+from onyxia_b200 import ir, llm, models
+
+
+def main():
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("ONYXIA_TP_TEST_WATCHDOG_S", "240")), exit=True)  # a hang ends with a stack dump
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    dist.init_process_group("gloo")
+    print(f"rank {rank}: process group up", flush=True)
+    cfg = models.config_c1()
+    cfg.act_dtype = ir.F16
+    cfg.layers, cfg.vocab = 2, 4096
+    cfg.explicit_zero_points = False
+    module = models.build_decoder(cfg, seed=7)
+    col, row, attn = module.tp_stats(world)
+    assert col == 5 * cfg.layers and row == 2 * cfg.layers and attn == cfg.layers, (col, row, attn)
+    prompt = np.random.default_rng(3).integers(0, cfg.vocab, 24).tolist()
+
+    backend = be.CudaBackend((local,))
+    backend.join_tp_torch()
+    print(f"rank {rank}: joined the tensor-parallel group", flush=True)
+    lm = llm.LlmSession(backend, module.tp_partition(world, rank), 256)
+    got = [lm.prefill(prompt)]
+    print(f"rank {rank}: prefill done", flush=True)
+    toks = []
+    for _ in range(12):
+        toks.append(llm.sample_greedy(got[-1]))
+        got.append(lm.decode(toks[-1]))
+
+    print(f"rank {rank}: decode done", flush=True)
+    # all ranks hold the same logits
+    mine = np.stack(got)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    for other in gathered:
+        assert np.array_equal(other, mine)
+
+    if rank == 0:
+        whole = llm.LlmSession(be.CudaBackend((local,)), module, 256)
+        want = [whole.prefill(prompt)]
+        for t in toks:  # teacher-forced with the partitioned run's tokens
+            want.append(whole.decode(t))
+        diff = max(float(np.abs(w - g).max()) for w, g in zip(want, got))
+        print(f"tp={world} max abs diff vs one GPU: {diff:.5f}", flush=True)
+        assert diff <= 2e-2, diff
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank} ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
