@@ -131,6 +131,51 @@ def cpu_reference_run(cfg, module, steps, warmup, threads):
     return steps / dt, dt
 
 
+C2_SHAPES = [(2048, 2048), (4096, 11008), (8192, 8192), (5376, 21504)]
+
+
+def gemv_sweep(backend, shapes, ms, peak, reps=10):
+    """int4 GEMV bandwidth per shape of the MatMulNBits sweep (config C2): one module holds enough
+    independent copies of the weight (> 126 MB of L2 in total) that every launch streams from HBM;
+    the launches run back to back in one CUDA graph and are timed with CUDA events."""
+    from onyxia_b200 import ir
+    from onyxia_b200.ir import HostTensor
+    rng = np.random.default_rng(0)
+    out = []
+    for (k, n) in shapes:
+        for m in ms:
+            nb = k // 32
+            wbytes = n * nb * 18
+            copies = max(2, min(48, int(300e6 // wbytes) + 1))
+            g = ir.GraphBuilder()
+            # one activation input per copy: nodes that share an input would be grouped into one launch
+            acts = [g.input(f"a{c}", ir.F16, [m, k]) for c in range(copies)]
+            for c in range(copies):
+                a = acts[c]
+                packed = rng.integers(0, 256, size=n * nb * 16, dtype=np.uint8)
+                scales = rng.uniform(0.005, 0.02, size=n * nb).astype(np.float16)
+                w = g.constant(HostTensor(ir.U4, [n, nb, 32], packed), borrow=True)
+                sc = g.constant(HostTensor.from_numpy(scales), borrow=True)
+                y = g.composite("com.microsoft.MatMulNBits", {"K": k, "N": n, "bits": 4, "block_size": 32}, [a, w, sc],
+                                [(ir.F16, [m, n])])[0]
+                g.output(f"y{c}", y)
+            s = backend.prepare(g.finish())
+            act = s.upload(HostTensor.from_numpy(rng.standard_normal((m, k)).astype(np.float16)))
+            feed = {f"a{c}": act for c in range(copies)}
+            for _ in range(3):
+                s.run(feed)
+            s.wait_idle()
+            s.timer_start()
+            for _ in range(reps):
+                s.run(feed)
+            us = s.timer_stop() * 1e3 / (reps * copies)
+            alg = wbytes + m * k * 2 + m * n * 2
+            out.append({"k": k, "n": n, "m": m, "copies": copies, "us_per_launch": us, "algorithmic_bytes": alg,
+                        "gbps": alg / us / 1e3, "frac_of_peak": alg / us / 1e3 / peak})
+            del s
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -138,6 +183,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemv-sweep", action="store_true",
+                    help="only run the int4 GEMV sweep over the C2 shapes (or --shapes KxN,... and --ms 1,8) and print it")
+    ap.add_argument("--shapes", default="")
+    ap.add_argument("--ms", default="1,8")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -167,6 +216,14 @@ def main():
                                  "sample": f"{steps} decode steps after a 4-token prompt"},
                 "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
+        return
+
+    if args.gemv_sweep:
+        from onyxia_b200 import backend as be
+        peak, peak_kind = load_peaks()
+        shapes = [tuple(int(x) for x in t.split("x")) for t in args.shapes.split(",") if t] or C2_SHAPES
+        res = gemv_sweep(be.CudaBackend((local_rank,)), shapes, [int(x) for x in args.ms.split(",")], peak)
+        print(json.dumps({"metric": "int4 GEMV HBM GB/s", "unit": "GB/s", "peak": peak, "peak_source": peak_kind, "gemv_sweep": res}))
         return
 
     import torch  # plumbing only: rendezvous, barrier, max over ranks
@@ -292,6 +349,8 @@ def main():
     kernel_share = {k: {"launches_per_step": v[0] / prof_steps, "us_per_step": v[1] / 1e3 / prof_steps}
                     for k, v in sorted(by_kernel.items(), key=lambda kv_: -kv_[1][1])}
 
+    sweep = gemv_sweep(backend, C2_SHAPES, [1], peak) if rank == 0 else None
+
     cpu = None
     if cpu_module is not None:
         try:
@@ -319,7 +378,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu,
             "model_roofline": {"bytes_per_token": weight_bytes + kv_bytes, "tok_s_at_peak": peak * 1e9 / (weight_bytes + kv_bytes),
                                "frac": value / world / (peak * 1e9 / (weight_bytes + kv_bytes))},
-            "planner": plan_stats, "kernels": kernel_share, "resident_bytes": sess.resident_bytes(), "model_build_s": build_s,
+            "gemv_sweep": sweep, "planner": plan_stats, "kernels": kernel_share, "resident_bytes": sess.resident_bytes(), "model_build_s": build_s,
         }
         print(json.dumps(line))
     if world > 1:
