@@ -280,6 +280,9 @@ struct NBitsGroup {
     double eps2;
 };
 void emit_nbits_group(Emitter&, const NBitsGroup&, const TRef& a, const TRef& tiles);
+// The tcgen05 GEMM form of a group's matrices (any number of activation rows, in passes of up to
+// 256): no prologue, no epilogue. `interleave2`: the stream alternates row tiles of segments 0 and 1.
+void emit_nbits_gemm_tc(Emitter&, const NBitsGroup&, const TRef& x, const TRef& tiles, bool interleave2);
 
 // y = Σ over the tensor-parallel ranks of x (executed by the session through its communicator).
 void emit_allreduce(Emitter&, const TRef& x, const TRef& y);

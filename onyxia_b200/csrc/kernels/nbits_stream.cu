@@ -698,8 +698,53 @@ float to_f16(double v) { return __half2float(__double2half(v)); }
 
 }  // namespace
 
+// More than 8 activation rows: the prologue and the epilogue run as their own launches around the
+// tensor-core GEMM, which reads the weight stream once per 256 rows instead of once per 8.
+static void emit_nbits_group_gemm(Emitter& em, const NBitsGroup& gr, const TRef& a, const TRef& tiles) {
+    auto scratch_like = [&](long long rows, long long cols) {
+        TRef t;
+        t.buf = em.scratch((size_t)(rows * cols * 2));
+        t.dtype = DT_F16;
+        t.shape = {rows, cols};
+        return t;
+    };
+    TRef cur = a;
+    cur.shape = {gr.m, gr.k};
+    if (gr.w1) {
+        TRef t = scratch_like(gr.m, gr.k);
+        emit_rmsnorm(em, cur, *gr.w1, t, gr.eps1, nullptr, nullptr);
+        cur = t;
+    }
+    if (gr.res) {
+        if (!gr.w2) throw std::runtime_error("MatMulNBits group: a residual add without the norm after it");
+        TRef t = scratch_like(gr.m, gr.k);
+        TRef res = *gr.res, sum = *gr.sum_out;
+        res.shape = sum.shape = {gr.m, gr.k};
+        emit_rmsnorm(em, cur, *gr.w2, t, gr.eps2, &res, &sum);
+        cur = t;
+    } else if (gr.w2) {
+        TRef t = scratch_like(gr.m, gr.k);
+        emit_rmsnorm(em, cur, *gr.w2, t, gr.eps2, nullptr, nullptr);
+        cur = t;
+    }
+    NBitsGroup g2 = gr;
+    g2.geglu = 0;
+    g2.w1 = g2.w2 = g2.res = g2.sum_out = nullptr;
+    if (gr.geglu) {
+        g2.y[0] = scratch_like(gr.m, gr.seg_n[0]);
+        g2.y[1] = scratch_like(gr.m, gr.seg_n[1]);
+    }
+    emit_nbits_gemm_tc(em, g2, cur, tiles, gr.geglu != 0);
+    if (gr.geglu) emit_gelu(em, g2.y[0], gr.y[0], gr.geglu == 1, &g2.y[1]);
+}
+
 void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TRef& tiles) {
     if (gr.m == 0) return;
+    static const int gemm_from = env_int("ONYXIA_GEMM_FROM_ROWS", 9, 1, 1 << 30);  // diagnostics: rows at which the GEMM takes over
+    if (gr.m >= gemm_from) {
+        emit_nbits_group_gemm(em, gr, a, tiles);
+        return;
+    }
     StreamP p{};
     p.m_total = gr.m;
     p.k = gr.k;

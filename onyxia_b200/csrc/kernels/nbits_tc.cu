@@ -1,0 +1,312 @@
+// MatMulNBits for more than 8 activation rows (prefill, batched decode): a
+// tcgen05 GEMM with the accumulator in tensor memory.
+//
+//   Yᵀ[n, m] = Σ_k W[n, k] · X[m, k],   W = round_f16((q − zp)·s) from the tile records
+//
+// The weights are the MMA's A operand (128 rows of W per CTA = 8 row tiles), the
+// activations its B operand (MB = 16 … 256 rows of X per pass), so the weight
+// stream is read once per MB activation rows. Per step of 128 k:
+//   * eight producer warps each widen one tile record (the streaming GEMV's
+//     nibble arithmetic, exact (q − zp)·s rounding) into the A panel in shared
+//     memory — K-major, 128-byte rows, 128-byte swizzle — and copy the matching
+//     activation columns into the B panel;
+//   * one thread of a ninth warp issues eight tcgen05.mma (M 128 × N MB × K 16,
+//     f16 inputs, f32 accumulation in TMEM) and commits them to the mbarrier that
+//     frees the stage.
+// Stages form a ring (full / empty mbarriers). After the last step the first four
+// warps read the accumulator with tcgen05.ld (a warp reads the 32 TMEM lanes of
+// its quarter), round to f16 and store Y, consecutive threads on consecutive n.
+//
+// Every wait is bounded; on expiry the kernel records ERR_WAIT_TIMEOUT, lets the
+// remaining phases run out and frees its tensor memory before it exits.
+//
+// FLOPs 2·M·N·K; bytes as for the GEMV (0.5625 per weight) once per MB rows.
+#include "common.cuh"
+#include "kernels.hpp"
+
+namespace oxk {
+
+namespace {
+
+constexpr int kProducerWarps = 8;
+constexpr int kThreadsTc = (kProducerWarps + 1) * 32;
+constexpr int kTileWt = 1024, kTileSt = 128, kTileZt = 64;
+constexpr int kPanelA = 128 * 128;  // bytes: 128 rows × 64 k of f16
+constexpr long long kWaitCyclesTc = 2000000000LL;
+
+struct TcP {
+    const __half* x;             // activations [M, K]
+    const unsigned char* tiles;  // tile records, row tile by row tile
+    __half* y[3];                // outputs per segment [M, seg_n]
+    ErrWord* err;
+    long long m0, m_total, k;
+    long long seg_n[3];
+    int seg_rt0[4];
+    int n_seg, interleave2;      // interleave2: row tiles alternate between segment 0 and 1
+    int k_tiles, row_tiles, mb, stages, tile_bytes, has_zp, node;
+};
+
+__device__ __forceinline__ unsigned s_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool bar_try_tc(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait_tc(unsigned bar, unsigned parity) {
+    if (bar_try_tc(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (clock64() - t0 < kWaitCyclesTc)
+        if (bar_try_tc(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ unsigned and_or_tc(unsigned a, unsigned b, unsigned c) {
+    unsigned d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned h2u_tc(__half2 h) { return *reinterpret_cast<unsigned*>(&h); }
+__device__ __forceinline__ __half2 u2h_tc(unsigned u) { return *reinterpret_cast<__half2*>(&u); }
+// One 32-bit word (8 interleaved nibbles) → 8 consecutive k as four f16 pairs.
+__device__ __forceinline__ uint4 widen_tc(unsigned w, __half2 sub_lo, __half2 add_hi, __half2 s2) {
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    const unsigned magic = 0x64006400u, m_lo = 0x000F000Fu, m_hi = 0x00F000F0u;
+    const unsigned lo = and_or_tc(w, m_lo, magic), hi = and_or_tc(w, m_hi, magic);
+    const unsigned w8 = w >> 8;
+    const unsigned lo2 = and_or_tc(w8, m_lo, magic), hi2 = and_or_tc(w8, m_hi, magic);
+    uint4 o;
+    o.x = h2u_tc(__hmul2(__hsub2(u2h_tc(lo), sub_lo), s2));
+    o.y = h2u_tc(__hmul2(__hfma2(u2h_tc(hi), sixteenth, add_hi), s2));
+    o.z = h2u_tc(__hmul2(__hsub2(u2h_tc(lo2), sub_lo), s2));
+    o.w = h2u_tc(__hmul2(__hfma2(u2h_tc(hi2), sixteenth, add_hi), s2));
+    return o;
+}
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1 024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc(unsigned smem_byte_addr) {
+    return (unsigned long long)((smem_byte_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // the swizzle pattern repeats every 1 024 bytes: panels start on that boundary
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int mb = p.mb, S = p.stages;
+    const int panel_b = mb * 128;                       // bytes of one 64-k activation panel
+    const int stage_bytes = 2 * kPanelA + 2 * panel_b;  // A panels, then B panels
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)S * stage_bytes);  // full[S], empty[S], done
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * S + 1);
+
+    pdl_enter();
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + S + s)) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + 2 * S)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    int tmem_cols = 32;
+    while (tmem_cols < mb) tmem_cols <<= 1;
+    if (warp == kProducerWarps) {  // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem = *tmem_slot;
+
+    const int rt0 = blockIdx.x * 8;  // first row tile of this CTA
+    const int steps = p.k_tiles;
+    bool ok = true;
+
+    if (warp < kProducerWarps) {
+        // ── producers: warp w widens row tile rt0 + w; all of them copy the activations ──
+        const int g = lane >> 2, t = lane & 3;
+        const int rt = rt0 + warp;
+        const bool rt_live = rt < p.row_tiles;
+        const unsigned char* rec = p.tiles + (size_t)(rt_live ? rt : 0) * p.k_tiles * p.tile_bytes;
+        const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+        for (int i = 0; i < steps; i++) {
+            const int s = i % S;
+            if (i >= S && ok && !bar_wait_tc(s_addr(bars + S + s), ((i / S) - 1) & 1)) ok = false;
+            unsigned char* stage = smem + (size_t)s * stage_bytes;
+            // A: rows 16·warp + g and + 8, k = 32·t + 8·m … + 8 of this 128-k step
+            uint4 wl = make_uint4(0, 0, 0, 0), wh = wl;
+            __half2 s2 = __float2half2_rn(0.f);
+            float zl = 8.f, zh = 8.f;
+            if (rt_live) {
+                const unsigned char* r = rec + (size_t)i * p.tile_bytes;
+                wl = __ldg(reinterpret_cast<const uint4*>(r) + lane);
+                wh = __ldg(reinterpret_cast<const uint4*>(r) + 32 + lane);
+                s2 = *reinterpret_cast<const __half2*>(r + kTileWt + lane * 4);
+                if (p.has_zp) {
+                    const uchar2 z = *reinterpret_cast<const uchar2*>(r + kTileWt + kTileSt + lane * 2);
+                    zl = (float)z.x;
+                    zh = (float)z.y;
+                }
+            }
+            const __half2 s2l = __low2half2(s2), s2h = __high2half2(s2);
+            const __half2 subl = __float2half2_rn(1024.f + zl), subh = __float2half2_rn(1024.f + zh);
+            const __half2 addl = __float2half2_rn(-64.f - zl), addh = __float2half2_rn(-64.f - zh);
+            const unsigned wls[4] = {wl.x, wl.y, wl.z, wl.w}, whs[4] = {wh.x, wh.y, wh.z, wh.w};
+            const int row_l = warp * 16 + g, row_h = row_l + 8;
+            unsigned char* panel = stage + (t >> 1) * kPanelA;  // blocks 0,1 → first 64 k; 2,3 → second
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const int chunk = (t & 1) * 4 + m;  // 16-byte chunk of the 128-byte row
+                *reinterpret_cast<uint4*>(panel + row_l * 128 + ((chunk ^ (row_l & 7)) << 4)) = widen_tc(wls[m], subl, addl, s2l);
+                *reinterpret_cast<uint4*>(panel + row_h * 128 + ((chunk ^ (row_h & 7)) << 4)) = widen_tc(whs[m], subh, addh, s2h);
+            }
+            // B: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels
+            unsigned char* bpan = stage + 2 * kPanelA;
+            for (int c = tid; c < mb * 16; c += kProducerWarps * 32) {
+                const int r = c >> 4, ch = c & 15;  // row, 16-byte chunk of the 256 bytes of this step
+                const long long row = p.m0 + r, k0 = (long long)i * 128 + ch * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row < p.m_total) {
+                    const __half* src = p.x + row * p.k + k0;
+                    if (vec && k0 + 8 <= p.k) {
+                        v = *reinterpret_cast<const uint4*>(src);
+                    } else {
+                        __half tmp[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) tmp[e] = k0 + e < p.k ? src[e] : __float2half(0.f);
+                        v = *reinterpret_cast<uint4*>(tmp);
+                    }
+                }
+                *reinterpret_cast<uint4*>(bpan + (ch >> 3) * panel_b + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the stores visible to the tensor core
+            __syncwarp();
+            if (lane == 0) bar_arrive(s_addr(bars + s));
+        }
+    } else {
+        // ── MMA issuer ──
+        const unsigned idesc = (1u << 4) | ((unsigned)(mb >> 3) << 17) | (8u << 24);  // f16 × f16 → f32, K-major, N = mb, M = 128
+        for (int i = 0; i < steps; i++) {
+            const int s = i % S;
+            if (ok && !bar_wait_tc(s_addr(bars + s), (i / S) & 1)) ok = false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+                const unsigned a0 = s_addr(smem + (size_t)s * stage_bytes), b0 = a0 + 2 * kPanelA;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const unsigned long long da = umma_desc(a0 + (j >> 2) * kPanelA + (j & 3) * 32);
+                    const unsigned long long db = umma_desc(b0 + (j >> 2) * panel_b + (j & 3) * 32);
+                    const unsigned accumulate = (i > 0 || j > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem),
+                        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+                        : "memory");
+                }
+                // the stage is free once these MMAs have read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bars + S + s)) : "memory");
+                if (i == steps - 1)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bars + 2 * S)) : "memory");
+            }
+            __syncwarp();
+        }
+    }
+
+    // ── epilogue: warps 0-3 read their quarter of the 128 accumulator lanes ──
+    if (warp < 4) {
+        if (ok && steps > 0 && !bar_wait_tc(s_addr(bars + 2 * S), 0)) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int row_in_cta = warp * 32 + lane;           // weight row = accumulator lane
+        const int rtg = rt0 + (row_in_cta >> 4);
+        int seg = 0;
+        long long row;
+        if (p.interleave2) {
+            seg = rtg & 1;
+            row = (long long)(rtg >> 1) * 16 + (row_in_cta & 15);
+        } else {
+            if (p.n_seg > 1 && rtg >= p.seg_rt0[1]) seg = 1;
+            if (p.n_seg > 2 && rtg >= p.seg_rt0[2]) seg = 2;
+            row = (long long)(rtg - p.seg_rt0[seg]) * 16 + (row_in_cta & 15);
+        }
+        const bool row_ok = rtg < p.row_tiles && row < p.seg_n[seg];
+        __half* yout = p.y[seg];
+        for (int c0 = 0; c0 < mb; c0 += 16) {
+            unsigned v[16];
+            const unsigned addr = tmem + ((unsigned)(warp * 32) << 16) + (unsigned)c0;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                  "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                : "r"(addr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const long long mrow = p.m0 + c0 + j;
+                if (ok && row_ok && mrow < p.m_total) yout[mrow * p.seg_n[seg] + row] = __float2half_rn(__uint_as_float(v[j]));
+            }
+        }
+    }
+    if (!ok && lane == 0) report(p.err, ERR_WAIT_TIMEOUT, p.node, (long long)blockIdx.x, (long long)warp);
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kProducerWarps)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+}  // namespace
+
+// The GEMM form of a MatMulNBits group (no prologue, no epilogue: the caller runs those as
+// separate launches). `interleave2`: the stream alternates row tiles of segment 0 and 1.
+void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const TRef& tiles, bool interleave2) {
+    if (gr.m == 0) return;
+    TcP p{};
+    p.m_total = gr.m;
+    p.k = gr.k;
+    p.k_tiles = (int)(((gr.k + 31) / 32 + 3) / 4);
+    p.n_seg = gr.n_seg;
+    p.interleave2 = interleave2 ? 1 : 0;
+    int rt = 0;
+    for (int i = 0; i < gr.n_seg; i++) {
+        p.seg_n[i] = gr.seg_n[i];
+        p.seg_rt0[i] = rt;
+        rt += (int)((gr.seg_n[i] + 15) / 16);
+    }
+    p.seg_rt0[gr.n_seg] = rt;
+    p.row_tiles = rt;
+    p.has_zp = gr.has_zp ? 1 : 0;
+    p.tile_bytes = kTileWt + kTileSt + (gr.has_zp ? kTileZt : 0);
+    p.node = em.node;
+    // activation rows per pass: the smallest MMA N that holds them all, at most 256
+    int mb = 16;
+    while (mb < gr.m && mb < 256) mb <<= 1;
+    p.mb = mb;
+    const size_t stage = 2 * (size_t)kPanelA + 2 * (size_t)mb * 128;
+    p.stages = stage * 3 + 2048 <= 200 * 1024 ? 3 : 2;
+    const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute((const void*)nbits_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const Buf null{kSlotNull, 0};
+    const unsigned grid = (unsigned)((p.row_tiles + 7) / 8);
+    for (long long m0 = 0; m0 < gr.m; m0 += mb) {
+        p.m0 = m0;
+        em.launch(nbits_gemm_tc, dim3(grid), dim3(kThreadsTc), (unsigned)smem, p,
+                  {{&p.x, x.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.y[0], gr.y[0].buf},
+                   {&p.y[1], gr.n_seg > 1 ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
+                  "nbits_gemm_tc", /*pdl=*/true);
+    }
+}
+
+}  // namespace oxk
