@@ -94,7 +94,7 @@ __device__ __forceinline__ unsigned long long umma_desc(unsigned smem_byte_addr)
     return (unsigned long long)((smem_byte_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
+__global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle pattern repeats every 1 024 bytes: panels start on that boundary
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -109,7 +109,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
 
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps) : "memory");
+            // a stage is full when every producer warp has arrived and every producer thread's
+            // asynchronous activation copies have landed
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps + kProducerWarps * 32) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + S + s)) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + 2 * S)) : "memory");
@@ -137,29 +139,60 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
         const bool rt_live = rt < p.row_tiles;
         const unsigned char* rec = p.tiles + (size_t)(rt_live ? rt : 0) * p.k_tiles * p.tile_bytes;
         const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+        // this warp's record of a step: two 16-byte words of nibbles per lane, the two rows' scales (and zero points)
+        struct Rec {
+            uint4 wl, wh;
+            __half2 s2;
+            uchar2 z;
+        };
+        auto fetch = [&](int i) {
+            Rec r;
+            r.wl = make_uint4(0, 0, 0, 0);
+            r.wh = r.wl;
+            r.s2 = __float2half2_rn(0.f);
+            r.z = make_uchar2(8, 8);
+            if (rt_live && i < steps) {
+                const unsigned char* q = rec + (size_t)i * p.tile_bytes;
+                r.wl = __ldg(reinterpret_cast<const uint4*>(q) + lane);
+                r.wh = __ldg(reinterpret_cast<const uint4*>(q) + 32 + lane);
+                r.s2 = *reinterpret_cast<const __half2*>(q + kTileWt + lane * 4);
+                if (p.has_zp) r.z = *reinterpret_cast<const uchar2*>(q + kTileWt + kTileSt + lane * 2);
+            }
+            return r;
+        };
+        Rec next = fetch(0);
         for (int i = 0; i < steps; i++) {
             const int s = i % S;
             if (i >= S && ok && !bar_wait_tc(s_addr(bars + S + s), ((i / S) - 1) & 1)) ok = false;
             unsigned char* stage = smem + (size_t)s * stage_bytes;
-            // A: rows 16·warp + g and + 8, k = 32·t + 8·m … + 8 of this 128-k step
-            uint4 wl = make_uint4(0, 0, 0, 0), wh = wl;
-            __half2 s2 = __float2half2_rn(0.f);
-            float zl = 8.f, zh = 8.f;
-            if (rt_live) {
-                const unsigned char* r = rec + (size_t)i * p.tile_bytes;
-                wl = __ldg(reinterpret_cast<const uint4*>(r) + lane);
-                wh = __ldg(reinterpret_cast<const uint4*>(r) + 32 + lane);
-                s2 = *reinterpret_cast<const __half2*>(r + kTileWt + lane * 4);
-                if (p.has_zp) {
-                    const uchar2 z = *reinterpret_cast<const uchar2*>(r + kTileWt + kTileSt + lane * 2);
-                    zl = (float)z.x;
-                    zh = (float)z.y;
+            // B: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels; 16-byte
+            // asynchronous copies straight into the swizzled rows (zero-filled beyond the matrix)
+            unsigned char* bpan = stage + 2 * kPanelA;
+            for (int c = tid; c < mb * 16; c += kProducerWarps * 32) {
+                const int r = c >> 4, ch = c & 15;  // row, 16-byte chunk of the 256 bytes of this step
+                const long long row = p.m0 + r, k0 = (long long)i * 128 + ch * 8;
+                unsigned char* dst = bpan + (ch >> 3) * panel_b + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+                if (vec) {
+                    const bool in = row < p.m_total && k0 < p.k;
+                    const __half* src = p.x + (in ? row * p.k + k0 : 0);
+                    const unsigned bytes = in ? 16u : 0u;  // K is a multiple of 8 here: a chunk is whole or absent
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s_addr(dst)), "l"(src), "r"(bytes) : "memory");
+                } else {
+                    __half tmp[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
+                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(tmp);
                 }
             }
-            const __half2 s2l = __low2half2(s2), s2h = __high2half2(s2);
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s_addr(bars + s)) : "memory");
+            // A: rows 16·warp + g and + 8, k = 32·t + 8·m … + 8 of this 128-k step; the next record is already on its way
+            const Rec cur = next;
+            next = fetch(i + 1);
+            const __half2 s2l = __low2half2(cur.s2), s2h = __high2half2(cur.s2);
+            const float zl = (float)cur.z.x, zh = (float)cur.z.y;
             const __half2 subl = __float2half2_rn(1024.f + zl), subh = __float2half2_rn(1024.f + zh);
             const __half2 addl = __float2half2_rn(-64.f - zl), addh = __float2half2_rn(-64.f - zh);
-            const unsigned wls[4] = {wl.x, wl.y, wl.z, wl.w}, whs[4] = {wh.x, wh.y, wh.z, wh.w};
+            const unsigned wls[4] = {cur.wl.x, cur.wl.y, cur.wl.z, cur.wl.w}, whs[4] = {cur.wh.x, cur.wh.y, cur.wh.z, cur.wh.w};
             const int row_l = warp * 16 + g, row_h = row_l + 8;
             unsigned char* panel = stage + (t >> 1) * kPanelA;  // blocks 0,1 → first 64 k; 2,3 → second
 #pragma unroll
@@ -167,25 +200,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
                 const int chunk = (t & 1) * 4 + m;  // 16-byte chunk of the 128-byte row
                 *reinterpret_cast<uint4*>(panel + row_l * 128 + ((chunk ^ (row_l & 7)) << 4)) = widen_tc(wls[m], subl, addl, s2l);
                 *reinterpret_cast<uint4*>(panel + row_h * 128 + ((chunk ^ (row_h & 7)) << 4)) = widen_tc(whs[m], subh, addh, s2h);
-            }
-            // B: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels
-            unsigned char* bpan = stage + 2 * kPanelA;
-            for (int c = tid; c < mb * 16; c += kProducerWarps * 32) {
-                const int r = c >> 4, ch = c & 15;  // row, 16-byte chunk of the 256 bytes of this step
-                const long long row = p.m0 + r, k0 = (long long)i * 128 + ch * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (row < p.m_total) {
-                    const __half* src = p.x + row * p.k + k0;
-                    if (vec && k0 + 8 <= p.k) {
-                        v = *reinterpret_cast<const uint4*>(src);
-                    } else {
-                        __half tmp[8];
-#pragma unroll
-                        for (int e = 0; e < 8; e++) tmp[e] = k0 + e < p.k ? src[e] : __float2half(0.f);
-                        v = *reinterpret_cast<uint4*>(tmp);
-                    }
-                }
-                *reinterpret_cast<uint4*>(bpan + (ch >> 3) * panel_b + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = v;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the stores visible to the tensor core
             __syncwarp();
@@ -197,6 +211,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
         for (int i = 0; i < steps; i++) {
             const int s = i % S;
             if (ok && !bar_wait_tc(s_addr(bars + s), (i / S) & 1)) ok = false;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the asynchronous copies landed through the generic proxy
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
                 const unsigned a0 = s_addr(smem + (size_t)s * stage_bytes), b0 = a0 + 2 * kPanelA;
@@ -290,7 +305,8 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     while (mb < gr.m && mb < 256) mb <<= 1;
     p.mb = mb;
     const size_t stage = 2 * (size_t)kPanelA + 2 * (size_t)mb * 128;
-    p.stages = stage * 3 + 2048 <= 200 * 1024 ? 3 : 2;
+    // two CTAs per SM where two stages of each fit (more producer warps to hide latencies), else one CTA with what fits
+    p.stages = stage * 2 + 2048 <= 110 * 1024 ? 2 : (stage * 3 + 2048 <= 200 * 1024 ? 3 : 2);
     const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
     static bool attr_set = false;
     if (!attr_set) {
