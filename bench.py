@@ -176,6 +176,81 @@ def gemv_sweep(backend, shapes, ms, peak, reps=10):
     return out
 
 
+def bench_c5(args, rank, local_rank, world):
+    """Batched decode of the 27B architecture (config C5: 64 sequences at a 2048-token context), tensor-parallel
+    over the launched ranks. Depth and vocabulary can be reduced (--layers, --vocab) to keep the run short; the
+    line reports the measured per-layer time and its extrapolation to the full 62 layers."""
+    import torch.distributed as dist
+    from onyxia_b200 import backend as be
+    from onyxia_b200 import ir, models
+    from onyxia_b200.ir import HostTensor
+    if world > 1:
+        dist.init_process_group("gloo")
+    cfg = models.config_gemma3_27b()
+    full_layers = cfg.layers
+    cfg.layers = args.layers
+    cfg.vocab = args.vocab
+    module = models.build_decoder(cfg, seed=0)
+    stats = module.tp_stats(world) if world > 1 else (0, 0, 0)
+    backend = be.CudaBackend((local_rank,))
+    if world > 1:
+        backend.join_tp_torch()
+        module = module.tp_partition(world, rank)
+    sess = backend.prepare(module)
+    B, ctx = args.batch, args.context
+    kvh = cfg.kv_heads // world if world > 1 and stats[2] else cfg.kv_heads
+    rng = np.random.default_rng(1)
+    block = HostTensor.from_numpy(rng.standard_normal((B, kvh, ctx - 1, cfg.head_dim)).astype(np.float16))
+    kv = {}
+    for l in range(cfg.layers):
+        for part in ("key", "value"):
+            kv[f"past_key_values.{l}.{part}"] = sess.upload(block)
+    del block
+    ids = sess.upload(HostTensor.from_numpy(rng.integers(0, cfg.vocab, (B, 1)).astype(np.int64)))
+    K, W = args.steps, args.warmup
+    masks = [sess.upload(HostTensor.from_numpy(np.ones((B, ctx + i), np.int64))) for i in range(W + K)]
+
+    def step(i):
+        feed = [("input_ids", ids), ("attention_mask", masks[i])] + list(kv.items())
+        outs = dict(sess.run(feed))
+        for l in range(cfg.layers):
+            for part in ("key", "value"):
+                kv[f"past_key_values.{l}.{part}"] = outs[f"present.{l}.{part}"]
+        return outs["logits"]
+
+    for i in range(W):
+        step(i)
+    sess.wait_idle()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    sess.timer_start()
+    for i in range(W, W + K):
+        step(i)
+    ms = sess.timer_stop()
+    clocks = sampler.stop()
+    if world > 1:
+        box = [None] * world
+        dist.all_gather_object(box, ms)
+        ms = max(box)
+    per_layer_ms = ms / K / cfg.layers  # includes the (small) embedding / lm_head share
+    peak, peak_kind = load_peaks()
+    weight_bytes_layer = cfg.weight_bytes_per_token() / max(cfg.layers, 1) if hasattr(cfg, "weight_bytes_per_token") else None
+    if rank == 0:
+        print(json.dumps({
+            "metric": "batched decode tok/s (Gemma-3-27B-arch int4, 64 sequences, 2048-token context)", "unit": "tok/s",
+            "value": B * K / (ms / 1e3), "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"gemma3-27b-arch int4 block-32, batch {B}, context {ctx}, tensor parallel over {world} GPU(s)",
+                       "layers_run": cfg.layers, "layers_full": full_layers, "vocab_run": cfg.vocab, "tp_split": list(stats)},
+            "ms_per_layer": per_layer_ms, "extrapolated_full_depth_tok_s": B / (per_layer_ms * full_layers / 1e3),
+            "clocks": clocks, "gpu_launches": sess.launch_count(), "peak_gbs": peak, "peak_source": peak_kind}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +260,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gemv-sweep", action="store_true",
                     help="only run the int4 GEMV sweep over the C2 shapes (or --shapes KxN,... and --ms 1,8) and print it")
+    ap.add_argument("--config", default="c4", help="c4: the 1B decode bench (default); c5: 27B-architecture batched decode, tensor-parallel over the ranks")
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--vocab", type=int, default=32768)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--shapes", default="")
     ap.add_argument("--ms", default="1,8")
     ap.add_argument("--profiler-range", action="store_true",
@@ -216,6 +296,10 @@ def main():
                                  "sample": f"{steps} decode steps after a 4-token prompt"},
                 "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
+        return
+
+    if args.config == "c5":
+        bench_c5(args, rank, local_rank, world)
         return
 
     if args.gemv_sweep:

@@ -408,45 +408,37 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
     float* xpart = reinterpret_cast<float*>(xsum + 8 * GT);                 // [8 ranks][GT][slice] partial outputs of this CTA's slice
 
     ox_trace(p.err, 11);
-    pdl_enter();
-    ox_trace(p.err, 12);
+    pdl_trigger();
 
     const long long b = blockIdx.z;
     const long long kvh = blockIdx.y / p.groups, gc = blockIdx.y % p.groups;
     const long long G = p.H / p.KV, h0 = kvh * G + gc * GT;
     const int live = (int)(G - gc * GT < GT ? G - gc * GT : GT);
-    const long long T = *p.dyn_t;
-    const long long tot = (long long)p.seqlens[b] + 1, qpos = tot - 1 > 0 ? tot - 1 : 0;
-    const long long hi = qpos < T - 1 ? qpos : T - 1;
-    const long long lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;
-    const int n = (int)(hi >= lo ? hi - lo + 1 : 0);
-    const int chunk = (n + CX - 1) / CX;
-    const long long my_lo = lo + (long long)rank * chunk;
-    int my_n = n - rank * chunk;
-    my_n = my_n < 0 ? 0 : (my_n > chunk ? chunk : my_n);
-    if (my_n > p.chunk_max) {
-        if (tid == 0) report(p.err, ERR_SLICE_OOB, p.node, my_n, p.chunk_max);
-        my_n = p.chunk_max;
-    }
-    const int n_blocks = (my_n + kKeyBlock - 1) / kKeyBlock;
     const long long head_base = (b * p.KV + kvh) * p.cap * D;
     __half* ck = reinterpret_cast<__half*>(p.cache_k) + head_base;
     __half* cv = reinterpret_cast<__half*>(p.cache_v) + head_base;
-    const bool owns_new = qpos <= T - 1 && n > 0 && (int)((hi - lo) / chunk) == rank;
-
-    long long rope_row = qpos;
-    if (p.half && rope_row >= p.cache_rows) {
-        if (tid == 0 && rank == 0) report(p.err, ERR_GATHER_OOB, p.node, rope_row, p.cache_rows);
-        rope_row = 0;
-    }
-    auto rope = [&](const void* x, long long base, int e) -> float {
-        if (e >= 2 * p.half) return ld<DT>(x, base + e);
-        const bool first = e < p.half;
-        const long long j = first ? e : e - p.half;
-        const float c = ld<DT>(p.cos, rope_row * p.half + j), s = ld<DT>(p.sin, rope_row * p.half + j);
-        const float x1 = ld<DT>(x, base + j), x2 = ld<DT>(x, base + j + p.half);
-        return first ? rndf<DT>(x1 * c) - rndf<DT>(x2 * s) : rndf<DT>(x2 * c) + rndf<DT>(x1 * s);
+    // The present length comes with the launch (written before the graph started), so the key range can
+    // be guessed — newest key at T − 1, the dense case — and the fetch of the old cache rows, which no
+    // kernel of this step writes, started before the wait for the predecessor. The per-row length
+    // (seqlens, produced inside this step) is checked after the wait; a ragged row fetches again.
+    const long long T = *p.dyn_t;
+    long long qpos, lo, my_lo;
+    int n, chunk, my_n, n_blocks;
+    bool owns_new;
+    auto set_range = [&](long long q) {
+        qpos = q;
+        const long long hi = qpos < T - 1 ? qpos : T - 1;
+        lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;
+        n = (int)(hi >= lo ? hi - lo + 1 : 0);
+        chunk = (n + CX - 1) / CX;
+        my_lo = lo + (long long)rank * chunk;
+        my_n = n - rank * chunk;
+        my_n = my_n < 0 ? 0 : (my_n > chunk ? chunk : my_n);
+        if (my_n > p.chunk_max) my_n = p.chunk_max;  // cannot happen for a launch sized by the host; never index past the rows
+        n_blocks = (my_n + kKeyBlock - 1) / kKeyBlock;
+        owns_new = qpos <= T - 1 && n > 0 && (int)((hi - lo) / chunk) == rank;
     };
+    set_range(T - 1 > 0 ? T - 1 : 0);
 
     // Block i of 2·n_blocks (K blocks, then V blocks) → ring slot i % kRing, as 16-byte asynchronous
     // copies into padded rows; every thread commits one group per block (empty beyond the last block).
@@ -471,6 +463,22 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_de
     };
     for (int i = 0; i < kRing; i++) fetch(i);
     ox_trace(p.err, 13);
+    pdl_wait();
+    ox_trace(p.err, 12);
+    {
+        const long long tot = (long long)p.seqlens[b] + 1, q = tot - 1 > 0 ? tot - 1 : 0;
+        if (q != qpos) {  // a row shorter than the batch's longest: drop what was fetched for the guess
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            set_range(q);
+            for (int i = 0; i < kRing; i++) fetch(i);
+        }
+    }
+    long long rope_row = qpos;
+    if (p.half && rope_row >= p.cache_rows) {
+        if (tid == 0 && rank == 0) report(p.err, ERR_GATHER_OOB, p.node, rope_row, p.cache_rows);
+        rope_row = 0;
+    }
 
     // 1. rotated q for the heads of the group (zero rows up to 8), the new k / v rows, zeroed padding.
     // Thread e owns element e of every row, so all its loads are independent and issued together.
