@@ -1,0 +1,38 @@
+"""MatMulNBits with more than 8 activation rows runs as a tcgen05 GEMM (accumulator in tensor memory):
+the sweep shapes of the MatMulNBits op benchmark at reduced sizes, against the CPU oracle, which
+evaluates the Dequantize + MatMul decomposition (crates/onyxia-ir/src/decomp.rs:615-663)."""
+import numpy as np
+import pytest
+
+from onyxia_b200 import backend as be
+from onyxia_b200 import ir, models
+from oracle import ref
+
+from gpu_util import cuda_backend
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,k,n,zp", [(16, 128, 128, False), (9, 256, 48, False), (64, 512, 256, False), (24, 1152, 1024, True),
+                                      (100, 1152, 1024, False), (300, 2048, 2048, False), (512, 1024, 272, False),
+                                      (64, 96, 40, True)])
+def test_matmul_nbits_many_rows_matches_oracle(m, k, n, zp):
+    module, act = models.build_matmul_nbits(m, k, n, act_dtype=ir.F16, seed=m + k, with_zp=zp)
+    ref.set_threads(8)
+    want = ref.run_once(module.clone(), {"a": act})[0][1].numpy().astype(np.float32)
+    got = be.run_once(cuda_backend(), module.clone(), {"a": act})[0][1].numpy().astype(np.float32)
+    # f32 accumulation against the oracle's f64, both rounded to f16 once: one f16 ulp of the largest output
+    bound = 2e-3 + 2.0 ** -10 * np.abs(want).max()
+    assert np.abs(got - want).max() <= bound, (float(np.abs(got - want).max()), float(bound))
+
+
+def test_rows_do_not_depend_on_the_pass_they_ran_in():
+    """The same activation row gives the same result whether it runs in the GEMV (≤ 8 rows) or the GEMM."""
+    k, n = 1152, 1024
+    module, act = models.build_matmul_nbits(40, k, n, act_dtype=ir.F16, seed=3)
+    big = be.run_once(cuda_backend(), module.clone(), {"a": act})[0][1].numpy().astype(np.float32)
+    small_mod, _ = models.build_matmul_nbits(4, k, n, act_dtype=ir.F16, seed=3)
+    a4 = ir.HostTensor.from_numpy(act.numpy()[:4].copy())
+    small = be.run_once(cuda_backend(), small_mod, {"a": a4})[0][1].numpy().astype(np.float32)
+    # f32 (tensor memory) vs f64 (GEMV) accumulation: at most one f16 ulp apart
+    assert np.abs(big[:4] - small).max() <= 2.0 ** -10 * np.abs(small).max() + 1e-3
