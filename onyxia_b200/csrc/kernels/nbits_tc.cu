@@ -167,21 +167,32 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
             unsigned char* stage = smem + (size_t)s * stage_bytes;
             // B: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels; 16-byte
             // asynchronous copies straight into the swizzled rows (zero-filled beyond the matrix)
+            // Thread tid copies chunk `tid & 15` of rows (tid >> 4) + 16·j: the swizzle term (row & 7) is the
+            // same for all of them, so source and destination advance by constant strides.
             unsigned char* bpan = stage + 2 * kPanelA;
-            for (int c = tid; c < mb * 16; c += kProducerWarps * 32) {
-                const int r = c >> 4, ch = c & 15;  // row, 16-byte chunk of the 256 bytes of this step
-                const long long row = p.m0 + r, k0 = (long long)i * 128 + ch * 8;
-                unsigned char* dst = bpan + (ch >> 3) * panel_b + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+            {
+                const int ch = tid & 15, r0 = tid >> 4;
+                const long long k0 = (long long)i * 128 + ch * 8;
+                const unsigned dst0 = s_addr(bpan + (ch >> 3) * panel_b + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4));
                 if (vec) {
-                    const bool in = row < p.m_total && k0 < p.k;
-                    const __half* src = p.x + (in ? row * p.k + k0 : 0);
-                    const unsigned bytes = in ? 16u : 0u;  // K is a multiple of 8 here: a chunk is whole or absent
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s_addr(dst)), "l"(src), "r"(bytes) : "memory");
+                    const bool k_in = k0 < p.k;  // K is a multiple of 8 here: a chunk is whole or absent
+                    const __half* src0 = p.x + (p.m0 + r0) * p.k + k0;
+                    for (int j = 0; j * 16 < mb; j++) {
+                        const bool in = k_in && p.m0 + r0 + 16 * j < p.m_total;
+                        const __half* src = in ? src0 + (long long)j * 16 * p.k : p.x;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + j * 2048), "l"(src), "r"(in ? 16u : 0u) : "memory");
+                    }
                 } else {
-                    __half tmp[8];
+                    for (int j = 0; j * 16 < mb; j++) {
+                        const long long row = p.m0 + r0 + 16 * j;
+                        __half tmp[8];
 #pragma unroll
-                    for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
-                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(tmp);
+                        for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 2048), "r"(reinterpret_cast<unsigned*>(tmp)[0]),
+                                     "r"(reinterpret_cast<unsigned*>(tmp)[1]), "r"(reinterpret_cast<unsigned*>(tmp)[2]),
+                                     "r"(reinterpret_cast<unsigned*>(tmp)[3])
+                                     : "memory");
+                    }
                 }
             }
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s_addr(bars + s)) : "memory");
