@@ -295,6 +295,22 @@ ox_status ox_session_argmax_last(ox_session*, const ox_tensor* logits, ox_tensor
  *     by the caller. Calls on one session are ordered by its stream. */
 ox_status ox_session_argmax_last_into(ox_session*, const ox_tensor* logits, ox_tensor* out);
 
+/* The KV-cache generation loop as one call per step ≙ LlmSession (crates/onyxia-cli/src/llm.rs:26-246):
+ * `present.N.*` outputs are fed back as `past_key_values.N.*` inputs, the cache starts empty, masks are
+ * all ones, `position_ids` (if the module has them) continue from the current length. `ox_llm_step` runs
+ * `n_ids` new tokens (a prompt, or one token); with `token_out` the greedy choice (highest logit of the last
+ * position, last index among equals ≙ sampling.rs:71-80) is made on the device and 8 bytes come back; with
+ * `logits_out` the last position's logits are copied out in their stored dtype. The session is borrowed and
+ * must outlive the loop object; one thread at a time. */
+typedef struct ox_llm ox_llm;
+ox_status ox_llm_create(ox_session*, int64_t max_seq_len, ox_llm** out);
+void ox_llm_free(ox_llm*);
+int64_t ox_llm_sequence_length(const ox_llm*);
+int32_t ox_llm_logits_dtype(const ox_llm*); /* ox_dtype code of the logits `ox_llm_step` copies out */
+void ox_llm_reset(ox_llm*);
+ox_status ox_llm_step(ox_llm*, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
+                      size_t* logits_written);
+
 #ifdef __cplusplus
 }
 #endif

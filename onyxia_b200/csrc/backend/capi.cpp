@@ -6,16 +6,7 @@
 
 using namespace ox;
 
-struct ox_backend {
-    std::unique_ptr<oxrt::Backend> b;
-};
-struct ox_session {
-    std::unique_ptr<oxrt::Session> s;
-    std::vector<oxrt::Timing> taken;  // keeps strings alive for take_timings
-};
-struct ox_tensor {
-    oxrt::DTensor t;
-};
+#include "capi_types.hpp"
 
 #define OX_TRY try {
 #define OX_CATCH                                                                          \

@@ -123,3 +123,48 @@ def sample_greedy(logits: np.ndarray) -> int:
     if logits.size == 0:
         raise ValueError("Cannot sample_greedy from empty logits")
     return int(logits.size - 1 - np.argmax(logits[::-1]))
+
+
+class NativeLlmSession:
+    """The same loop run natively by the CUDA library (`ox_llm_*`): one call per step, greedy choice
+    on the device. Use it where the per-step host overhead matters; `LlmSession` stays the generic form
+    that also drives the CPU oracle."""
+
+    def __init__(self, backend, module: Module, max_seq_len: int):
+        import ctypes as C
+        from . import _ffi
+        self._C, self._lib = C, _ffi.cuda_lib()
+        self.session = backend.prepare(module)
+        h = C.c_void_p()
+        _ffi.check(self._lib.ox_llm_create(self.session._h, max_seq_len, C.byref(h)))
+        self._h = h
+
+    def step_greedy(self, ids) -> int:
+        C = self._C
+        from . import _ffi
+        arr = (C.c_int64 * len(ids))(*ids)
+        tok = C.c_int64()
+        _ffi.check(self._lib.ox_llm_step(self._h, arr, len(ids), C.byref(tok), None, 0, None))
+        return tok.value
+
+    def step_logits(self, ids) -> np.ndarray:
+        C = self._C
+        from . import _ffi
+        arr = (C.c_int64 * len(ids))(*ids)
+        buf = np.empty(1 << 20, dtype=np.uint8)
+        written = C.c_size_t()
+        _ffi.check(self._lib.ox_llm_step(self._h, arr, len(ids), None, buf.ctypes.data_as(C.c_void_p), buf.size, C.byref(written)))
+        raw = buf[:written.value]
+        np_dt = np.float16 if self._lib.ox_llm_logits_dtype(self._h) == ir.F16 else np.float32
+        return raw.view(np_dt).astype(np.float32)
+
+    def sequence_length(self) -> int:
+        return self._lib.ox_llm_sequence_length(self._h)
+
+    def reset(self) -> None:
+        self._lib.ox_llm_reset(self._h)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.ox_llm_free(self._h)
+            self._h = None

@@ -134,3 +134,23 @@ def test_tensor_parallel_two_gpus_match_one():
                        env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-4000:]
     assert "max abs diff vs one GPU" in r.stdout
+
+
+def test_native_generation_loop_matches_the_python_loop():
+    """`ox_llm_step` (the loop inside the library) and `LlmSession` produce the same greedy tokens and logits."""
+    cfg = models.config_c1()
+    cfg.vocab = 4096
+    module = models.build_decoder(cfg, seed=9)
+    prompt = np.random.default_rng(4).integers(0, cfg.vocab, 12).tolist()
+    py = llm.LlmSession(cuda_backend(), module.clone(), 128)
+    nat = llm.NativeLlmSession(cuda_backend(), module.clone(), 128)
+    t_py, t_nat = py.step_greedy(prompt, list(range(len(prompt)))), nat.step_greedy(prompt)
+    assert t_py == t_nat
+    for _ in range(6):
+        t_py, t_nat = py.step_greedy([t_py], [py.sequence_length()]), nat.step_greedy([t_nat])
+        assert t_py == t_nat
+    assert nat.sequence_length() == py.sequence_length()
+    a, b = py.decode(t_py), nat.step_logits([t_nat])
+    assert np.array_equal(a, b)
+    with pytest.raises(Exception):
+        llm.NativeLlmSession(cuda_backend(), module.clone(), 4).step_greedy(prompt)
