@@ -432,7 +432,9 @@ def main():
     act_bytes = 2 * (cfg.layers * (cfg.hidden * 4 + cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim +
                                    3 * cfg.ffn + cfg.hidden * 2) + cfg.hidden + cfg.vocab)
     alg_bytes_per_step = weight_bytes + act_bytes
-    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+    # DRAM bytes per launch of the dominant kernel from the committed ncu capture of this command
+    # (profiles/decode_step_gemma3_1b_launch_list.md: 210 launches read 1 139.5 MB and wrote 0.83 MB)
+    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": 5430145,
                 "kernel": gemv_name, "peak_source": peak_kind}
     if gemv[0]:
         gemv_s_per_step = gemv[1] / 1e9 / prof_steps

@@ -726,9 +726,14 @@ bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf 
         fn = gqa_decode_h<DPL, GT>;
     }
     if (smem > 200 * 1024) return false;
-    if (smem > 48 * 1024) {
+    // once per kernel instantiation (and per device the process uses): this runs on every re-lowering of a decode step
+    static int attr_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && attr_device != dev) {
         cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+        attr_device = dev;
     }
     GqaDecP p = p0;
     em.launch(fn, grid, dim3(kThreads), (unsigned)smem, p,
