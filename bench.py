@@ -176,6 +176,75 @@ def gemv_sweep(backend, shapes, ms, peak, reps=10):
     return out
 
 
+def gqa_sweep(backend, peak, batches=(1, 16, 64), pasts=(512, 4096, 32768), windows=(-1, 1024), steps=12):
+    """GroupQueryAttention decode op (config C3): 32 query / 8 KV heads of 128, one new token per sequence
+    over an f16 cache that is appended in place; GB/s of the K/V bytes a step has to read."""
+    from onyxia_b200 import ir, models
+    from onyxia_b200.ir import HostTensor
+    H, KV, D = 32, 8, 128
+    out = []
+    for B in batches:
+        for P in pasts:
+            for w in windows:
+                b = ir.GraphBuilder()
+                Ps = b.sym("past_sequence_length")
+                q = b.input("q", ir.F16, [B, 1, H * D])
+                k = b.input("k", ir.F16, [B, 1, KV * D])
+                v = b.input("v", ir.F16, [B, 1, KV * D])
+                pk = b.input("past_key", ir.F16, [B, KV, Ps, D])
+                pv = b.input("past_value", ir.F16, [B, KV, Ps, D])
+                sl = b.input("seqlens_k", ir.I32, [B])
+                cfg = models.DecoderConfig("gqa", 0, 0, H, KV, D, 0, 0, act_dtype=ir.F16, max_positions=P + steps + 8)
+                c, sn = models.rope_caches(cfg)
+                outs = b.composite("com.microsoft.GroupQueryAttention",
+                                   {"num_heads": H, "kv_num_heads": KV, "scale": 0.0, "local_window_size": w, "do_rotary": 1,
+                                    "rotary_interleaved": 0, "has_attention_bias": 0},
+                                   [q, k, v, pk, pv, sl, b.constant(HostTensor.from_numpy(c)), b.constant(HostTensor.from_numpy(sn))],
+                                   [(ir.F16, [B, 1, H * D]), (ir.F16, [B, KV, Ps + 1, D]), (ir.F16, [B, KV, Ps + 1, D])])
+                b.output("out", outs[0])
+                b.output("present_key", outs[1])
+                b.output("present_value", outs[2])
+                s = backend.prepare(b.finish())
+                rng = np.random.default_rng(B + P)
+                up = lambda a: s.upload(HostTensor.from_numpy(a))
+                qt, kt, vt = (up(rng.standard_normal((B, 1, n * D)).astype(np.float16)) for n in (H, KV, KV))
+                past_k = up(np.zeros((B, KV, P, D), np.float16))
+                past_v = up(np.zeros((B, KV, P, D), np.float16))
+                lens = [up(np.full(B, P + i, np.int32)) for i in range(steps + 3)]
+
+                def step(i, past_k, past_v):
+                    o = dict(s.run({"q": qt, "k": kt, "v": vt, "past_key": past_k, "past_value": past_v, "seqlens_k": lens[i]}))
+                    return o["present_key"], o["present_value"]
+
+                for i in range(3):
+                    past_k, past_v = step(i, past_k, past_v)
+                s.wait_idle()
+                s.timer_start()
+                for i in range(3, 3 + steps):
+                    past_k, past_v = step(i, past_k, past_v)
+                us = s.timer_stop() * 1e3 / steps
+                keys = min(P + 4 + steps // 2, (w + 1) if w >= 0 else 1 << 40)
+                kv_bytes = B * KV * keys * D * 2 * 2
+                out.append({"batch": B, "past": P, "window": w, "us_per_step": us, "kv_bytes": kv_bytes,
+                            "gbps": kv_bytes / us / 1e3, "frac_of_peak": kv_bytes / us / 1e3 / peak})
+                del s, past_k, past_v
+    return out
+
+
+def c1_decode(backend, steps=32):
+    """Config C1: the 2-layer fp32 decoder (hidden 512, 8Q/2KV heads of 64, FFN 2048, vocab 32000, explicit zero points)."""
+    from onyxia_b200 import llm, models
+    cfg = models.config_c1()
+    lm = llm.NativeLlmSession(backend, models.build_decoder(cfg, seed=0), 256)
+    tok = lm.step_greedy(np.random.default_rng(0).integers(0, cfg.vocab, 16).tolist())
+    for _ in range(4):
+        tok = lm.step_greedy([tok])
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = lm.step_greedy([tok])
+    return steps / (time.perf_counter() - t0)
+
+
 def bench_c5(args, rank, local_rank, world):
     """Batched decode of the 27B architecture (config C5: 64 sequences at a 2048-token context), tensor-parallel
     over the launched ranks. Depth and vocabulary can be reduced (--layers, --vocab) to keep the run short; the
@@ -265,6 +334,8 @@ def main():
     ap.add_argument("--vocab", type=int, default=32768)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--config-table", action="store_true",
+                    help="measure the other configurations: C1 decode, the C2 MatMulNBits sweep (M = 1, 8, 64, 512), the C3 attention sweep")
     ap.add_argument("--shapes", default="")
     ap.add_argument("--ms", default="1,8")
     ap.add_argument("--profiler-range", action="store_true",
@@ -300,6 +371,16 @@ def main():
 
     if args.config == "c5":
         bench_c5(args, rank, local_rank, world)
+        return
+
+    if args.config_table:
+        from onyxia_b200 import backend as be
+        peak, peak_kind = load_peaks()
+        bk = be.CudaBackend((local_rank,))
+        print(json.dumps({"peak_gbs": peak, "peak_source": peak_kind,
+                          "c1_decode_tok_s_end_to_end": c1_decode(bk),
+                          "c2_matmul_nbits": gemv_sweep(bk, C2_SHAPES, [1, 8, 64, 512], peak),
+                          "c3_gqa_decode": gqa_sweep(bk, peak)}))
         return
 
     if args.gemv_sweep:

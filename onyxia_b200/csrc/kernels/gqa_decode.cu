@@ -385,7 +385,7 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1) gqa_decode_h(const GqaDecP p) {
+template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_decode_h(const GqaDecP p) {
     constexpr int DT = DT_F16;
     constexpr int D = 32 * DPL, RS = D + kRowPad;      // row stride in elements
     constexpr int kBlockBytes = kKeyBlock * RS * 2;
@@ -725,13 +725,13 @@ bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf 
         smem = decode_h_smem<DPL, GT>(p0.chunk_max);
         fn = gqa_decode_h<DPL, GT>;
     }
-    if (smem > 200 * 1024) return false;
+    if (smem > 224 * 1024) return false;
     // once per kernel instantiation (and per device the process uses): this runs on every re-lowering of a decode step
     static int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (smem > 48 * 1024 && attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
         attr_device = dev;
     }
@@ -778,7 +778,16 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     const int groups = (int)((G + GT - 1) / GT);
     if (KV * groups > 65535) return false;
     const long long span = (d.window >= 0 && d.window + 1 < t_size) ? d.window + 1 : t_size;
-    const int cx = span > 128 ? 8 : span > 64 ? 4 : span > 32 ? 2 : 1;
+    // CTAs per cluster: as many as the key range is worth splitting into, but no more than it takes to
+    // fill the machine — with many (batch row, KV head) pairs each CTA should rather own more keys than
+    // pay the cluster exchanges for a handful.
+    const long long pairs = B * KV * groups;
+    int cx = span > 128 ? 8 : span > 64 ? 4 : span > 32 ? 2 : 1;
+    int cx_fill = 1;
+    while (cx_fill < 8 && pairs * cx_fill * 2 <= 296) cx_fill <<= 1;
+    if (cx > cx_fill) cx = cx_fill;
+    // … unless a CTA's share of the scores would not fit in shared memory
+    while (cx < 8 && (span + cx - 1) / cx > 6144) cx <<= 1;
 
     GqaDecP p{};
     p.H = H;
