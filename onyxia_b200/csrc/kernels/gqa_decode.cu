@@ -785,7 +785,9 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     int cx = span > 128 ? 8 : span > 64 ? 4 : span > 32 ? 2 : 1;
     int cx_fill = 1;
     while (cx_fill < 8 && pairs * cx_fill * 2 <= 296) cx_fill <<= 1;
-    if (cx > cx_fill) cx = cx_fill;
+    int cx_long = 1;  // a single CTA streams a long key range slowly: at most ≈ 1 024 keys each
+    while (cx_long < 8 && span > 1024LL * cx_long) cx_long <<= 1;
+    if (cx > std::max(cx_fill, cx_long)) cx = std::max(cx_fill, cx_long);
     // … unless a CTA's share of the scores would not fit in shared memory
     while (cx < 8 && (span + cx - 1) / cx > 6144) cx <<= 1;
 
