@@ -128,8 +128,28 @@ ox_status ox_llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* tok
         if (l->present_of[i] >= 0) l->cache[i] = outs[(size_t)l->present_of[i]].second;
     l->past += n_ids;
     const oxrt::DTensor& logits = outs[(size_t)l->logits_out].second;
+    oxrt::DTensor tok;
+    if (token_out) tok = s.argmax_last(logits);
+    // While the device works on this step, get the plan of the next one-token step ready.
+    if (l->past + 1 <= l->max_seq_len) {
+        std::vector<std::pair<std::string, oxrt::DTensor>> next;
+        next.reserve(l->names.size());
+        bool ok = true;
+        for (size_t i = 0; i < l->names.size() && ok; i++) {
+            oxrt::DTensor t;
+            if (l->present_of[i] >= 0) {
+                t = l->cache[i];
+            } else {
+                t.dtype = m.values[m.inputs[i].second].ty.dtype;
+                if (l->names[i] == "input_ids" || l->names[i] == "position_ids") t.shape = {1, 1};
+                else if (l->names[i] == "attention_mask") t.shape = {1, l->past + 1};
+                else ok = false;  // an auxiliary input this loop cannot predict
+            }
+            next.emplace_back(l->names[i], std::move(t));
+        }
+        if (ok) s.preplan(next);
+    }
     if (token_out) {
-        oxrt::DTensor tok = s.argmax_last(logits);
         std::vector<int64_t> host((size_t)std::max<int64_t>(tok.numel(), 1));
         size_t written = 0;
         s.download(tok, host.data(), host.size() * sizeof(int64_t), &written);

@@ -731,13 +731,14 @@ inline double now_us() {
 }
 }  // namespace
 
-std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std::pair<std::string, DTensor>>& named) {
-    const double t_start = now_us();
-    OX_CUDA(cudaSetDevice(device_));
+// Selects (patches, builds) the plan for a set of inputs. With `shapes_only` the inputs need no buffers
+// except the KV caches: the call only gets the plan for an announced next step ready.
+Plan* Session::plan_for(const std::vector<std::pair<std::string, DTensor>>& named, std::vector<DTensor>& inputs, bool shapes_only,
+                        double* t_bound_out) {
     const Module& m = module_;
     // match by name against the signature (crates/onyxia-ir/src/backend.rs:47-50);
     // callers usually pass inputs in signature order, which is checked first
-    std::vector<DTensor> inputs(m.inputs.size());
+    inputs.assign(m.inputs.size(), DTensor{});
     std::vector<std::vector<size_t>> shape_store(m.inputs.size());
     std::vector<InputDesc> descs;
     descs.reserve(m.inputs.size());
@@ -748,7 +749,8 @@ std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std:
             for (auto& kv : named)
                 if (kv.first == m.inputs[i].first) found = &kv.second;
         if (!found) fail(ErrKind::Binding, "missing input '" + m.inputs[i].first + "'");
-        if (!found->buf) fail(ErrKind::Runtime, "input '" + m.inputs[i].first + "' is not a device tensor of this backend");
+        if (!found->buf && !shapes_only)
+            fail(ErrKind::Runtime, "input '" + m.inputs[i].first + "' is not a device tensor of this backend");
         inputs[i] = *found;
         shape_store[i].assign(found->shape.begin(), found->shape.end());
         descs.push_back(InputDesc{m.inputs[i].first.c_str(), inputs[i].dtype, shape_store[i].data(), shape_store[i].size()});
@@ -756,7 +758,10 @@ std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std:
     Bindings bindings = bind_shapes(m, descs);
 
     for (size_t i = 0; i < inputs.size(); i++)
-        if (inputs[i].cap && input_needs_dense_[i]) inputs[i] = dense_copy(inputs[i]);
+        if (inputs[i].cap && input_needs_dense_[i]) {
+            if (shapes_only) return nullptr;  // would have to copy: leave it to the real run
+            inputs[i] = dense_copy(inputs[i]);
+        }
 
     // Which KV caches can be appended to in place this time?
     std::vector<char> kv_in_place(m.nodes.size(), 0);
@@ -767,13 +772,13 @@ std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std:
         ValueId pres = m.nodes[n].outputs[1];
         int64_t total = (int64_t)m.values[pres].ty.shape[2].eval(bindings);
         auto ok = [&](const DTensor& t) {
-            return t.cap >= total && t.offset == 0 && t.shape.size() == 4 && t.buf->kv_rows == t.shape[2];
+            return t.buf && t.cap >= total && t.offset == 0 && t.shape.size() == 4 && t.buf->kv_rows == t.shape[2];
         };
         bool outs = is_output_root_[m.nodes[n].outputs[1]] && is_output_root_[m.nodes[n].outputs[2]];
         kv_in_place[n] = ok(tk) && ok(tv) && tk.buf != tv.buf && outs;
     }
 
-    const double t_bound = now_us();
+    if (t_bound_out) *t_bound_out = now_us();
     // ── find, patch or build the plan ──
     std::vector<uint64_t> key = structure_key(inputs, kv_in_place);
     Plan* plan = nullptr;
@@ -797,10 +802,31 @@ std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std:
                 break;
             }
     if (!plan) {
+        if (shapes_only) return nullptr;  // a full build needs the real inputs
         plans_.push_front(build_plan(bindings, inputs, kv_in_place));
         plan = plans_.front().get();
         while (plans_.size() > 6) plans_.pop_back();
     }
+    return plan;
+}
+
+// Announces the shapes of the next run (buffers are only needed for the KV caches) so that its plan is
+// patched now, while the device is still busy with the current step.
+void Session::preplan(const std::vector<std::pair<std::string, DTensor>>& named) {
+    std::vector<DTensor> inputs;
+    try {
+        plan_for(named, inputs, true, nullptr);
+    } catch (const Error&) {
+        // the real run reports whatever is wrong with its inputs
+    }
+}
+
+std::vector<std::pair<std::string, DTensor>> Session::run(const std::vector<std::pair<std::string, DTensor>>& named) {
+    const double t_start = now_us();
+    OX_CUDA(cudaSetDevice(device_));
+    std::vector<DTensor> inputs;
+    double t_bound = t_start;
+    Plan* plan = plan_for(named, inputs, false, &t_bound);
 
     const double t_planned = now_us();
     std::vector<BufferRef> out_bufs;

@@ -77,6 +77,7 @@ public:
 
     DTensor upload(DType dtype, const std::vector<int64_t>& shape, const void* bytes, size_t nbytes);
     std::vector<std::pair<std::string, DTensor>> run(const std::vector<std::pair<std::string, DTensor>>& inputs);
+    void preplan(const std::vector<std::pair<std::string, DTensor>>& next_inputs);
     void download(const DTensor& t, void* dst, size_t cap, size_t* written);
     DTensor argmax_last(const DTensor& logits);
     void argmax_last_into(const DTensor& logits, const DTensor& out);
@@ -153,6 +154,8 @@ private:
                     const std::vector<oxk::TRef>& outs);
     void finish_outputs(Plan& plan);
     void execute(Plan& plan, const std::vector<DTensor>& inputs, std::vector<BufferRef>& out_bufs);
+    Plan* plan_for(const std::vector<std::pair<std::string, DTensor>>& named, std::vector<DTensor>& inputs, bool shapes_only,
+                   double* t_bound_out);
     void build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& params);
     void launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_pdl);
     void check_device_error();

@@ -319,11 +319,13 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     // two CTAs per SM where two stages of each fit (more producer warps to hide latencies), else one CTA with what fits
     p.stages = stage * 2 + 2048 <= 110 * 1024 ? 2 : (stage * 3 + 2048 <= 200 * 1024 ? 3 : 2);
     const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static int attr_device = -1;  // the attribute belongs to the device: set it again when the process moves on to another
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_device != dev) {
         cudaError_t e = cudaFuncSetAttribute((const void*)nbits_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-        attr_set = true;
+        attr_device = dev;
     }
     const Buf null{kSlotNull, 0};
     const unsigned grid = (unsigned)((p.row_tiles + 7) / 8);
