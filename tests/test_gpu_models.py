@@ -154,3 +154,25 @@ def test_native_generation_loop_matches_the_python_loop():
     assert np.array_equal(a, b)
     with pytest.raises(Exception):
         llm.NativeLlmSession(cuda_backend(), module.clone(), 4).step_greedy(prompt)
+
+
+def test_long_decode_crosses_length_buckets_and_cache_growth():
+    """300 greedy steps after a 500-token prompt on a 2-layer 1B-architecture model: the attention launches are
+    re-sized when the length leaves its 256-row bucket, the caches outgrow their capacity and move, the plan is
+    patched every step and replayed as a CUDA graph — and the last logits still equal those of one prefill over
+    the whole sequence."""
+    cfg = models.config_gemma3_1b()
+    cfg.layers, cfg.vocab = 2, 8192
+    module = models.build_decoder(cfg, seed=21)
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, cfg.vocab, 500).tolist()
+    nat = llm.NativeLlmSession(cuda_backend(), module.clone(), 2048)
+    toks = [nat.step_greedy(prompt)]
+    for _ in range(299):
+        toks.append(nat.step_greedy([toks[-1]]))
+    inc = nat.step_logits([toks[-1]])
+    assert nat.sequence_length() == 800
+    whole = llm.LlmSession(cuda_backend(), module.clone(), 2048)
+    full = whole.prefill(prompt + toks)
+    assert np.isfinite(inc).all()
+    assert np.abs(full - inc).max() <= 2e-2, float(np.abs(full - inc).max())
