@@ -152,6 +152,10 @@ Session::~Session() {
         cudaEventDestroy(r.b);
     }
     for (auto e : prof_free_) cudaEventDestroy(e);
+    if (stage_pinned_) {
+        cudaFreeHost(stage_pinned_);
+        for (auto e : stage_events_) cudaEventDestroy(e);
+    }
     if (ev_t0_) cudaEventDestroy(ev_t0_);
     if (ev_t1_) cudaEventDestroy(ev_t1_);
     if (stream_) cudaStreamDestroy(stream_);
@@ -628,7 +632,21 @@ DTensor Session::upload(DType dtype, const std::vector<int64_t>& shape, const vo
         fail(ErrKind::Interp, "tensor data size mismatch: " + std::to_string(nbytes) + " bytes for " + dtype_name(dtype) +
                                   " (expected " + std::to_string(t.nbytes()) + ")");
     t.buf = pool_->alloc(nbytes ? nbytes : 1);
-    if (nbytes) OX_CUDA(cudaMemcpyAsync(t.buf->ptr, bytes, nbytes, cudaMemcpyHostToDevice, stream_));
+    if (nbytes && nbytes <= kStageBytes) {
+        // Small uploads (token ids, masks) go through a ring of pinned staging slots: the copy is truly
+        // asynchronous and the caller's memory is free for reuse when this returns.
+        if (!stage_pinned_) {
+            OX_CUDA(cudaMallocHost((void**)&stage_pinned_, kStageBytes * kStageSlots));
+            for (auto& e : stage_events_) OX_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        }
+        const unsigned slot = stage_cursor_++ % kStageSlots;
+        if (stage_cursor_ > kStageSlots) OX_CUDA(cudaEventSynchronize(stage_events_[slot]));
+        std::memcpy(stage_pinned_ + (size_t)slot * kStageBytes, bytes, nbytes);
+        OX_CUDA(cudaMemcpyAsync(t.buf->ptr, stage_pinned_ + (size_t)slot * kStageBytes, nbytes, cudaMemcpyHostToDevice, stream_));
+        OX_CUDA(cudaEventRecord(stage_events_[slot], stream_));
+    } else if (nbytes) {
+        OX_CUDA(cudaMemcpyAsync(t.buf->ptr, bytes, nbytes, cudaMemcpyHostToDevice, stream_));
+    }
     return t;
 }
 

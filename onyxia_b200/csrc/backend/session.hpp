@@ -187,6 +187,12 @@ private:
     bool err_pending_ = false;
     std::list<std::unique_ptr<Plan>> plans_;  // most recently used first
     cudaEvent_t ev_t0_ = nullptr, ev_t1_ = nullptr;
+    // pinned staging for small uploads
+    static constexpr size_t kStageBytes = 64 * 1024;
+    static constexpr unsigned kStageSlots = 16;
+    uint8_t* stage_pinned_ = nullptr;
+    cudaEvent_t stage_events_[kStageSlots] = {};
+    unsigned stage_cursor_ = 0;
     // profiling: one event pair per launch, read back in take_timings
     struct ProfRec {
         cudaEvent_t a, b;

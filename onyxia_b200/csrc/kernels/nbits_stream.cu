@@ -775,9 +775,25 @@ void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TR
 
     // tuning knob: resident CTAs per SM the grid should fill
     static const int ctas_per_sm = env_int("ONYXIA_GEMV_CTAS_PER_SM", 2, 1, 8);
-    p.rts_per_cta = (int)((p.row_tiles + 148LL * ctas_per_sm - 1) / (148LL * ctas_per_sm));
-    if (gr.geglu) p.rts_per_cta = (p.rts_per_cta + 1) & ~1;  // a CTA holds whole gate/up pairs
-    const long long grid = (p.row_tiles + p.rts_per_cta - 1) / p.rts_per_cta;
+    auto split = [&](int per_sm, int* rts, long long* grid, long long* load) {
+        *rts = (int)((p.row_tiles + 148LL * per_sm - 1) / (148LL * per_sm));
+        if (gr.geglu) *rts = (*rts + 1) & ~1;  // a CTA holds whole gate/up pairs
+        *grid = (p.row_tiles + *rts - 1) / *rts;
+        *load = ((*grid + 147) / 148) * *rts;  // row tiles the busiest SM streams
+    };
+    long long grid, load;
+    split(ctas_per_sm, &p.rts_per_cta, &grid, &load);
+    // With a long K a CTA's fixed costs (staging K activations, the fold) are large: if one CTA per SM
+    // balances as well, take that.
+    if (p.k_tiles >= 64 && ctas_per_sm > 1) {
+        int rts1;
+        long long grid1, load1;
+        split(1, &rts1, &grid1, &load1);
+        if (load1 <= load) {
+            p.rts_per_cta = rts1;
+            grid = grid1;
+        }
+    }
 
     const bool prologue = gr.w1 || gr.res || gr.w2;
     const size_t fixed = (size_t)kWarps * kStages * kStageTiles * tile_bytes + (size_t)kWarps * kStages * 8 +
