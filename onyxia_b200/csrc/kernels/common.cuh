@@ -107,8 +107,21 @@ __device__ __forceinline__ void ox_trace(ErrWord* e, int id) {
         }
     }
 }
+// the same for a thread other than thread 0 (the caller picks one thread of block 0)
+__device__ __forceinline__ void ox_trace_here(ErrWord* e, int id) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long* t = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(e) + 256);
+        const unsigned i = atomicAdd(reinterpret_cast<unsigned*>(t), 1u);
+        if (i < 8000) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            t[1 + i] = ((unsigned long long)id << 56) | (now & 0x00FFFFFFFFFFFFFFull);
+        }
+    }
+}
 #else
 #define ox_trace(e, id) ((void)0)
+#define ox_trace_here(e, id) ((void)0)
 #endif
 
 // Programmatic dependent launch. `pdl_trigger` lets the next kernel in the

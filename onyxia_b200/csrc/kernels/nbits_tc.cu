@@ -28,8 +28,10 @@ namespace oxk {
 
 namespace {
 
-constexpr int kProducerWarps = 8;
-constexpr int kThreadsTc = (kProducerWarps + 1) * 32;
+constexpr int kProducerWarps = 8;                       // warps that widen the weights (A panels)
+constexpr int kCopyWarps = 8;                           // warps that copy the activations (B panels)
+constexpr int kMmaWarp = kProducerWarps + kCopyWarps;   // the warp that issues the MMAs
+constexpr int kThreadsTc = (kMmaWarp + 1) * 32;
 constexpr int kTileWt = 1024, kTileSt = 128, kTileZt = 64;
 constexpr int kPanelA = 128 * 128;  // bytes: 128 rows × 64 k of f16
 constexpr long long kWaitCyclesTc = 2000000000LL;
@@ -94,7 +96,7 @@ __device__ __forceinline__ unsigned long long umma_desc(unsigned smem_byte_addr)
     return (unsigned long long)((smem_byte_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
+__global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle pattern repeats every 1 024 bytes: panels start on that boundary
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
         for (int s = 0; s < S; s++) {
             // a stage is full when every producer warp has arrived and every producer thread's
             // asynchronous activation copies have landed
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps + kProducerWarps * 32) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps + kCopyWarps * 32) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + S + s)) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + 2 * S)) : "memory");
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
     }
     int tmem_cols = 32;
     while (tmem_cols < mb) tmem_cols <<= 1;
-    if (warp == kProducerWarps) {  // the MMA warp owns the tensor-memory allocation
+    if (warp == kMmaWarp) {  // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -138,7 +140,6 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
         const int rt = rt0 + warp;
         const bool rt_live = rt < p.row_tiles;
         const unsigned char* rec = p.tiles + (size_t)(rt_live ? rt : 0) * p.k_tiles * p.tile_bytes;
-        const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
         // this warp's record of a step: two 16-byte words of nibbles per lane, the two rows' scales (and zero points)
         struct Rec {
             uint4 wl, wh;
@@ -165,37 +166,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
             const int s = i % S;
             if (i >= S && ok && !bar_wait_tc(s_addr(bars + S + s), ((i / S) - 1) & 1)) ok = false;
             unsigned char* stage = smem + (size_t)s * stage_bytes;
-            // B: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels; 16-byte
-            // asynchronous copies straight into the swizzled rows (zero-filled beyond the matrix)
-            // Thread tid copies chunk `tid & 15` of rows (tid >> 4) + 16·j: the swizzle term (row & 7) is the
-            // same for all of them, so source and destination advance by constant strides.
-            unsigned char* bpan = stage + 2 * kPanelA;
-            {
-                const int ch = tid & 15, r0 = tid >> 4;
-                const long long k0 = (long long)i * 128 + ch * 8;
-                const unsigned dst0 = s_addr(bpan + (ch >> 3) * panel_b + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4));
-                if (vec) {
-                    const bool k_in = k0 < p.k;  // K is a multiple of 8 here: a chunk is whole or absent
-                    const __half* src0 = p.x + (p.m0 + r0) * p.k + k0;
-                    for (int j = 0; j * 16 < mb; j++) {
-                        const bool in = k_in && p.m0 + r0 + 16 * j < p.m_total;
-                        const __half* src = in ? src0 + (long long)j * 16 * p.k : p.x;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + j * 2048), "l"(src), "r"(in ? 16u : 0u) : "memory");
-                    }
-                } else {
-                    for (int j = 0; j * 16 < mb; j++) {
-                        const long long row = p.m0 + r0 + 16 * j;
-                        __half tmp[8];
-#pragma unroll
-                        for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 2048), "r"(reinterpret_cast<unsigned*>(tmp)[0]),
-                                     "r"(reinterpret_cast<unsigned*>(tmp)[1]), "r"(reinterpret_cast<unsigned*>(tmp)[2]),
-                                     "r"(reinterpret_cast<unsigned*>(tmp)[3])
-                                     : "memory");
-                    }
-                }
-            }
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s_addr(bars + s)) : "memory");
+            ox_trace(p.err, 41);
             // A: rows 16·warp + g and + 8, k = 32·t + 8·m … + 8 of this 128-k step; the next record is already on its way
             const Rec cur = next;
             next = fetch(i + 1);
@@ -215,6 +186,45 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the stores visible to the tensor core
             __syncwarp();
             if (lane == 0) bar_arrive(s_addr(bars + s));
+            ox_trace(p.err, 43);
+        }
+    } else if (warp < kMmaWarp) {
+        // ── copy warps: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels; 16-byte
+        // asynchronous copies straight into the swizzled rows (zero-filled beyond the matrix). Thread c copies
+        // chunk `c & 15` of rows (c >> 4) + 16·j: the swizzle term (row & 7) is the same for all of them, so
+        // source and destination advance by constant strides.
+        const int c = tid - kProducerWarps * 32;
+        const int ch = c & 15, r0 = c >> 4;
+        const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+        for (int i = 0; i < steps; i++) {
+            const int s = i % S;
+            if (i >= S && ok && !bar_wait_tc(s_addr(bars + S + s), ((i / S) - 1) & 1)) ok = false;
+            unsigned char* bpan = smem + (size_t)s * stage_bytes + 2 * kPanelA;
+            const long long k0 = (long long)i * 128 + ch * 8;
+            const unsigned dst0 = s_addr(bpan + (ch >> 3) * panel_b + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4));
+            if (vec) {
+                const bool k_in = k0 < p.k;  // K is a multiple of 8 here: a chunk is whole or absent
+                const __half* src0 = p.x + (p.m0 + r0) * p.k + k0;
+                for (int j = 0; j * 16 < mb; j++) {
+                    const bool in = k_in && p.m0 + r0 + 16 * j < p.m_total;
+                    const __half* src = in ? src0 + (long long)j * 16 * p.k : p.x;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + j * 2048), "l"(src), "r"(in ? 16u : 0u) : "memory");
+                }
+            } else {
+                for (int j = 0; j * 16 < mb; j++) {
+                    const long long row = p.m0 + r0 + 16 * j;
+                    __half tmp[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 2048), "r"(reinterpret_cast<unsigned*>(tmp)[0]),
+                                 "r"(reinterpret_cast<unsigned*>(tmp)[1]), "r"(reinterpret_cast<unsigned*>(tmp)[2]),
+                                 "r"(reinterpret_cast<unsigned*>(tmp)[3])
+                                 : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            // counts as this thread's arrival once its copies of this step have landed
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s_addr(bars + s)) : "memory");
         }
     } else {
         // ── MMA issuer ──
@@ -225,6 +235,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the asynchronous copies landed through the generic proxy
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
+                ox_trace_here(p.err, 44);
                 const unsigned a0 = s_addr(smem + (size_t)s * stage_bytes), b0 = a0 + 2 * kPanelA;
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
@@ -239,6 +250,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
                 }
                 // the stage is free once these MMAs have read it
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bars + S + s)) : "memory");
+                ox_trace_here(p.err, 45);
                 if (i == steps - 1)
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_addr(bars + 2 * S)) : "memory");
             }
@@ -284,7 +296,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const TcP p) {
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == kProducerWarps)
+    if (warp == kMmaWarp)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
@@ -316,8 +328,9 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     while (mb < gr.m && mb < 256) mb <<= 1;
     p.mb = mb;
     const size_t stage = 2 * (size_t)kPanelA + 2 * (size_t)mb * 128;
-    // two CTAs per SM where two stages of each fit (more producer warps to hide latencies), else one CTA with what fits
-    p.stages = stage * 2 + 2048 <= 110 * 1024 ? 2 : (stage * 3 + 2048 <= 200 * 1024 ? 3 : 2);
+    // one CTA per SM (17 warps): as many stages as fit, at most 4
+    p.stages = (int)std::min<size_t>(4, (200 * 1024 - 2048) / stage);
+    if (p.stages < 2) p.stages = 2;
     const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
     static int attr_device = -1;  // the attribute belongs to the device: set it again when the process moves on to another
     int dev = 0;
