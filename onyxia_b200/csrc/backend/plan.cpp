@@ -11,6 +11,8 @@
 #include <climits>
 #include <cstring>
 
+#include <cuda.h>
+
 #include "../kernels/common.cuh"
 #include "session.hpp"
 
@@ -514,6 +516,31 @@ std::vector<Timing> Session::take_timings() {
     return out;
 }
 
+// Encodes a tiled 2-D f16 tensor map (128-byte swizzle, zero fill outside the tensor) for the address a
+// record's tensor has in this run. The driver entry point is looked up through the runtime, so the
+// library still has no link-time dependency on the driver.
+static void encode_tensor_map(const oxk::TmapReloc& tm, void* base, uint8_t* dst) {
+    using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode encode = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
+            fail(ErrKind::Runtime, "cuTensorMapEncodeTiled is not available from this driver");
+        return reinterpret_cast<Encode>(fn);
+    }();
+    alignas(64) CUtensorMap map;
+    const cuuint64_t dims[2] = {tm.dim0, tm.dim1};
+    const cuuint64_t strides[1] = {tm.stride1_bytes};
+    const cuuint32_t box[2] = {tm.box0, tm.box1};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) fail(ErrKind::Runtime, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)rc));
+    std::memcpy(dst, &map, sizeof(map));
+}
+
 // One launch of a record with its parameter bytes. Kernels written for
 // programmatic dependent launch get the stream-serialisation attribute, so they
 // may begin while the launch before them is still running.
@@ -660,6 +687,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
                 void* p = resolve(rl.buf);
                 std::memcpy(params[i].data() + rl.field_off, &p, sizeof(void*));
             }
+            for (auto& tm : r.tmaps) encode_tensor_map(tm, resolve(tm.buf), params[i].data() + tm.field_off);
         }
         if (!rebuild) {
             for (size_t i = 0; i < n && !rebuild; i++) {
@@ -701,6 +729,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
                 void* p = resolve(rl.buf);
                 std::memcpy(params.data() + rl.field_off, &p, sizeof(void*));
             }
+            for (auto& tm : r.tmaps) encode_tensor_map(tm, resolve(tm.buf), params.data() + tm.field_off);
             void* args[1] = {params.data()};
             ProfRec pr{};
             if (profiling) {

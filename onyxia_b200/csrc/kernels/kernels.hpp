@@ -66,6 +66,16 @@ struct Reloc {
     Buf buf;
 };
 
+// A 2-D tiled tensor map over f16 elements that has to be encoded into the parameter bytes once the
+// address of its tensor is known (TMA loads: `cp.async.bulk.tensor`).
+struct TmapReloc {
+    uint32_t field_off;      // byte offset of the 128-byte map inside the parameter struct (64-byte aligned there)
+    Buf buf;                 // base of the tensor
+    uint64_t dim0, dim1;     // extents in elements: contiguous axis, outer axis
+    uint64_t stride1_bytes;  // bytes between outer rows (a multiple of 16)
+    uint32_t box0, box1;     // tile extents in elements (box0·2 ≤ 128 bytes with the 128-byte swizzle)
+};
+
 struct LaunchRec {
     const void* func = nullptr;
     dim3 grid{1, 1, 1}, block{1, 1, 1};
@@ -73,6 +83,7 @@ struct LaunchRec {
     unsigned smem = 0;
     std::vector<uint8_t> params;
     std::vector<Reloc> relocs;
+    std::vector<TmapReloc> tmaps;
     const char* label = "";
     int node = -1;  // IR node index, for error messages and profiling
     // The kernel executes `griddepcontrol.wait` before it reads anything an
@@ -121,7 +132,7 @@ public:
     }
 
     template <class P>
-    void launch(void (*kernel)(const P), dim3 grid, dim3 block, unsigned smem, const P& p,
+    LaunchRec& launch(void (*kernel)(const P), dim3 grid, dim3 block, unsigned smem, const P& p,
                 std::initializer_list<std::pair<const void*, Buf>> ptrs, const char* label, bool pdl = false) {
         static_assert(sizeof(P) <= 4000, "kernel parameter struct too large");
         LaunchRec r;
@@ -141,6 +152,7 @@ public:
         r.node = node;
         r.pdl = pdl;
         recs.push_back(std::move(r));
+        return recs.back();
     }
 
 private:

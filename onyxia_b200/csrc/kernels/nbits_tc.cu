@@ -8,8 +8,10 @@
 // stream is read once per MB activation rows. Per step of 128 k:
 //   * eight producer warps each widen one tile record (the streaming GEMV's
 //     nibble arithmetic, exact (q − zp)·s rounding) into the A panel in shared
-//     memory — K-major, 128-byte rows, 128-byte swizzle — and copy the matching
-//     activation columns into the B panel;
+//     memory — K-major, 128-byte rows, 128-byte swizzle; one of their threads asks the
+//     TMA unit for the matching activation columns (two tiled loads of 64 k × MB rows
+//     through a tensor map with the same swizzle, zero-filled outside the matrix), which
+//     land in the B panel and complete the stage's barrier by byte count;
 //   * one thread of a ninth warp issues eight tcgen05.mma (M 128 × N MB × K 16,
 //     f16 inputs, f32 accumulation in TMEM) and commits them to the mbarrier that
 //     frees the stage.
@@ -28,15 +30,15 @@ namespace oxk {
 
 namespace {
 
-constexpr int kProducerWarps = 8;                       // warps that widen the weights (A panels)
-constexpr int kCopyWarps = 8;                           // warps that copy the activations (B panels)
-constexpr int kMmaWarp = kProducerWarps + kCopyWarps;   // the warp that issues the MMAs
+constexpr int kProducerWarps = 8;         // warps that widen the weights (A panels), one per row tile
+constexpr int kMmaWarp = kProducerWarps;  // the warp that issues the MMAs
 constexpr int kThreadsTc = (kMmaWarp + 1) * 32;
 constexpr int kTileWt = 1024, kTileSt = 128, kTileZt = 64;
 constexpr int kPanelA = 128 * 128;  // bytes: 128 rows × 64 k of f16
 constexpr long long kWaitCyclesTc = 2000000000LL;
 
 struct TcP {
+    alignas(64) unsigned char xmap[128];  // tensor map over the activations [M, K] (box 64 k × mb rows), when use_tma
     const __half* x;             // activations [M, K]
     const unsigned char* tiles;  // tile records, row tile by row tile
     __half* y[3];                // outputs per segment [M, seg_n]
@@ -46,6 +48,7 @@ struct TcP {
     int seg_rt0[4];
     int n_seg, interleave2;      // interleave2: row tiles alternate between segment 0 and 1
     int k_tiles, row_tiles, mb, stages, tile_bytes, has_zp, node;
+    int use_tma;                 // 0: K is not a multiple of 8 (or x is not 16-byte aligned) — plain loads
 };
 
 __device__ __forceinline__ unsigned s_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -96,7 +99,7 @@ __device__ __forceinline__ unsigned long long umma_desc(unsigned smem_byte_addr)
     return (unsigned long long)((smem_byte_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-__global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
+__global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_constant__ TcP p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the swizzle pattern repeats every 1 024 bytes: panels start on that boundary
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -111,9 +114,9 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
 
     if (tid == 0) {
         for (int s = 0; s < S; s++) {
-            // a stage is full when every producer warp has arrived and every producer thread's
-            // asynchronous activation copies have landed
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps + kCopyWarps * 32) : "memory");
+            // a stage is full when every producer warp has arrived, and so has the thread that posted the
+            // activation bytes, and those bytes have landed
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_addr(bars + s)), "r"(kProducerWarps + 1) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + S + s)) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_addr(bars + 2 * S)) : "memory");
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
     bool ok = true;
 
     if (warp < kProducerWarps) {
-        // ── producers: warp w widens row tile rt0 + w; all of them copy the activations ──
+        // ── producers: warp w widens row tile rt0 + w ──
         const int g = lane >> 2, t = lane & 3;
         const int rt = rt0 + warp;
         const bool rt_live = rt < p.row_tiles;
@@ -167,6 +170,40 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
             if (i >= S && ok && !bar_wait_tc(s_addr(bars + S + s), ((i / S) - 1) & 1)) ok = false;
             unsigned char* stage = smem + (size_t)s * stage_bytes;
             ox_trace(p.err, 41);
+            if (p.use_tma) {
+                // B: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels
+                if (tid == 0) {
+                    const unsigned bar = s_addr(bars + s), dst = s_addr(stage + 2 * kPanelA);
+                    const unsigned long long map = reinterpret_cast<unsigned long long>(&p.xmap);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * (unsigned)panel_b) : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                        "l"(map), "r"(i * 128), "r"((int)p.m0), "r"(bar)
+                        : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                            dst + (unsigned)panel_b),
+                        "l"(map), "r"(i * 128 + 64), "r"((int)p.m0), "r"(bar)
+                        : "memory");
+                }
+            } else {
+                // plain loads, element by element: thread c fills chunk `c & 15` of rows (c >> 4) + 16·j
+                const int ch = tid & 15, r0 = tid >> 4;
+                unsigned char* bpan = stage + 2 * kPanelA;
+                const long long k0 = (long long)i * 128 + ch * 8;
+                const unsigned dst0 = s_addr(bpan + (ch >> 3) * panel_b + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4));
+                for (int j = 0; j * 16 < mb; j++) {
+                    const long long row = p.m0 + r0 + 16 * j;
+                    __half tmp[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 2048), "r"(reinterpret_cast<unsigned*>(tmp)[0]),
+                                 "r"(reinterpret_cast<unsigned*>(tmp)[1]), "r"(reinterpret_cast<unsigned*>(tmp)[2]),
+                                 "r"(reinterpret_cast<unsigned*>(tmp)[3])
+                                 : "memory");
+                }
+                if (tid == 0) bar_arrive(s_addr(bars + s));  // stands for the byte-count arrival; the warp's own arrival below orders the stores
+            }
             // A: rows 16·warp + g and + 8, k = 32·t + 8·m … + 8 of this 128-k step; the next record is already on its way
             const Rec cur = next;
             next = fetch(i + 1);
@@ -187,44 +224,6 @@ __global__ void __launch_bounds__(kThreadsTc, 1) nbits_gemm_tc(const TcP p) {
             __syncwarp();
             if (lane == 0) bar_arrive(s_addr(bars + s));
             ox_trace(p.err, 43);
-        }
-    } else if (warp < kMmaWarp) {
-        // ── copy warps: activation rows m0 … m0 + mb, columns 128·i … + 128, as two 64-k panels; 16-byte
-        // asynchronous copies straight into the swizzled rows (zero-filled beyond the matrix). Thread c copies
-        // chunk `c & 15` of rows (c >> 4) + 16·j: the swizzle term (row & 7) is the same for all of them, so
-        // source and destination advance by constant strides.
-        const int c = tid - kProducerWarps * 32;
-        const int ch = c & 15, r0 = c >> 4;
-        const bool vec = (p.k & 7) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
-        for (int i = 0; i < steps; i++) {
-            const int s = i % S;
-            if (i >= S && ok && !bar_wait_tc(s_addr(bars + S + s), ((i / S) - 1) & 1)) ok = false;
-            unsigned char* bpan = smem + (size_t)s * stage_bytes + 2 * kPanelA;
-            const long long k0 = (long long)i * 128 + ch * 8;
-            const unsigned dst0 = s_addr(bpan + (ch >> 3) * panel_b + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4));
-            if (vec) {
-                const bool k_in = k0 < p.k;  // K is a multiple of 8 here: a chunk is whole or absent
-                const __half* src0 = p.x + (p.m0 + r0) * p.k + k0;
-                for (int j = 0; j * 16 < mb; j++) {
-                    const bool in = k_in && p.m0 + r0 + 16 * j < p.m_total;
-                    const __half* src = in ? src0 + (long long)j * 16 * p.k : p.x;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst0 + j * 2048), "l"(src), "r"(in ? 16u : 0u) : "memory");
-                }
-            } else {
-                for (int j = 0; j * 16 < mb; j++) {
-                    const long long row = p.m0 + r0 + 16 * j;
-                    __half tmp[8];
-#pragma unroll
-                    for (int e = 0; e < 8; e++) tmp[e] = (row < p.m_total && k0 + e < p.k) ? p.x[row * p.k + k0 + e] : __float2half(0.f);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0 + j * 2048), "r"(reinterpret_cast<unsigned*>(tmp)[0]),
-                                 "r"(reinterpret_cast<unsigned*>(tmp)[1]), "r"(reinterpret_cast<unsigned*>(tmp)[2]),
-                                 "r"(reinterpret_cast<unsigned*>(tmp)[3])
-                                 : "memory");
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            // counts as this thread's arrival once its copies of this step have landed
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s_addr(bars + s)) : "memory");
         }
     } else {
         // ── MMA issuer ──
@@ -328,9 +327,11 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     while (mb < gr.m && mb < 256) mb <<= 1;
     p.mb = mb;
     const size_t stage = 2 * (size_t)kPanelA + 2 * (size_t)mb * 128;
-    // one CTA per SM (17 warps): as many stages as fit, at most 4
-    p.stages = (int)std::min<size_t>(4, (200 * 1024 - 2048) / stage);
+    // two CTAs per SM where two stages of each fit in half the shared memory, else one CTA with up to 4
+    const size_t half_sm = 110 * 1024, whole_sm = 216 * 1024;
+    p.stages = (int)std::min<size_t>(4, (2 * stage <= half_sm ? half_sm : whole_sm) / stage);
     if (p.stages < 2) p.stages = 2;
+    p.use_tma = (gr.k % 8 == 0 && x.buf.off % 16 == 0) ? 1 : 0;
     const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
     static int attr_device = -1;  // the attribute belongs to the device: set it again when the process moves on to another
     int dev = 0;
@@ -344,10 +345,12 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     const unsigned grid = (unsigned)((p.row_tiles + 7) / 8);
     for (long long m0 = 0; m0 < gr.m; m0 += mb) {
         p.m0 = m0;
-        em.launch(nbits_gemm_tc, dim3(grid), dim3(kThreadsTc), (unsigned)smem, p,
+        LaunchRec& rec = em.launch(nbits_gemm_tc, dim3(grid), dim3(kThreadsTc), (unsigned)smem, p,
                   {{&p.x, x.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.y[0], gr.y[0].buf},
                    {&p.y[1], gr.n_seg > 1 ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
                   "nbits_gemm_tc", /*pdl=*/true);
+        if (p.use_tma)
+            rec.tmaps.push_back(TmapReloc{(uint32_t)offsetof(TcP, xmap), x.buf, (uint64_t)gr.k, (uint64_t)gr.m, (uint64_t)gr.k * 2, 64u, (uint32_t)mb});
     }
 }
 
