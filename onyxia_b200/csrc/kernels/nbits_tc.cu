@@ -22,7 +22,17 @@
 // Every wait is bounded; on expiry the kernel records ERR_WAIT_TIMEOUT, lets the
 // remaining phases run out and frees its tensor memory before it exits.
 //
+// Accuracy: the tensor core adds into its f32 accumulator without rounding to nearest, so a long chain of
+// MMAs drifts. Consecutive steps therefore rotate over up to four accumulators side by side in tensor
+// memory, which the epilogue adds: chains a quarter as long, at no cost in the main loop.
+//
+// Split K: a matrix with few row blocks (or a few more than a whole wave of CTAs) would leave SMs idle,
+// so the k range can be cut into `splits` pieces (blockIdx.y), each CTA writing its f32 partial
+// accumulator to scratch; a second kernel adds the pieces in fixed order and rounds once.
+//
 // FLOPs 2·M·N·K; bytes as for the GEMV (0.5625 per weight) once per MB rows.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.hpp"
 
@@ -49,6 +59,10 @@ struct TcP {
     int n_seg, interleave2;      // interleave2: row tiles alternate between segment 0 and 1
     int k_tiles, row_tiles, mb, stages, tile_bytes, has_zp, node;
     int use_tma;                 // 0: K is not a multiple of 8 (or x is not 16-byte aligned) — plain loads
+    int n_acc;                   // accumulators in tensor memory that the steps rotate over (1, 2 or 4)
+    int splits;                  // pieces of the k range (gridDim.y); > 1: partial sums go to `partial`
+    float* partial;              // [splits][mb][n_pad] f32
+    long long n_pad;             // weight rows covered by the grid (128 per CTA)
 };
 
 __device__ __forceinline__ unsigned s_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -123,7 +137,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     int tmem_cols = 32;
-    while (tmem_cols < mb) tmem_cols <<= 1;
+    while (tmem_cols < mb * p.n_acc) tmem_cols <<= 1;
     if (warp == kMmaWarp) {  // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -134,7 +148,9 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
     const unsigned tmem = *tmem_slot;
 
     const int rt0 = blockIdx.x * 8;  // first row tile of this CTA
-    const int steps = p.k_tiles;
+    const int split = blockIdx.y;
+    const int kt_lo = (int)((long long)p.k_tiles * split / p.splits);  // this CTA's piece of the k range, in 128-k steps
+    const int steps = (int)((long long)p.k_tiles * (split + 1) / p.splits) - kt_lo;
     bool ok = true;
 
     if (warp < kProducerWarps) {
@@ -156,7 +172,7 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
             r.s2 = __float2half2_rn(0.f);
             r.z = make_uchar2(8, 8);
             if (rt_live && i < steps) {
-                const unsigned char* q = rec + (size_t)i * p.tile_bytes;
+                const unsigned char* q = rec + (size_t)(kt_lo + i) * p.tile_bytes;
                 r.wl = __ldg(reinterpret_cast<const uint4*>(q) + lane);
                 r.wh = __ldg(reinterpret_cast<const uint4*>(q) + 32 + lane);
                 r.s2 = *reinterpret_cast<const __half2*>(q + kTileWt + lane * 4);
@@ -178,19 +194,19 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
                     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2u * (unsigned)panel_b) : "memory");
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-                        "l"(map), "r"(i * 128), "r"((int)p.m0), "r"(bar)
+                        "l"(map), "r"((kt_lo + i) * 128), "r"((int)p.m0), "r"(bar)
                         : "memory");
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
                             dst + (unsigned)panel_b),
-                        "l"(map), "r"(i * 128 + 64), "r"((int)p.m0), "r"(bar)
+                        "l"(map), "r"((kt_lo + i) * 128 + 64), "r"((int)p.m0), "r"(bar)
                         : "memory");
                 }
             } else {
                 // plain loads, element by element: thread c fills chunk `c & 15` of rows (c >> 4) + 16·j
                 const int ch = tid & 15, r0 = tid >> 4;
                 unsigned char* bpan = stage + 2 * kPanelA;
-                const long long k0 = (long long)i * 128 + ch * 8;
+                const long long k0 = (long long)(kt_lo + i) * 128 + ch * 8;
                 const unsigned dst0 = s_addr(bpan + (ch >> 3) * panel_b + r0 * 128 + (((ch & 7) ^ (r0 & 7)) << 4));
                 for (int j = 0; j * 16 < mb; j++) {
                     const long long row = p.m0 + r0 + 16 * j;
@@ -240,10 +256,10 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
                 for (int j = 0; j < 8; j++) {
                     const unsigned long long da = umma_desc(a0 + (j >> 2) * kPanelA + (j & 3) * 32);
                     const unsigned long long db = umma_desc(b0 + (j >> 2) * panel_b + (j & 3) * 32);
-                    const unsigned accumulate = (i > 0 || j > 0) ? 1u : 0u;
+                    const unsigned accumulate = (i >= p.n_acc || j > 0) ? 1u : 0u;  // the first step of each accumulator overwrites it
                     asm volatile(
                         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem),
+                        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n" ::"r"(tmem + (unsigned)((i % p.n_acc) * mb)),
                         "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
                         : "memory");
                 }
@@ -275,19 +291,34 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
         }
         const bool row_ok = rtg < p.row_tiles && row < p.seg_n[seg];
         __half* yout = p.y[seg];
+        const int acc_used = min(p.n_acc, steps);
         for (int c0 = 0; c0 < mb; c0 += 16) {
-            unsigned v[16];
-            const unsigned addr = tmem + ((unsigned)(warp * 32) << 16) + (unsigned)c0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                  "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                : "r"(addr));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float sum[16];  // adding two to four f32 partial sums rounds to nearest: three roundings at 2^-24
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const long long mrow = p.m0 + c0 + j;
-                if (ok && row_ok && mrow < p.m_total) yout[mrow * p.seg_n[seg] + row] = __float2half_rn(__uint_as_float(v[j]));
+            for (int j = 0; j < 16; j++) sum[j] = 0.f;
+            for (int a = 0; a < acc_used; a++) {
+                unsigned v[16];
+                const unsigned addr = tmem + ((unsigned)(warp * 32) << 16) + (unsigned)(a * mb + c0);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                    : "r"(addr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; j++) sum[j] += __uint_as_float(v[j]);
+            }
+            if (p.splits > 1) {
+                float* part = p.partial + ((size_t)split * mb + c0) * p.n_pad + (size_t)rt0 * 16 + row_in_cta;
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    if (ok && p.m0 + c0 + j < p.m_total) part[(size_t)j * p.n_pad] = sum[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const long long mrow = p.m0 + c0 + j;
+                    if (ok && row_ok && mrow < p.m_total) yout[mrow * p.seg_n[seg] + row] = __float2half_rn(sum[j]);
+                }
             }
         }
     }
@@ -297,6 +328,38 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
     __syncthreads();
     if (warp == kMmaWarp)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+}
+
+// Adds the pieces of a split-K pass in fixed order and stores the f16 outputs.
+struct TcReduceP {
+    const float* partial;
+    __half* y[3];
+    long long m0, m_total, n_pad;
+    long long seg_n[3];
+    int seg_rt0[4];
+    int n_seg, interleave2, row_tiles, mb, splits;
+};
+
+__global__ void __launch_bounds__(256) nbits_gemm_reduce(const TcReduceP p) {
+    const long long rows = (long long)p.row_tiles * 16;
+    const long long m_here = min((long long)p.mb, p.m_total - p.m0);
+    for (long long i = global_tid(); i < rows * m_here; i += global_threads()) {
+        const long long r = i % rows, m = i / rows;
+        double acc = 0.0;
+        for (int sp = 0; sp < p.splits; sp++) acc += (double)p.partial[((size_t)sp * p.mb + m) * p.n_pad + r];
+        const int rtg = (int)(r >> 4);
+        int seg = 0;
+        long long row;
+        if (p.interleave2) {
+            seg = rtg & 1;
+            row = (long long)(rtg >> 1) * 16 + (r & 15);
+        } else {
+            if (p.n_seg > 1 && rtg >= p.seg_rt0[1]) seg = 1;
+            if (p.n_seg > 2 && rtg >= p.seg_rt0[2]) seg = 2;
+            row = (long long)(rtg - p.seg_rt0[seg]) * 16 + (r & 15);
+        }
+        if (row < p.seg_n[seg]) p.y[seg][(p.m0 + m) * p.seg_n[seg] + row] = __double2half(acc);
+    }
 }
 
 }  // namespace
@@ -331,6 +394,7 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     const size_t half_sm = 110 * 1024, whole_sm = 216 * 1024;
     p.stages = (int)std::min<size_t>(4, (2 * stage <= half_sm ? half_sm : whole_sm) / stage);
     if (p.stages < 2) p.stages = 2;
+    p.n_acc = mb <= 128 ? 4 : 2;  // 512 columns of tensor memory per SM; two CTAs share it when mb ≤ 64
     p.use_tma = (gr.k % 8 == 0 && x.buf.off % 16 == 0) ? 1 : 0;
     const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
     static int attr_device = -1;  // the attribute belongs to the device: set it again when the process moves on to another
@@ -343,14 +407,53 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     }
     const Buf null{kSlotNull, 0};
     const unsigned grid = (unsigned)((p.row_tiles + 7) / 8);
+    // Pieces of the k range: the count that minimises, in units of one 128-k step (≈ 1.3 µs), waves × (steps
+    // per piece + about four steps of set-up and drain per CTA) + the second kernel's launch and the partial
+    // sums' trip to memory and back; at least two steps per piece.
+    const long long slots = 148LL * (2 * stage <= half_sm ? 2 : 1);
+    int splits = 1;
+    {
+        double best = 1e300;
+        for (int sp = 1; sp <= 8 && sp * 2 <= std::max(p.k_tiles, 2); sp++) {
+            const long long waves = ((long long)grid * sp + slots - 1) / slots;
+            double cost = (double)waves * ((double)p.k_tiles / sp + 4.0);
+            if (sp > 1) cost += 2.5 + (double)sp * mb * (double)grid * 128 * 8.0 / 3.9e6;
+            if (cost < best * 0.97) {  // a larger count has to earn its extra pass over the partial sums
+                best = cost;
+                splits = sp;
+            }
+        }
+    }
+    if (const char* e = std::getenv("ONYXIA_GEMM_SPLITS")) splits = std::max(1, std::min({std::atoi(e), 8, std::max(p.k_tiles, 1)}));
+    p.splits = splits;
+    p.n_pad = (long long)grid * 128;
+    const Buf partial = splits > 1 ? em.scratch((size_t)splits * mb * p.n_pad * sizeof(float)) : null;
     for (long long m0 = 0; m0 < gr.m; m0 += mb) {
         p.m0 = m0;
-        LaunchRec& rec = em.launch(nbits_gemm_tc, dim3(grid), dim3(kThreadsTc), (unsigned)smem, p,
-                  {{&p.x, x.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.y[0], gr.y[0].buf},
+        LaunchRec& rec = em.launch(nbits_gemm_tc, dim3(grid, splits), dim3(kThreadsTc), (unsigned)smem, p,
+                  {{&p.x, x.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.partial, partial}, {&p.y[0], gr.y[0].buf},
                    {&p.y[1], gr.n_seg > 1 ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
                   "nbits_gemm_tc", /*pdl=*/true);
         if (p.use_tma)
             rec.tmaps.push_back(TmapReloc{(uint32_t)offsetof(TcP, xmap), x.buf, (uint64_t)gr.k, (uint64_t)gr.m, (uint64_t)gr.k * 2, 64u, (uint32_t)mb});
+        if (splits > 1) {
+            TcReduceP q{};
+            q.m0 = m0;
+            q.m_total = gr.m;
+            q.n_pad = p.n_pad;
+            q.n_seg = p.n_seg;
+            q.interleave2 = p.interleave2;
+            q.row_tiles = p.row_tiles;
+            q.mb = mb;
+            q.splits = splits;
+            for (int i = 0; i < 3; i++) q.seg_n[i] = p.seg_n[i];
+            for (int i = 0; i < 4; i++) q.seg_rt0[i] = p.seg_rt0[i];
+            const long long work = (long long)p.row_tiles * 16 * std::min<long long>(mb, gr.m - m0);
+            em.launch(nbits_gemm_reduce, dim3(grid_for(work, 256)), dim3(256), 0, q,
+                      {{&q.partial, partial}, {&q.y[0], gr.y[0].buf}, {&q.y[1], gr.n_seg > 1 ? gr.y[1].buf : null},
+                       {&q.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
+                      "nbits_gemm_reduce");
+        }
     }
 }
 
