@@ -142,7 +142,9 @@ def test_matmul_nbits_reference_kat_on_device():
 
 @pytest.mark.parametrize("dt", [f16, f32])
 @pytest.mark.parametrize("m_,k,n,zp", [(1, 64, 8, False), (1, 1152, 256, True), (3, 96, 40, False), (8, 2048, 64, True),
-                                        (1, 50, 7, False), (17, 128, 33, False)])
+                                        (1, 50, 7, False), (17, 128, 33, False),
+                                        # few row tiles and a long K (the shape of a down projection)
+                                        (1, 6912, 1152, False), (3, 4096, 48, True), (8, 3200, 272, False), (1, 3100, 20, True)])
 def test_matmul_nbits_fused_vs_oracle(dt, m_, k, n, zp):
     mod, act = models.build_matmul_nbits(m_, k, n, adt(dt), seed=5, with_zp=zp)
     t = dict(atol=2e-2, rtol=4e-3) if dt == f16 else dict(atol=1e-3, rtol=1e-3)
