@@ -76,6 +76,50 @@ template <int DT> __global__ void prim_reduce(const ReduceP p) {
     }
 }
 
+// Few outputs, each over many elements (the attention mask's row sums at batch 1): one CTA per output, four
+// independent loads in flight per thread, warps combined through shared memory. Same operations and order
+// classes as above (integers exact; float sums differ from the interpreter's only by rounding).
+template <int DT> __global__ void __launch_bounds__(256) prim_reduce_block(const ReduceP p) {
+    using W = typename Ty<DT>::W;
+    __shared__ W part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (long long o = blockIdx.x; o < p.out_n; o += gridDim.x) {
+        const long long base = nd_offset(o, p.kept, p.skept);
+        W acc = red_init<W>(p.op);
+        for (long long r0 = threadIdx.x; r0 < p.count; r0 += 4 * 256) {
+            W v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const long long r = r0 + u * 256;
+                v[u] = r < p.count ? (W)ld<DT>(p.x, base + nd_offset(r, p.red, p.sred)) : red_init<W>(p.op);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (r0 + u * 256 < p.count) acc = red_step(p.op, acc, v[u]);
+        }
+#pragma unroll
+        for (int s = 16; s > 0; s >>= 1) acc = red_step(p.op, acc, __shfl_xor_sync(0xffffffffu, acc, s));
+        if (lane == 0) part[warp] = acc;
+        __syncthreads();
+        if (warp == 0) {
+            acc = lane < 8 ? part[lane] : red_init<W>(p.op);
+#pragma unroll
+            for (int s = 4; s > 0; s >>= 1) {
+                W other = __shfl_xor_sync(0xffffffffu, acc, s);
+                if (lane < 8) acc = red_step(p.op, acc, other);
+            }
+            if (lane == 0) {
+                if (p.op == R_MEAN) {
+                    if constexpr (Ty<DT>::is_float) acc = acc / (float)p.count;
+                    else if (p.count != 0) acc = acc / p.count;  // truncating integer mean
+                }
+                st<DT>(p.y, o, acc);
+            }
+        }
+        __syncthreads();  // `part` is reused by the next output
+    }
+}
+
 void emit_reduce(Emitter& em, int op, const TRef& x, const TRef& y, const std::vector<size_t>& axes) {
     ReduceP p{};
     p.op = op;
@@ -96,8 +140,11 @@ void emit_reduce(Emitter& em, int op, const TRef& x, const TRef& y, const std::v
         }
     }
     (void)y;
-    dim3 g(grid_for(p.out_n * 32, 256)), b(256);
-#define CALL(DT) em.launch(prim_reduce<DT>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "prim_reduce")
+    const bool per_block = p.count >= 256 && p.out_n <= 148 * 2;
+    dim3 g(per_block ? (unsigned)std::max<long long>(p.out_n, 1) : grid_for(p.out_n * 32, 256)), b(256);
+#define CALL(DT)                                                                                              \
+    if (per_block) em.launch(prim_reduce_block<DT>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "prim_reduce"); \
+    else em.launch(prim_reduce<DT>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "prim_reduce")
     switch (x.dtype) {
         case DT_F32: CALL(DT_F32); break;
         case DT_F16: CALL(DT_F16); break;

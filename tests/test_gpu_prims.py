@@ -217,6 +217,19 @@ def test_reduce_f16_row():
     check_prim(ir.P_REDUCE, [rand((6, 1152), f16)], f16, op=ir.MEAN, axes=[1], keepdims=True)
 
 
+@pytest.mark.parametrize("op", [ir.SUM, ir.MEAN, ir.RMAX, ir.RMIN, ir.PROD])
+def test_reduce_few_outputs_over_many_elements(op):
+    """Few outputs over at least 256 elements each run one CTA per output (the attention mask's row sum)."""
+    check_prim(ir.P_REDUCE, [rand((1, 777), i64)], op=op, axes=[1], keepdims=False)
+    check_prim(ir.P_REDUCE, [rand((3, 1300), i32)], op=op, axes=[1], keepdims=True)
+    check_prim(ir.P_REDUCE, [rand((2, 300, 5), i64)], op=op, axes=[1], keepdims=False)  # strided reduced axis
+    x = rand((2, 2049), f32)
+    if op == ir.PROD:
+        x = (x * f32(0.01) + f32(1.0)).astype(f32)
+    check_prim(ir.P_REDUCE, [x], op=op, axes=[1], keepdims=False)
+    check_prim(ir.P_REDUCE, [rand((5, 256), f16)], f16, op=ir.RMAX if op == ir.PROD else op, axes=[1], keepdims=True)
+
+
 # ── Data movement ────────────────────────────────────────────────────────
 @pytest.mark.parametrize("dtype", [f32, f16, i64, np.uint8, np.bool_])
 def test_reshape_transpose_broadcast(dtype):
