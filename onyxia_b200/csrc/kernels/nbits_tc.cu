@@ -27,7 +27,8 @@
 // memory, which the epilogue adds: chains a quarter as long, at no cost in the main loop.
 //
 // Split K: a matrix with few row blocks (or a few more than a whole wave of CTAs) would leave SMs idle,
-// so the k range can be cut into `splits` pieces (blockIdx.y), each CTA writing its f32 partial
+// so the k range of the row blocks beyond the last whole wave (all of them when there is less than one
+// wave) can be cut into `splits` pieces, each CTA writing its f32 partial
 // accumulator to scratch; a second kernel adds the pieces in fixed order and rounds once.
 //
 // FLOPs 2·M·N·K; bytes as for the GEMV (0.5625 per weight) once per MB rows.
@@ -60,9 +61,10 @@ struct TcP {
     int k_tiles, row_tiles, mb, stages, tile_bytes, has_zp, node;
     int use_tma;                 // 0: K is not a multiple of 8 (or x is not 16-byte aligned) — plain loads
     int n_acc;                   // accumulators in tensor memory that the steps rotate over (1, 2 or 4)
-    int splits;                  // pieces of the k range (gridDim.y); > 1: partial sums go to `partial`
-    float* partial;              // [splits][mb][n_pad] f32
-    long long n_pad;             // weight rows covered by the grid (128 per CTA)
+    int n_full;                  // row blocks (CTAs) that take all of K; the blocks after them are cut along k
+    int splits;                  // pieces of the k range of those tail blocks; > 1: partial sums go to `partial`
+    float* partial;              // [splits][mb][n_pad] f32, rows counted from the first tail block
+    long long n_pad;             // weight rows of the tail blocks (128 per block)
 };
 
 __device__ __forceinline__ unsigned s_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -147,10 +149,13 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem = *tmem_slot;
 
-    const int rt0 = blockIdx.x * 8;  // first row tile of this CTA
-    const int split = blockIdx.y;
-    const int kt_lo = (int)((long long)p.k_tiles * split / p.splits);  // this CTA's piece of the k range, in 128-k steps
-    const int steps = (int)((long long)p.k_tiles * (split + 1) / p.splits) - kt_lo;
+    // CTAs 0 … n_full − 1 own a whole row block; the ones after them share the tail blocks, `splits` CTAs each
+    const int tail_j = (int)blockIdx.x - p.n_full;
+    const int block = tail_j < 0 ? (int)blockIdx.x : p.n_full + tail_j / p.splits;
+    const int splits = tail_j < 0 ? 1 : p.splits, split = tail_j < 0 ? 0 : tail_j % p.splits;
+    const int rt0 = block * 8;  // first row tile of this CTA
+    const int kt_lo = (int)((long long)p.k_tiles * split / splits);  // this CTA's piece of the k range, in 128-k steps
+    const int steps = (int)((long long)p.k_tiles * (split + 1) / splits) - kt_lo;
     bool ok = true;
 
     if (warp < kProducerWarps) {
@@ -308,8 +313,8 @@ __global__ void __launch_bounds__(kThreadsTc, 2) nbits_gemm_tc(const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 16; j++) sum[j] += __uint_as_float(v[j]);
             }
-            if (p.splits > 1) {
-                float* part = p.partial + ((size_t)split * mb + c0) * p.n_pad + (size_t)rt0 * 16 + row_in_cta;
+            if (splits > 1) {
+                float* part = p.partial + ((size_t)split * mb + c0) * p.n_pad + (size_t)(block - p.n_full) * 128 + row_in_cta;
 #pragma unroll
                 for (int j = 0; j < 16; j++)
                     if (ok && p.m0 + c0 + j < p.m_total) part[(size_t)j * p.n_pad] = sum[j];
@@ -338,15 +343,16 @@ struct TcReduceP {
     long long seg_n[3];
     int seg_rt0[4];
     int n_seg, interleave2, row_tiles, mb, splits;
+    long long row0;  // first weight row (in stream order) of the tail blocks
 };
 
 __global__ void __launch_bounds__(256) nbits_gemm_reduce(const TcReduceP p) {
-    const long long rows = (long long)p.row_tiles * 16;
+    const long long rows = (long long)p.row_tiles * 16 - p.row0;
     const long long m_here = min((long long)p.mb, p.m_total - p.m0);
     for (long long i = global_tid(); i < rows * m_here; i += global_threads()) {
-        const long long r = i % rows, m = i / rows;
+        const long long rl = i % rows, m = i / rows, r = p.row0 + rl;
         double acc = 0.0;
-        for (int sp = 0; sp < p.splits; sp++) acc += (double)p.partial[((size_t)sp * p.mb + m) * p.n_pad + r];
+        for (int sp = 0; sp < p.splits; sp++) acc += (double)p.partial[((size_t)sp * p.mb + m) * p.n_pad + rl];
         const int rtg = (int)(r >> 4);
         int seg = 0;
         long long row;
@@ -407,30 +413,45 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     }
     const Buf null{kSlotNull, 0};
     const unsigned grid = (unsigned)((p.row_tiles + 7) / 8);
-    // Pieces of the k range: the count that minimises, in units of one 128-k step (≈ 1.3 µs), waves × (steps
-    // per piece + about four steps of set-up and drain per CTA) + the second kernel's launch and the partial
-    // sums' trip to memory and back; at least two steps per piece.
+    // Whole waves of row blocks take all of K. The blocks left over (all of them when there is less than one
+    // wave) are cut into the number of pieces that minimises, in units of one 128-k step (≈ 1.3 µs),
+    // waves × (steps per piece + about four steps of set-up and drain per CTA) + the second kernel's launch
+    // and the partial sums' trip to memory and back; at least two steps per piece.
     const long long slots = 148LL * (2 * stage <= half_sm ? 2 : 1);
+    long long n_full = (long long)grid / slots * slots, tail = grid - n_full;
+    if (tail * 10 >= slots * 6) {  // the last wave is well filled as it is
+        n_full = grid;
+        tail = 0;
+    }
     int splits = 1;
-    {
+    if (tail > 0) {
         double best = 1e300;
         for (int sp = 1; sp <= 8 && sp * 2 <= std::max(p.k_tiles, 2); sp++) {
-            const long long waves = ((long long)grid * sp + slots - 1) / slots;
+            const long long waves = (tail * sp + slots - 1) / slots;
             double cost = (double)waves * ((double)p.k_tiles / sp + 4.0);
-            if (sp > 1) cost += 2.5 + (double)sp * mb * (double)grid * 128 * 8.0 / 3.9e6;
+            if (sp > 1) cost += 2.5 + (double)sp * mb * (double)tail * 128 * 8.0 / 3.9e6;
             if (cost < best * 0.97) {  // a larger count has to earn its extra pass over the partial sums
                 best = cost;
                 splits = sp;
             }
         }
     }
-    if (const char* e = std::getenv("ONYXIA_GEMM_SPLITS")) splits = std::max(1, std::min({std::atoi(e), 8, std::max(p.k_tiles, 1)}));
+    if (const char* e = std::getenv("ONYXIA_GEMM_SPLITS")) {  // diagnostics: every row block cut into that many pieces
+        splits = std::max(1, std::min({std::atoi(e), 8, std::max(p.k_tiles, 1)}));
+        n_full = 0;
+        tail = grid;
+    }
+    if (splits == 1) {
+        n_full = grid;
+        tail = 0;
+    }
+    p.n_full = (int)n_full;
     p.splits = splits;
-    p.n_pad = (long long)grid * 128;
+    p.n_pad = tail * 128;
     const Buf partial = splits > 1 ? em.scratch((size_t)splits * mb * p.n_pad * sizeof(float)) : null;
     for (long long m0 = 0; m0 < gr.m; m0 += mb) {
         p.m0 = m0;
-        LaunchRec& rec = em.launch(nbits_gemm_tc, dim3(grid, splits), dim3(kThreadsTc), (unsigned)smem, p,
+        LaunchRec& rec = em.launch(nbits_gemm_tc, dim3((unsigned)(n_full + tail * splits)), dim3(kThreadsTc), (unsigned)smem, p,
                   {{&p.x, x.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.partial, partial}, {&p.y[0], gr.y[0].buf},
                    {&p.y[1], gr.n_seg > 1 ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
                   "nbits_gemm_tc", /*pdl=*/true);
@@ -446,9 +467,10 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
             q.row_tiles = p.row_tiles;
             q.mb = mb;
             q.splits = splits;
+            q.row0 = n_full * 128;
             for (int i = 0; i < 3; i++) q.seg_n[i] = p.seg_n[i];
             for (int i = 0; i < 4; i++) q.seg_rt0[i] = p.seg_rt0[i];
-            const long long work = (long long)p.row_tiles * 16 * std::min<long long>(mb, gr.m - m0);
+            const long long work = ((long long)p.row_tiles * 16 - q.row0) * std::min<long long>(mb, gr.m - m0);
             em.launch(nbits_gemm_reduce, dim3(grid_for(work, 256)), dim3(256), 0, q,
                       {{&q.partial, partial}, {&q.y[0], gr.y[0].buf}, {&q.y[1], gr.n_seg > 1 ? gr.y[1].buf : null},
                        {&q.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},

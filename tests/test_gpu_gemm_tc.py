@@ -17,7 +17,9 @@ pytestmark = pytest.mark.gpu
                                       (100, 1152, 1024, False), (300, 2048, 2048, False), (512, 1024, 272, False),
                                       (64, 96, 40, True),
                                       # K not a multiple of 8: rows are not 16-byte aligned, the activations go by plain loads
-                                      (20, 100, 48, False), (130, 1004, 272, True)])
+                                      (20, 100, 48, False), (130, 1004, 272, True),
+                                      # a few row blocks more than a whole wave of CTAs: only those are cut along K
+                                      (130, 1024, 19200, False), (16, 1024, 38400, False)])
 def test_matmul_nbits_many_rows_matches_oracle(m, k, n, zp):
     module, act = models.build_matmul_nbits(m, k, n, act_dtype=ir.F16, seed=m + k, with_zp=zp)
     ref.set_threads(8)
