@@ -112,14 +112,14 @@ def build_model(seed=0):
     return cfg, module, time.time() - t
 
 
-def cpu_reference_run(cfg, module, steps, warmup, threads):
-    """The CPU oracle through the same KV loop: a short prefill, then timed decode steps."""
+def cpu_reference_run(cfg, module, steps, warmup, threads, prompt_len=4):
+    """The CPU oracle through the same KV loop: a prefill of `prompt_len` tokens (untimed), then timed decode steps."""
     from onyxia_b200 import llm
     from oracle import ref
     ref.set_threads(threads)
     s = llm.LlmSession(ref.RefBackend(), module, 4096)
     rng = np.random.default_rng(0)
-    prompt = rng.integers(0, cfg.vocab, 4).tolist()
+    prompt = rng.integers(0, cfg.vocab, prompt_len).tolist()
     logits = s.prefill(prompt)
     tok = llm.sample_greedy(logits)
     for _ in range(warmup):
@@ -245,16 +245,16 @@ def c1_decode(backend, steps=32):
     return steps / (time.perf_counter() - t0)
 
 
-def bench_c5(args, rank, local_rank, world):
+def run_c5(args, rank, local_rank, world, group=None):
     """Batched decode of the 27B architecture (config C5: 64 sequences at a 2048-token context), tensor-parallel
     over the launched ranks. Depth and vocabulary can be reduced (--layers, --vocab) to keep the run short; the
-    line reports the measured per-layer time and its extrapolation to the full 62 layers."""
+    result reports the measured per-layer time and its extrapolation to the full 62 layers. `group` is a
+    torch.distributed group that can pass Python objects between the ranks (it only carries the NCCL id and the
+    max over ranks of the timing)."""
     import torch.distributed as dist
     from onyxia_b200 import backend as be
     from onyxia_b200 import ir, models
     from onyxia_b200.ir import HostTensor
-    if world > 1:
-        dist.init_process_group("gloo")
     cfg = models.config_gemma3_27b()
     full_layers = cfg.layers
     cfg.layers = args.layers
@@ -263,7 +263,7 @@ def bench_c5(args, rank, local_rank, world):
     stats = module.tp_stats(world) if world > 1 else (0, 0, 0)
     backend = be.CudaBackend((local_rank,))
     if world > 1:
-        backend.join_tp_torch()
+        backend.join_tp_torch(group)
         module = module.tp_partition(world, rank)
     sess = backend.prepare(module)
     B, ctx = args.batch, args.context
@@ -291,7 +291,7 @@ def bench_c5(args, rank, local_rank, world):
         step(i)
     sess.wait_idle()
     if world > 1:
-        dist.barrier()
+        dist.barrier(group)
     sampler = ClockSampler(local_rank)
     sampler.start()
     sess.timer_start()
@@ -301,20 +301,65 @@ def bench_c5(args, rank, local_rank, world):
     clocks = sampler.stop()
     if world > 1:
         box = [None] * world
-        dist.all_gather_object(box, ms)
+        dist.all_gather_object(box, ms, group=group)
         ms = max(box)
     per_layer_ms = ms / K / cfg.layers  # includes the (small) embedding / lm_head share
     peak, peak_kind = load_peaks()
-    weight_bytes_layer = cfg.weight_bytes_per_token() / max(cfg.layers, 1) if hasattr(cfg, "weight_bytes_per_token") else None
+    # the block's HBM roofline: this rank's share of the weights and of the K/V rows of one layer
+    lm_head_bytes = cfg.vocab * ((cfg.hidden + 31) // 32) * 18
+    layer_bytes = (cfg.weight_bytes_per_token() - lm_head_bytes) / max(cfg.layers, 1)
+    kv_bytes = 2 * B * cfg.kv_heads * ctx * cfg.head_dim * 2
+    result = {
+        "metric": "batched decode tok/s (Gemma-3-27B-arch int4, 64 sequences, 2048-token context)", "unit": "tok/s",
+        "value": B * K / (ms / 1e3), "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"gemma3-27b-arch int4 block-32, batch {B}, context {ctx}, tensor parallel over {world} GPU(s)",
+                   "layers_run": cfg.layers, "layers_full": full_layers, "vocab_run": cfg.vocab, "tp_split": list(stats)},
+        "ms_per_layer": per_layer_ms, "extrapolated_full_depth_tok_s": B / (per_layer_ms * full_layers / 1e3),
+        "layer_roofline_frac": (layer_bytes + kv_bytes) / world / (peak * 1e9) / (per_layer_ms / 1e3),
+        "clocks": clocks, "gpu_launches": sess.launch_count(), "peak_gbs": peak, "peak_source": peak_kind}
+    del sess, kv
+    return result
+
+
+def tp_agreement(rank, local_rank, world, group):
+    """Tensor-parallel vs single-GPU logits on a small f16 decoder (prefill + 8 greedy steps): max-abs difference,
+    measured on rank 0."""
+    import torch.distributed as dist
+    from onyxia_b200 import backend as be
+    from onyxia_b200 import ir, llm, models
+    cfg = models.config_c1()
+    cfg.act_dtype, cfg.layers, cfg.vocab, cfg.explicit_zero_points = ir.F16, 2, 4096, False
+    if cfg.kv_heads % world or cfg.heads % world:
+        cfg.heads, cfg.kv_heads = 8 * max(1, world // 8), max(2, world)
+        cfg.hidden = cfg.heads * cfg.head_dim
+    module = models.build_decoder(cfg, seed=7)
+    prompt = np.random.default_rng(3).integers(0, cfg.vocab, 24).tolist()
+    backend = be.CudaBackend((local_rank,))
+    backend.join_tp_torch(group)
+    lm = llm.LlmSession(backend, module.tp_partition(world, rank), 256)
+    got, toks = [lm.prefill(prompt)], []
+    for _ in range(8):
+        toks.append(llm.sample_greedy(got[-1]))
+        got.append(lm.decode(toks[-1]))
+    diff = None
     if rank == 0:
-        print(json.dumps({
-            "metric": "batched decode tok/s (Gemma-3-27B-arch int4, 64 sequences, 2048-token context)", "unit": "tok/s",
-            "value": B * K / (ms / 1e3), "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": f"gemma3-27b-arch int4 block-32, batch {B}, context {ctx}, tensor parallel over {world} GPU(s)",
-                       "layers_run": cfg.layers, "layers_full": full_layers, "vocab_run": cfg.vocab, "tp_split": list(stats)},
-            "ms_per_layer": per_layer_ms, "extrapolated_full_depth_tok_s": B / (per_layer_ms * full_layers / 1e3),
-            "clocks": clocks, "gpu_launches": sess.launch_count(), "peak_gbs": peak, "peak_source": peak_kind}))
+        whole = llm.LlmSession(be.CudaBackend((local_rank,)), module, 256)
+        want = [whole.prefill(prompt)]
+        for t in toks:
+            want.append(whole.decode(t))
+        diff = max(float(np.abs(w - g).max()) for w, g in zip(want, got))
+    dist.barrier(group)
+    return diff
+
+
+def bench_c5(args, rank, local_rank, world):
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("gloo")
+    result = run_c5(args, rank, local_rank, world)
+    if rank == 0:
+        print(json.dumps(result))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -338,6 +383,9 @@ def main():
                     help="measure the other configurations: C1 decode, the C2 MatMulNBits sweep (M = 1, 8, 64, 512), the C3 attention sweep")
     ap.add_argument("--shapes", default="")
     ap.add_argument("--ms", default="1,8")
+    ap.add_argument("--ref-prompt-len", type=int, default=PROMPT_LEN,
+                    help="prompt length of the CPU reference arm (its prefill is untimed; 512 tokens take about a minute)")
+    ap.add_argument("--no-tp", action="store_true", help="with more than one rank: skip the tensor-parallel 27B-architecture slice")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -356,15 +404,18 @@ def main():
         cfg, module, _ = build_model()
         steps = min(args.steps, 8)  # a bounded sample: each CPU token takes about a second
         warm = min(args.warmup, 1)
-        tps, dt = cpu_reference_run(cfg, module, steps, warm, threads)
+        tps, dt = cpu_reference_run(cfg, module, steps, warm, threads, prompt_len=args.ref_prompt_len)
         line = {"metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
                 "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic", "impl": "reference",
-                "config": {"workload": "gemma3-1b-arch int4 block-32, fp16 activations, batch 1, greedy decode",
-                           "prompt_len": 4, "note": "CPU port of onyxia-backend-ref (the Rust interpreter cannot be "
-                                                    "built offline); decode steps after a 4-token prompt"},
+                "config": {"workload": "gemma3-1b-arch int4 block-32 (26 layers, hidden 1152, 4Q/1KV heads of 256, FFN 6912, "
+                                       "vocab 262144, 5 local(512):1 global), fp16 activations, batch 1, "
+                                       f"{args.ref_prompt_len}-token prompt, greedy decode",
+                           "prompt_len": args.ref_prompt_len, "same_config": args.ref_prompt_len == PROMPT_LEN,
+                           "note": "CPU port of onyxia-backend-ref (the Rust interpreter cannot be built offline); the timed "
+                                   f"region is {steps} decode steps after the (untimed) prompt prefill"},
                 "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
-                                 "sample": f"{steps} decode steps after a 4-token prompt"},
+                                 "sample": f"{steps} decode steps after a {args.ref_prompt_len}-token prompt"},
                 "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -506,37 +557,74 @@ def main():
         a[0] += 1
         a[1] += ns
     peak, peak_kind = load_peaks()
-    gemv_name = max((k for k in by_kernel if k.startswith("nbits_")), key=lambda k: by_kernel[k][1], default="nbits_stream")
-    gemv = by_kernel.get(gemv_name, [0, 0])
     weight_bytes = cfg.weight_bytes_per_token()
-    # activations in and out of the 7 matrices per layer + lm_head, fp16
-    act_bytes = 2 * (cfg.layers * (cfg.hidden * 4 + cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim +
-                                   3 * cfg.ffn + cfg.hidden * 2) + cfg.hidden + cfg.vocab)
-    alg_bytes_per_step = weight_bytes + act_bytes
-    # DRAM bytes per launch of the dominant kernel from the committed ncu capture of this command
-    # (profiles/decode_step_gemma3_1b_launch_list.md: 210 launches read 1 139.5 MB and wrote 0.83 MB)
-    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": 5430145,
-                "kernel": gemv_name, "peak_source": peak_kind}
-    if gemv[0]:
-        gemv_s_per_step = gemv[1] / 1e9 / prof_steps
-        roofline["achieved"] = alg_bytes_per_step / gemv_s_per_step / 1e9
+    lm_head_bytes = cfg.vocab * ((cfg.hidden + 31) // 32) * 18
+    kv_now = cfg.kv_bytes_per_token(lm.past_seq_len)
+    # activations in and out of the 7 matrices per layer, fp16
+    layer_act_bytes = 2 * cfg.layers * (cfg.hidden * 4 + cfg.heads * cfg.head_dim * 2 + 2 * cfg.kv_heads * cfg.head_dim + 3 * cfg.ffn + cfg.hidden * 2)
+    # Algorithmic bytes per launch of each kernel that streams weights: the persistent step kernel reads every
+    # layer's weights and the visible K/V rows once; the streaming GEMV reads one matrix (group) per launch.
+    per_launch = {}
+    if "persist_step" in by_kernel:
+        per_launch["persist_step"] = weight_bytes - lm_head_bytes + kv_now + layer_act_bytes
+        if "nbits_stream" in by_kernel:
+            per_launch["nbits_stream"] = lm_head_bytes + 2 * (cfg.hidden + cfg.vocab)
+    elif "nbits_stream" in by_kernel:
+        n_l = by_kernel["nbits_stream"][0] / prof_steps
+        per_launch["nbits_stream"] = (weight_bytes + layer_act_bytes + 2 * (cfg.hidden + cfg.vocab)) / n_l
+    dom = max(per_launch, key=lambda k: by_kernel[k][1], default=None)
+    # DRAM traffic per launch: ncu captures of these kernels read 1.01× (streaming GEMV) and 1.04× (persistent
+    # step, a 4-layer model) their algorithmic bytes; the figure here is that ratio applied to this launch.
+    traffic_ratio = {"persist_step": 1.04, "nbits_stream": 1.01}
+    roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
+                "kernel": dom, "peak_source": peak_kind,
+                "traffic_source": "static: ratio of DRAM bytes to algorithmic bytes from the ncu capture summarised under profiles/"}
+    if dom:
+        n_launch, ns = by_kernel[dom]
+        avg_s = ns / n_launch / 1e9
+        roofline["algorithmic_bytes_per_launch"] = per_launch[dom]
+        roofline["launches_per_step"] = n_launch / prof_steps
+        roofline["avg_launch_us"] = avg_s * 1e6
+        roofline["achieved"] = per_launch[dom] / avg_s / 1e9
         roofline["frac"] = roofline["achieved"] / peak
-        roofline["launches_per_step"] = gemv[0] / prof_steps
-        roofline["avg_launch_us"] = gemv[1] / gemv[0] / 1e3
-        roofline["algorithmic_bytes_per_launch"] = alg_bytes_per_step / (gemv[0] / prof_steps)
+        roofline["traffic"] = int(per_launch[dom] * traffic_ratio[dom])
+        roofline["timing"] = "CUDA event pair around each launch in a separate pass of 4 decode steps (launches serialised)"
+    # the whole step against the same peak: self-consistent by construction
+    step_roofline = {"bytes_per_token": weight_bytes + kv_now, "ms_per_step": ms / K,
+                     "achieved": (weight_bytes + kv_now) / (ms / K / 1e3) / 1e9, "unit": "GB/s"}
+    step_roofline["frac"] = step_roofline["achieved"] / peak
     kernel_share = {k: {"launches_per_step": v[0] / prof_steps, "us_per_step": v[1] / 1e3 / prof_steps}
                     for k, v in sorted(by_kernel.items(), key=lambda kv_: -kv_[1][1])}
+    kernel_share["_note"] = ("event pairs serialise the launches and add ~6 µs each: with many small launches the sum exceeds "
+                             "ms_per_step; shares, not absolutes")
 
     sweep = gemv_sweep(backend, C2_SHAPES, [1], peak) if rank == 0 else None
+    resident = sess.resident_bytes()
 
     cpu = None
     if cpu_module is not None:
         try:
             tps, dt = cpu_reference_run(cfg, cpu_module, 6, 1, threads)
             cpu = {"value": tps, "unit": "tok/s", "cores": threads, "kind": "port",
-                   "sample": "6 decode steps after a 4-token prompt, same weights"}
+                   "sample": "6 decode steps after a 4-token prompt, same weights (the full 512-token prompt is what "
+                             "`--impl reference` runs)"}
         except Exception as e:  # the baseline is a report, never a reason to lose the measurement
             cpu = {"value": None, "unit": "tok/s", "cores": threads, "kind": "port", "sample": f"failed: {e}"}
+
+    c5_tp = None
+    if world > 1 and not args.no_tp:
+        # the 27B-architecture slice, tensor-parallel over the launched ranks (strong scaling; the headline above stays replicas)
+        del lm, sess, kv, masks, tok
+        import types
+        gloo = dist.new_group(backend="gloo")
+        tp_args = types.SimpleNamespace(layers=8, vocab=32768, batch=64, context=2048, steps=10, warmup=3)
+        try:
+            c5_tp = run_c5(tp_args, rank, local_rank, world, gloo)
+            c5_tp["tp_vs_single_max_abs"] = tp_agreement(rank, local_rank, world, gloo)
+            c5_tp["note"] = ("8 of the 62 layers at full width and a 32k vocabulary; strong scaling: the same 64 sequences on "
+                             "every rank count; one ncclAllReduce after the attention block and one after the FFN block")
+        except Exception as e:  # never lose the headline measurement to the side measurement
+            c5_tp = {"error": str(e)[:300]}
 
     if rank == 0:
         kv_bytes = cfg.kv_bytes_per_token(past + W + K // 2)
@@ -553,10 +641,11 @@ def main():
             "e2e": {"value": max(e2e_val, e2e_native_val), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "path": "ox_llm_step: upload(ids, mask) → run → device argmax → download(token id), per step",
                     "python_loop": e2e_val, "with_logits_download_and_host_argmax": e2e_logits_val},
-            "roofline": roofline, "cpu_baseline": cpu,
+            "roofline": roofline, "step_roofline": step_roofline, "cpu_baseline": cpu,
             "model_roofline": {"bytes_per_token": weight_bytes + kv_bytes, "tok_s_at_peak": peak * 1e9 / (weight_bytes + kv_bytes),
                                "frac": value / world / (peak * 1e9 / (weight_bytes + kv_bytes))},
-            "gemv_sweep": sweep, "planner": plan_stats, "kernels": kernel_share, "resident_bytes": sess.resident_bytes(), "model_build_s": build_s,
+            "gemv_sweep": sweep, "planner": plan_stats, "kernels": kernel_share, "resident_bytes": resident, "model_build_s": build_s,
+            "c5_tp": c5_tp,
         }
         print(json.dumps(line))
     if world > 1:

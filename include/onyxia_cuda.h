@@ -200,11 +200,14 @@ typedef struct ox_backend_options {
     int32_t without_fused_kernels; /* ≙ WgpuBackend::without_fused_kernels (session.rs:125-134) */
     int32_t disable_graphs;        /* launch kernels one by one instead of replaying CUDA graphs */
     int32_t disable_pattern_fusion;/* keep every node its own launch (no cross-node fusion) */
-    int32_t reserved[5];
+    int32_t disable_persistent_step; /* one launch per operation of a decode step instead of the persistent step kernel */
+    int32_t reserved[4];
 } ox_backend_options;
 
 /* One backend per process and device set. `device_ordinals` lists the CUDA
- * devices (1 entry = single GPU). */
+ * devices. A backend drives ONE device — the first of the list; further entries are checked for
+ * validity and otherwise unused. Several GPUs are used by running one process (one backend) per
+ * GPU and joining them into a tensor-parallel group, see below. */
 ox_status ox_backend_create(const int32_t* device_ordinals, int32_t n_devices, ox_backend** out);
 ox_status ox_backend_create_ex(const int32_t* device_ordinals, int32_t n_devices,
                                const ox_backend_options* options, ox_backend** out);
@@ -215,7 +218,10 @@ void ox_backend_free(ox_backend*);
  * `world` ranks have joined). A joined backend executes the `onyxia.AllReduce` composites that
  * ox_module_tp_partition inserts as NCCL all-reduces on the session's stream.
  * `nccl_library_path` names libnccl.so.2 when the process has not loaded NCCL yet (NULL: search
- * the loader path); the library is opened at run time, so nothing here is needed on one GPU. */
+ * the loader path); the library is opened at run time, so nothing here is needed on one GPU.
+ * The group's communicator lives until the process exits: ox_backend_free on a joined backend
+ * does not tear it down (destroying or aborting an NCCL communicator while the host language's
+ * runtime shuts down was seen to block). */
 ox_status ox_tp_unique_id(const char* nccl_library_path, uint8_t out[128]);
 ox_status ox_backend_join_tp(ox_backend*, int32_t rank, int32_t world, const uint8_t id[128], const char* nccl_library_path);
 /* ≙ Backend::supports (backend.rs:28-31): 1 if a fused kernel is registered under this name. */

@@ -54,7 +54,7 @@ class TensorTypeC(C.Structure):
 class BackendOptions(C.Structure):
     _fields_ = [
         ("without_fused_kernels", C.c_int32), ("disable_graphs", C.c_int32),
-        ("disable_pattern_fusion", C.c_int32), ("reserved", C.c_int32 * 5),
+        ("disable_pattern_fusion", C.c_int32), ("disable_persistent_step", C.c_int32), ("reserved", C.c_int32 * 4),
     ]
 
 

@@ -173,12 +173,14 @@ class CudaBackend:
     """≙ ``impl Backend`` (session.rs:107-242)."""
 
     def __init__(self, devices: Sequence[int] = (0,), *, without_fused_kernels: bool = False,
-                 disable_graphs: bool = False, disable_pattern_fusion: bool = False):
+                 disable_graphs: bool = False, disable_pattern_fusion: bool = False,
+                 disable_persistent_step: bool = False):
         self._lib = _ffi.cuda_lib()
         opts = _ffi.BackendOptions()
         opts.without_fused_kernels = int(without_fused_kernels)
         opts.disable_graphs = int(disable_graphs)
         opts.disable_pattern_fusion = int(disable_pattern_fusion)
+        opts.disable_persistent_step = int(disable_persistent_step)
         devs = (C.c_int32 * max(len(devices), 1))(*devices)
         h = C.c_void_p()
         check(self._lib.ox_backend_create_ex(devs, len(devices), C.byref(opts), C.byref(h)))

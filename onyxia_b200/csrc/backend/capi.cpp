@@ -26,6 +26,7 @@ ox_status ox_backend_create_ex(const int32_t* device_ordinals, int32_t n_devices
         opt.without_fused = options->without_fused_kernels != 0;
         opt.disable_graphs = options->disable_graphs != 0;
         opt.disable_pattern_fusion = options->disable_pattern_fusion != 0;
+        opt.disable_persist = options->disable_persistent_step != 0;
     }
     auto* b = new ox_backend();
     try {

@@ -3,6 +3,8 @@
 // machines without a GPU, never touch NCCL).
 #include <dlfcn.h>
 
+#include <mutex>
+
 #include <cstring>
 
 #include "runtime.hpp"
@@ -29,12 +31,17 @@ struct NcclApi {
 
 NcclApi& nccl(const char* path) {
     static NcclApi api;
+    static std::mutex mu;  // two backends may join from different host threads
+    std::lock_guard<std::mutex> lock(mu);
     if (api.lib) return api;
     // a process that already loaded NCCL (torch does) shares that copy
     void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
     if (!lib && path && *path) lib = dlopen(path, RTLD_NOW | RTLD_GLOBAL);
     if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-    if (!lib) fail(ErrKind::Runtime, std::string("cannot load NCCL: ") + (dlerror() ? dlerror() : "libnccl.so.2 not found"));
+    if (!lib) {
+        const char* why = dlerror();  // the call clears the message: read it once
+        fail(ErrKind::Runtime, std::string("cannot load NCCL: ") + (why ? why : "libnccl.so.2 not found"));
+    }
     auto sym = [&](const char* name) {
         void* p = dlsym(lib, name);
         if (!p) fail(ErrKind::Runtime, std::string("NCCL symbol missing: ") + name);

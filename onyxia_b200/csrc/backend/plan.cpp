@@ -9,6 +9,8 @@
 #include <algorithm>
 #include <chrono>
 #include <climits>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include <cuda.h>
@@ -353,7 +355,7 @@ std::unique_ptr<Plan> Session::build_plan(const Bindings& bindings_in, const std
     plan->trefs.assign(nv, TRef{});
     plan->arena_size.assign(nv, 0);
     plan->node_recs.assign(m.nodes.size(), {0, 0});
-    plan->dyn_host.assign(m.nodes.size() * oxk::kDynPerNode, 0);
+    plan->dyn_host.assign(m.nodes.size() * oxk::kDynPerNode + 1, 0);  // the last slot holds the run's epoch
     plan->node_bucket.assign(m.nodes.size(), 0);
     plan->node_bucket_step.assign(m.nodes.size(), 0);
     plan->structure = structure_key(inputs, kv_in_place);
@@ -384,6 +386,7 @@ std::unique_ptr<Plan> Session::build_plan(const Bindings& bindings_in, const std
     plan->recs = std::move(em.recs);
     plan->bindings = bindings;
     finish_outputs(*plan);
+    fuse_persistent(*plan);
     plans_built++;
     return plan;
 }
@@ -427,8 +430,73 @@ bool Session::update_plan(Plan& plan, const Bindings& bindings_in, const std::ve
     plan.scratch_bytes = scratch;
     plan.bindings = bindings;
     finish_outputs(plan);
+    fuse_persistent(plan);
     plans_updated++;
     return true;
+}
+
+// Builds the list of launches a run executes. Every maximal run of consecutive records that carry a
+// persistent-operation descriptor becomes one launch of the persistent step kernel; the launch is
+// rebuilt only when the operations it was built from changed.
+void Session::fuse_persistent(Plan& plan) {
+    static const bool disabled = [] {
+        const char* e = std::getenv("ONYXIA_DISABLE_PERSIST");  // diagnostics: keep one launch per operation
+        return e && std::atoi(e) != 0;
+    }();
+    const bool enabled = !disabled && !opt_.without_fused && !opt_.disable_pattern_fusion && !opt_.disable_persist;
+    const auto& recs = plan.recs;
+    const size_t max_ops = (size_t)oxk::persist_max_ops();
+    const Buf epoch{oxk::kSlotDyn, (int64_t)((plan.dyn_host.size() - 1) * sizeof(int64_t))};
+    plan.launches.clear();
+    std::vector<Plan::PersistRun> runs;
+    size_t xoff = 0, i = 0;
+    while (i < recs.size()) {
+        size_t j = i;
+        while (enabled && j < recs.size() && recs[j].pop && j - i < max_ops) j++;
+        if (j - i >= 2) {
+            Plan::PersistRun run;
+            const size_t idx = runs.size();
+            bool cached = idx < plan.persist_runs.size() && plan.persist_runs[idx].ops.size() == j - i && plan.persist_runs[idx].xoff == xoff;
+            for (size_t k = i; cached && k < j; k++) cached = oxk::same_op(plan.persist_runs[idx].ops[k - i], *recs[k].pop);
+            if (cached) {
+                run = std::move(plan.persist_runs[idx]);
+            } else {
+                std::vector<const oxk::PersistOp*> ops;
+                for (size_t k = i; k < j; k++) {
+                    run.ops.push_back(*recs[k].pop);
+                    ops.push_back(recs[k].pop.get());
+                }
+                run.xoff = xoff;
+                std::string why;
+                run.ok = oxk::build_persist_launch(ops, epoch, &run.launch, &why);
+                static const bool debug = std::getenv("ONYXIA_PERSIST_DEBUG") != nullptr;  // diagnostics
+                if (debug) std::fprintf(stderr, "persistent step: %zu operations: %s\n", ops.size(), run.ok ? "fused" : why.c_str());
+                if (run.ok)  // this run's words live after those of the runs before it
+                    for (auto& rl : run.launch.rec.relocs)
+                        if (rl.buf.slot == oxk::kSlotXbuf) rl.buf.off += (int64_t)xoff;
+            }
+            const bool ok = run.ok;
+            if (ok) xoff += (run.launch.xbuf_bytes + 255) / 256 * 256;
+            runs.push_back(std::move(run));
+            if (ok) {
+                plan.launches.push_back(nullptr);  // patched below, once `runs` no longer moves
+                i = j;
+                continue;
+            }
+        }
+        if (j == i) j = i + 1;
+        for (size_t k = i; k < j; k++) plan.launches.push_back(&recs[k]);
+        i = j;
+    }
+    plan.persist_runs = std::move(runs);
+    size_t r = 0;
+    for (auto& l : plan.launches)
+        if (!l) {
+            while (!plan.persist_runs[r].ok) r++;
+            l = &plan.persist_runs[r++].launch.rec;
+        }
+    plan.xbuf_bytes = xoff;
+    if (xoff) plan.dyn_used = true;
 }
 
 void Session::lower_prim(oxk::Emitter& em, const Node& node, const Bindings& b, const std::vector<TRef>& ins,
@@ -519,7 +587,15 @@ std::vector<Timing> Session::take_timings() {
 // Encodes a tiled 2-D f16 tensor map (128-byte swizzle, zero fill outside the tensor) for the address a
 // record's tensor has in this run. The driver entry point is looked up through the runtime, so the
 // library still has no link-time dependency on the driver.
-static void encode_tensor_map(const oxk::TmapReloc& tm, void* base, uint8_t* dst) {
+static void encode_tensor_map(const oxk::TmapReloc& tm, void* base, uint8_t* params) {
+    uint8_t* dst = params + tm.field_off;
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) {
+        // only known now: the tensor is a view at an odd offset of its buffer
+        if (tm.enable_off == 0xFFFFFFFFu) fail(ErrKind::Runtime, "a tensor read through a tensor map is not 16-byte aligned");
+        const int32_t off = 0;
+        std::memcpy(params + tm.enable_off, &off, sizeof(off));
+        return;
+    }
     using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -558,8 +634,17 @@ void Session::launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_
     cfg.blockDim = r.block;
     cfg.dynamicSmemBytes = r.smem;
     cfg.stream = stream_;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[3];
     unsigned n_attr = 0;
+    static const bool coop_off = [] {
+        const char* e = std::getenv("ONYXIA_PERSIST_COOP");  // diagnostics: "0" launches the persistent kernel the ordinary way
+        return e && std::atoi(e) == 0;
+    }();
+    if (r.cooperative && !coop_off) {
+        attr[n_attr].id = cudaLaunchAttributeCooperative;
+        attr[n_attr].val.cooperative = 1;
+        n_attr++;
+    }
     if (allow_pdl && r.pdl) {
         attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
@@ -589,13 +674,13 @@ void Session::build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& p
     plan.graph_nodes.clear();
     OX_CUDA(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeRelaxed));
     try {
-        for (size_t i = 0; i < plan.recs.size(); i++) {
-            launch_rec(plan.recs[i], const_cast<uint8_t*>(params[i].data()), !opt_.disable_pdl);
+        for (size_t i = 0; i < plan.launches.size(); i++) {
+            launch_rec(*plan.launches[i], const_cast<uint8_t*>(params[i].data()), !opt_.disable_pdl);
             cudaStreamCaptureStatus status;
             const cudaGraphNode_t* deps = nullptr;
             size_t n_deps = 0;
             OX_CUDA(cudaStreamGetCaptureInfo_v3(stream_, &status, nullptr, nullptr, &deps, nullptr, &n_deps));
-            if (plan.recs[i].coll) {  // a collective may record several nodes; it is never patched in place
+            if (plan.launches[i]->coll) {  // a collective may record several nodes; it is never patched in place
                 plan.graph_nodes.push_back(nullptr);
                 continue;
             }
@@ -615,7 +700,13 @@ void Session::build_graph(Plan& plan, const std::vector<std::vector<uint8_t>>& p
     OX_CUDA(cudaGraphInstantiate(&plan.exec, plan.graph, 0));
     plan.graph_params = params;
     plan.graph_grids.clear();
-    for (auto& r : plan.recs) plan.graph_grids.push_back(r.grid);
+    plan.graph_clusters.clear();
+    plan.graph_funcs.clear();
+    for (auto* r : plan.launches) {
+        plan.graph_grids.push_back(r->grid);
+        plan.graph_clusters.push_back(r->cluster);
+        plan.graph_funcs.push_back(r->func);
+    }
 }
 
 void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vector<BufferRef>& out_bufs) {
@@ -625,6 +716,15 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
         plan.arena = pool_->alloc(plan.arena_bytes + plan.scratch_bytes * 2 + 512);
     }
     if (plan.dyn_used && !plan.dyn_dev) plan.dyn_dev = pool_->alloc(plan.dyn_host.size() * sizeof(int64_t));
+    if (plan.xbuf_bytes && (!plan.xbuf || plan.xbuf->bytes < plan.xbuf_bytes)) {
+        // tags of earlier epochs never match again, so only a fresh area has to be cleared
+        plan.xbuf = pool_->alloc(plan.xbuf_bytes);
+        OX_CUDA(cudaMemsetAsync(plan.xbuf->ptr, 0, plan.xbuf->bytes, stream_));
+    }
+    if (plan.xbuf_bytes) {  // a fresh non-zero 32-bit tag for this run's words
+        if ((++plan.epoch & 0xFFFFFFFFull) == 0) ++plan.epoch;
+        plan.dyn_host.back() = (int64_t)(plan.epoch & 0xFFFFFFFFull);
+    }
     char* arena_base = (char*)plan.arena->ptr;
     size_t scratch_off = (plan.arena_bytes + 255) / 256 * 256;
 
@@ -641,6 +741,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
             case oxk::kSlotCounters: return (void*)d_counters_;
             case oxk::kSlotDyn: return (char*)plan.dyn_dev->ptr + buf.off;
             case oxk::kSlotScratch: return arena_base + scratch_off + buf.off;
+            case oxk::kSlotXbuf: return (char*)plan.xbuf->ptr + buf.off;
             default: break;
         }
         const ValueLoc& l = plan.loc[buf.slot];
@@ -672,7 +773,7 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
     }
 
     plan.uses++;
-    const size_t n = plan.recs.size();
+    const size_t n = plan.launches.size();
     bool use_graph = !profiling && !opt_.disable_graphs && n >= 2 && plan.uses >= 2;
 
     if (use_graph) {
@@ -681,18 +782,25 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
         static thread_local std::vector<std::vector<uint8_t>> params;
         params.resize(n);
         for (size_t i = 0; i < n; i++) {
-            const oxk::LaunchRec& r = plan.recs[i];
+            const oxk::LaunchRec& r = *plan.launches[i];
             params[i].assign(r.params.begin(), r.params.end());
             for (auto& rl : r.relocs) {
                 void* p = resolve(rl.buf);
                 std::memcpy(params[i].data() + rl.field_off, &p, sizeof(void*));
             }
-            for (auto& tm : r.tmaps) encode_tensor_map(tm, resolve(tm.buf), params[i].data() + tm.field_off);
+            for (auto& tm : r.tmaps) encode_tensor_map(tm, resolve(tm.buf), params[i].data());
         }
         if (!rebuild) {
             for (size_t i = 0; i < n && !rebuild; i++) {
-                const oxk::LaunchRec& r = plan.recs[i];
+                const oxk::LaunchRec& r = *plan.launches[i];
                 bool same_grid = plan.graph_grids[i].x == r.grid.x && plan.graph_grids[i].y == r.grid.y && plan.graph_grids[i].z == r.grid.z;
+                // The cluster shape and the cooperative attribute belong to the captured node and cannot be
+                // patched: a launch that changed either (or its kernel) has the graph recorded again.
+                const dim3& gc = plan.graph_clusters[i];
+                if (gc.x != r.cluster.x || gc.y != r.cluster.y || gc.z != r.cluster.z || plan.graph_funcs[i] != r.func) {
+                    rebuild = true;
+                    break;
+                }
                 if (same_grid && params[i] == plan.graph_params[i]) continue;
                 if (r.coll) {  // the buffers of a captured collective moved: record the graph again
                     rebuild = true;
@@ -723,13 +831,13 @@ void Session::execute(Plan& plan, const std::vector<DTensor>& inputs, std::vecto
     } else {
         std::vector<uint8_t> params;
         for (size_t i = 0; i < n; i++) {
-            const oxk::LaunchRec& r = plan.recs[i];
+            const oxk::LaunchRec& r = *plan.launches[i];
             params = r.params;
             for (auto& rl : r.relocs) {
                 void* p = resolve(rl.buf);
                 std::memcpy(params.data() + rl.field_off, &p, sizeof(void*));
             }
-            for (auto& tm : r.tmaps) encode_tensor_map(tm, resolve(tm.buf), params.data() + tm.field_off);
+            for (auto& tm : r.tmaps) encode_tensor_map(tm, resolve(tm.buf), params.data());
             void* args[1] = {params.data()};
             ProfRec pr{};
             if (profiling) {

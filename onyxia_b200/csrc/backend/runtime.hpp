@@ -90,6 +90,7 @@ struct Options {
     bool disable_graphs = false;
     bool disable_pattern_fusion = false;
     bool disable_pdl = false;  // launch every kernel fully serialised
+    bool disable_persist = false;  // one launch per operation instead of the persistent step kernel
 };
 
 class Session;

@@ -756,8 +756,8 @@ void Session::argmax_last_into(const DTensor& logits, const DTensor& out) {
         fail(ErrKind::Shape, "argmax needs a tensor with a non-empty last axis");
     if (logits.cap != 0) fail(ErrKind::Shape, "argmax: logits must be densely packed");
     const int64_t cols = logits.shape.back(), rows = logits.numel() / cols;
-    if (out.dtype != DType::I64 || !out.buf || out.numel() != rows)
-        fail(ErrKind::Shape, "argmax: the result tensor must be I64 with one element per row of the logits");
+    if (out.dtype != DType::I64 || !out.buf || out.numel() != rows || out.cap != 0)
+        fail(ErrKind::Shape, "argmax: the result tensor must be a densely packed I64 tensor with one element per row of the logits");
     const char* err = oxk::argmax_last_static(device_, stream_, logits.ptr(), (int)logits.dtype, rows, cols,
                                               (long long*)out.ptr());
     if (err) fail(ErrKind::Runtime, err);

@@ -4,6 +4,7 @@
 #include <list>
 
 #include "runtime.hpp"
+#include "../kernels/persist.hpp"
 
 namespace oxrt {
 
@@ -60,12 +61,26 @@ struct Plan {
     int64_t* dyn_pinned = nullptr;               // kDynRing staging copies of dyn_host
     cudaEvent_t dyn_events[kDynRing] = {};
     unsigned dyn_cursor = 0;
+    // What a run executes: the records of `recs`, with every run of consecutive records that the
+    // persistent step kernel can execute replaced by one launch of it.
+    struct PersistRun {
+        std::vector<oxk::PersistOp> ops;  // what the launch was built from (compared on every re-lowering)
+        bool ok = false;                  // false: the run was found unsuitable, its records launch one by one
+        size_t xoff = 0;                  // where the run's words start in the exchange area
+        oxk::PersistLaunch launch;
+    };
+    std::vector<PersistRun> persist_runs;
+    std::vector<const oxk::LaunchRec*> launches;
+    BufferRef xbuf;                              // exchange area of the persistent launches (tagged words)
+    size_t xbuf_bytes = 0;
+    uint64_t epoch = 0;                          // tags the words of one run; never repeats within a plan
     // CUDA graph of the launch list, with the launch state each node currently holds.
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     std::vector<cudaGraphNode_t> graph_nodes;
     std::vector<std::vector<uint8_t>> graph_params;
-    std::vector<dim3> graph_grids;
+    std::vector<dim3> graph_grids, graph_clusters;
+    std::vector<const void*> graph_funcs;
     uint64_t uses = 0;
     ~Plan();
 };
@@ -153,6 +168,7 @@ private:
     void lower_prim(oxk::Emitter& em, const Node& node, const ox::Bindings& b, const std::vector<oxk::TRef>& ins,
                     const std::vector<oxk::TRef>& outs);
     void finish_outputs(Plan& plan);
+    void fuse_persistent(Plan& plan);
     void execute(Plan& plan, const std::vector<DTensor>& inputs, std::vector<BufferRef>& out_bufs);
     Plan* plan_for(const std::vector<std::pair<std::string, DTensor>>& named, std::vector<DTensor>& inputs, bool shapes_only,
                    double* t_bound_out);

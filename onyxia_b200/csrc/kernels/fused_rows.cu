@@ -71,7 +71,7 @@ void emit_softmax(Emitter& em, const TRef& x, const TRef& y) {
     p.cols = x.shape.empty() ? 1 : x.shape.back();
     p.rows = p.cols ? x.numel() / p.cols : 0;
     if (p.rows == 0 || p.cols == 0) return;
-    dim3 g((unsigned)std::min<long long>(p.rows, 148 * 32)), b(256);
+    dim3 g((unsigned)std::min<long long>(p.rows, sm_count() * 32LL)), b(256);
     if (x.dtype == DT_F32) em.launch(fused_softmax<DT_F32>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "fused_softmax");
     else em.launch(fused_softmax<DT_F16>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "fused_softmax");
 }
@@ -159,7 +159,7 @@ void emit_rmsnorm(Emitter& em, const TRef& x, const TRef& w, const TRef& y, doub
     // ≤ 4 elements per thread where the row allows it, warps of whole lanes
     long long threads = std::min<long long>(1024, std::max<long long>(64, ((p.cols + 3) / 4 + 31) / 32 * 32));
     long long ept = (p.cols + threads - 1) / threads;
-    dim3 g((unsigned)std::min<long long>(p.rows, 148 * 32)), b((unsigned)threads);
+    dim3 g((unsigned)std::min<long long>(p.rows, sm_count() * 32LL)), b((unsigned)threads);
     Buf rb = res ? res->buf : Buf{kSlotNull, 0}, sb = sum_out ? sum_out->buf : Buf{kSlotNull, 0};
 #define GO(DT, E) \
     em.launch(fused_rmsnorm<DT, E>, g, b, 0, p, {{&p.x, x.buf}, {&p.res, rb}, {&p.w, w.buf}, {&p.y, y.buf}, {&p.sum_out, sb}}, "fused_rmsnorm", /*pdl=*/true)

@@ -376,7 +376,7 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
     // Split the visible key range so that the launch fills the machine; the
     // arrival counters bound the number of queries a split launch may have.
     long long queries = B * KV * ap.groups * S;
-    long long want = (148 * 4 + queries - 1) / queries;   // ≈ 4 CTAs per SM
+    long long want = (sm_count() * 4LL + queries - 1) / queries;   // ≈ 4 CTAs per SM
     long long max_split = (ap.span + 7) / 8;              // ≥ 8 keys per CTA (two per warp)
     long long nsplit = std::max<long long>(1, std::min<long long>(want, max_split));
     if (2 * queries > (long long)kCounterWords) nsplit = 1;

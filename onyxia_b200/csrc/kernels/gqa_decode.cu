@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "persist.hpp"
 
 namespace oxk {
 
@@ -434,7 +435,10 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         my_lo = lo + (long long)rank * chunk;
         my_n = n - rank * chunk;
         my_n = my_n < 0 ? 0 : (my_n > chunk ? chunk : my_n);
-        if (my_n > p.chunk_max) my_n = p.chunk_max;  // cannot happen for a launch sized by the host; never index past the rows
+        if (my_n > p.chunk_max) {  // a launch whose cluster shape and key capacity disagree: say so, never index past the rows
+            if (tid == 0) report(p.err, ERR_SLICE_OOB, p.node, my_n, p.chunk_max);
+            my_n = p.chunk_max;
+        }
         n_blocks = (my_n + kKeyBlock - 1) / kKeyBlock;
         owns_new = qpos <= T - 1 && n > 0 && (int)((hi - lo) / chunk) == rank;
     };
@@ -726,15 +730,7 @@ bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf 
         fn = gqa_decode_h<DPL, GT>;
     }
     if (smem > 224 * 1024) return false;
-    // once per kernel instantiation (and per device the process uses): this runs on every re-lowering of a decode step
-    static int attr_device = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (smem > 48 * 1024 && attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-        if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-        attr_device = dev;
-    }
+    if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)fn, 224 * 1024);  // cached per device and kernel
     GqaDecP p = p0;
     em.launch(fn, grid, dim3(kThreads), (unsigned)smem, p,
               {{&p.q, bufs[0]}, {&p.k, bufs[1]}, {&p.v, bufs[2]}, {&p.cache_k, bufs[3]}, {&p.cache_v, bufs[4]},
@@ -784,7 +780,7 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     const long long pairs = B * KV * groups;
     int cx = span > 128 ? 8 : span > 64 ? 4 : span > 32 ? 2 : 1;
     int cx_fill = 1;
-    while (cx_fill < 8 && pairs * cx_fill * 2 <= 296) cx_fill <<= 1;
+    while (cx_fill < 8 && pairs * cx_fill * 2 <= 2 * sm_count()) cx_fill <<= 1;
     int cx_long = 1;  // a single CTA streams a long key range slowly: at most ≈ 1 024 keys each
     while (cx_long < 8 && span > 1024LL * cx_long) cx_long <<= 1;
     if (cx > std::max(cx_fill, cx_long)) cx = std::max(cx_fill, cx_long);
@@ -806,8 +802,35 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     const Buf bufs[11] = {q.buf, k.buf, v.buf, present_k.buf, present_v.buf, seqlens.buf, cos ? cos->buf : null,
                           sin ? sin->buf : null, out.buf, Buf{kSlotErr, 0}, dyn_t};
     dim3 grid((unsigned)cx, (unsigned)(KV * groups), (unsigned)B);
-    return q.dtype == DT_F16 ? launch_decode_g<DT_F16>(em, p, grid, cx, bufs, D, GT)
-                             : launch_decode_g<DT_F32>(em, p, grid, cx, bufs, D, GT);
+    const bool ok = q.dtype == DT_F16 ? launch_decode_g<DT_F16>(em, p, grid, cx, bufs, D, GT)
+                                      : launch_decode_g<DT_F32>(em, p, grid, cx, bufs, D, GT);
+    // A single sequence in f16: the launch can also run as an operation of the persistent step kernel.
+    if (ok && B == 1 && q.dtype == DT_F16 && D >= 64 && G <= 8 && p.cap < (1LL << 31) && d.cache_rows < (1LL << 31)) {
+        auto op = std::make_shared<PersistOp>();
+        op->kind = POP_ATTN;
+        op->node = em.node;
+        op->q = q.buf;
+        op->kx = k.buf;
+        op->vx = v.buf;
+        op->cache_k = present_k.buf;
+        op->cache_v = present_v.buf;
+        op->seqlens = seqlens.buf;
+        if (cos) op->cos = cos->buf;
+        if (sin) op->sin = sin->buf;
+        op->out = out.buf;
+        op->dyn_t = dyn_t;
+        op->H = H;
+        op->KV = KV;
+        op->D = D;
+        op->cap = p.cap;
+        op->window = d.window;
+        op->half = d.rot_half;
+        op->cache_rows = d.cache_rows;
+        op->span = span;
+        op->scale = p.scale;
+        em.recs.back().pop = std::move(op);
+    }
+    return ok;
 }
 
 }  // namespace oxk

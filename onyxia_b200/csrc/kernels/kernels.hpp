@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <cmath>
 #include <initializer_list>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -74,7 +75,13 @@ struct TmapReloc {
     uint64_t dim0, dim1;     // extents in elements: contiguous axis, outer axis
     uint64_t stride1_bytes;  // bytes between outer rows (a multiple of 16)
     uint32_t box0, box1;     // tile extents in elements (box0·2 ≤ 128 bytes with the 128-byte swizzle)
+    // Byte offset of an int32 field of the parameter struct that the kernel reads as "use the map"; it is
+    // cleared when the tensor's address in a run turns out not to be 16-byte aligned (the kernel then takes
+    // its plain-load path). 0xFFFFFFFF: no such field, a misaligned tensor is an error.
+    uint32_t enable_off = 0xFFFFFFFFu;
 };
+
+struct PersistOp;  // persist.hpp
 
 struct LaunchRec {
     const void* func = nullptr;
@@ -91,10 +98,19 @@ struct LaunchRec {
     // to its exit. Such a kernel may be launched while its predecessor in the
     // stream is still running (programmatic dependent launch): its prologue —
     // barrier set-up, prefetch of constant weights — overlaps the predecessor.
+    // Every such kernel triggers its own dependents at entry, so the section
+    // before its wait may overlap not only the launch before it but several
+    // earlier ones: it may read only memory that NO launch of the same run
+    // writes (constants, rows of a KV cache below the step's first new row).
     bool pdl = false;
     // Not a kernel of this library: a collective the session enqueues itself. The parameter bytes
     // are a CollP (with the usual pointer relocations); `func` is null.
     int coll = 0;  // 1 = sum over the tensor-parallel ranks
+    // The grid's CTAs wait on one another: the launch must be cooperative (all CTAs co-resident).
+    bool cooperative = false;
+    // What this launch does, in the form the persistent step kernel executes: a run of consecutive
+    // launches that all carry one can be replaced by a single launch of that kernel.
+    std::shared_ptr<const PersistOp> pop;
 };
 
 struct CollP {
@@ -174,7 +190,13 @@ struct TRef {
     }
 };
 
-inline unsigned grid_for(int64_t n, int block, int64_t max_blocks = 148 * 16) {
+// Streaming multiprocessors of the current device (cached per device; thread-safe).
+int sm_count();
+// Raises a kernel's dynamic shared-memory limit on the current device once (thread-safe); throws on failure.
+void ensure_max_dynamic_smem(const void* func, int bytes);
+
+inline unsigned grid_for(int64_t n, int block, int64_t max_blocks = 0) {
+    if (max_blocks <= 0) max_blocks = (int64_t)sm_count() * 16;
     int64_t g = (n + block - 1) / block;
     if (g < 1) g = 1;
     if (g > max_blocks) g = max_blocks;

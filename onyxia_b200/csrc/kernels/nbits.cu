@@ -96,7 +96,7 @@ template <int ADT, int SDT> static void launch_gemv(Emitter& em, NBitsGemvP p, c
                                                     const TRef& scales, const TRef* zp, const TRef& y) {
     Buf zb = zp ? zp->buf : Buf{kSlotNull, 0};
     long long warps = p.n;
-    dim3 g((unsigned)std::min<long long>((warps + 7) / 8, 148 * 8)), b(256);
+    dim3 g((unsigned)std::min<long long>((warps + 7) / 8, sm_count() * 8LL)), b(256);
     for (long long m0 = 0; m0 < p.m_total; m0 += 8) {
         p.m0 = m0;
         long long left = p.m_total - m0;

@@ -236,7 +236,7 @@ void emit_matmul_nbits_mma(Emitter& em, const NBitsDesc& d, const TRef& a, const
         int v = e ? std::atoi(e) : 4;
         return v < 1 ? 1 : v;
     }();
-    long long want = (148 * ctas_per_sm + p.row_tiles - 1) / p.row_tiles;
+    long long want = ((long long)sm_count() * ctas_per_sm + p.row_tiles - 1) / p.row_tiles;
     long long max_split = (p.k_tiles + 3) / 4;
     p.ksplit = (int)std::max<long long>(1, std::min<long long>(want, max_split));
     p.tiles_per_split = (p.k_tiles + p.ksplit - 1) / p.ksplit;

@@ -35,6 +35,7 @@
 
 #include "common.cuh"
 #include "kernels.hpp"
+#include "persist.hpp"
 
 namespace oxk {
 
@@ -776,10 +777,11 @@ void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TR
     // tuning knob: resident CTAs per SM the grid should fill
     static const int ctas_per_sm = env_int("ONYXIA_GEMV_CTAS_PER_SM", 2, 1, 8);
     auto split = [&](int per_sm, int* rts, long long* grid, long long* load) {
-        *rts = (int)((p.row_tiles + 148LL * per_sm - 1) / (148LL * per_sm));
+        const long long sms = sm_count();
+        *rts = (int)((p.row_tiles + sms * per_sm - 1) / (sms * per_sm));
         if (gr.geglu) *rts = (*rts + 1) & ~1;  // a CTA holds whole gate/up pairs
         *grid = (p.row_tiles + *rts - 1) / *rts;
-        *load = ((*grid + 147) / 148) * *rts;  // row tiles the busiest SM streams
+        *load = ((*grid + sms - 1) / sms) * *rts;  // row tiles the busiest SM streams
     };
     long long grid, load;
     split(ctas_per_sm, &p.rts_per_cta, &grid, &load);
@@ -817,16 +819,38 @@ void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TR
         p.aux_bytes = (int)aux_bytes(mr);
         const size_t smem = (size_t)p.act_bytes + p.aux_bytes + fixed;
         StreamFn fn = gr.has_zp ? stream_fn<true>(mr) : stream_fn<false>(mr);
-        if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
-            if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-        }
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)fn, (int)kSmemBudget);
         em.launch(fn, dim3((unsigned)grid), dim3(kWarps * 32), (unsigned)smem, p,
                   {{&p.a, a.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.y[0], gr.y[0].buf},
                    {&p.y[1], gr.n_seg > 1 && !gr.geglu ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null},
                    {&p.w1, gr.w1 ? gr.w1->buf : null}, {&p.res, gr.res ? gr.res->buf : null},
                    {&p.sum_out, gr.sum_out ? gr.sum_out->buf : null}, {&p.w2, gr.w2 ? gr.w2->buf : null}},
                   "nbits_stream", /*pdl=*/true);
+    }
+    // One activation row, default zero points: the launch can also run as an operation of the persistent step kernel.
+    if (gr.m == 1 && !gr.has_zp && (!gr.res || gr.sum_out)) {
+        auto op = std::make_shared<PersistOp>();
+        op->kind = POP_GEMV;
+        op->node = em.node;
+        op->a = a.buf;
+        op->tiles = tiles.buf;
+        op->n_seg = gr.n_seg;
+        op->geglu = gr.geglu;
+        op->k = gr.k;
+        for (int i = 0; i < gr.n_seg; i++) {
+            op->seg_n[i] = gr.seg_n[i];
+            if (!gr.geglu || i == 0) op->y[i] = gr.y[i].buf;
+        }
+        op->has_w1 = gr.w1 != nullptr;
+        op->has_w2 = gr.w2 != nullptr;
+        op->has_res = gr.res != nullptr;
+        if (gr.w1) op->w1 = gr.w1->buf;
+        if (gr.w2) op->w2 = gr.w2->buf;
+        if (gr.res) op->res = gr.res->buf;
+        if (gr.sum_out) op->sum_out = gr.sum_out->buf;
+        op->eps1 = gr.eps1;
+        op->eps2 = gr.eps2;
+        em.recs.back().pop = std::move(op);
     }
 }
 

@@ -403,21 +403,14 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
     p.n_acc = mb <= 128 ? 4 : 2;  // 512 columns of tensor memory per SM; two CTAs share it when mb ≤ 64
     p.use_tma = (gr.k % 8 == 0 && x.buf.off % 16 == 0) ? 1 : 0;
     const size_t smem = stage * p.stages + 1024 /*alignment slack*/ + (2 * p.stages + 1) * 8 + 16;
-    static int attr_device = -1;  // the attribute belongs to the device: set it again when the process moves on to another
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute((const void*)nbits_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-        if (e != cudaSuccess) throw std::runtime_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-        attr_device = dev;
-    }
+    ensure_max_dynamic_smem((const void*)nbits_gemm_tc, 220 * 1024);
     const Buf null{kSlotNull, 0};
     const unsigned grid = (unsigned)((p.row_tiles + 7) / 8);
     // Whole waves of row blocks take all of K. The blocks left over (all of them when there is less than one
     // wave) are cut into the number of pieces that minimises, in units of one 128-k step (≈ 1.3 µs),
     // waves × (steps per piece + about four steps of set-up and drain per CTA) + the second kernel's launch
     // and the partial sums' trip to memory and back; at least two steps per piece.
-    const long long slots = 148LL * (2 * stage <= half_sm ? 2 : 1);
+    const long long slots = (long long)sm_count() * (2 * stage <= half_sm ? 2 : 1);
     long long n_full = (long long)grid / slots * slots, tail = grid - n_full;
     if (tail * 10 >= slots * 6) {  // the last wave is well filled as it is
         n_full = grid;
@@ -456,7 +449,8 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
                    {&p.y[1], gr.n_seg > 1 ? gr.y[1].buf : null}, {&p.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
                   "nbits_gemm_tc", /*pdl=*/true);
         if (p.use_tma)
-            rec.tmaps.push_back(TmapReloc{(uint32_t)offsetof(TcP, xmap), x.buf, (uint64_t)gr.k, (uint64_t)gr.m, (uint64_t)gr.k * 2, 64u, (uint32_t)mb});
+            rec.tmaps.push_back(TmapReloc{(uint32_t)offsetof(TcP, xmap), x.buf, (uint64_t)gr.k, (uint64_t)gr.m, (uint64_t)gr.k * 2, 64u, (uint32_t)mb,
+                                          (uint32_t)offsetof(TcP, use_tma)});
         if (splits > 1) {
             TcReduceP q{};
             q.m0 = m0;

@@ -140,7 +140,7 @@ void emit_reduce(Emitter& em, int op, const TRef& x, const TRef& y, const std::v
         }
     }
     (void)y;
-    const bool per_block = p.count >= 256 && p.out_n <= 148 * 2;
+    const bool per_block = p.count >= 256 && p.out_n <= 2 * sm_count();
     dim3 g(per_block ? (unsigned)std::max<long long>(p.out_n, 1) : grid_for(p.out_n * 32, 256)), b(256);
 #define CALL(DT)                                                                                              \
     if (per_block) em.launch(prim_reduce_block<DT>, g, b, 0, p, {{&p.x, x.buf}, {&p.y, y.buf}}, "prim_reduce"); \

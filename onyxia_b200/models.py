@@ -78,7 +78,7 @@ class DecoderConfig:
         return total
 
 
-# The configurations BASELINE.json names.
+# The benchmark configurations.
 def config_c1() -> DecoderConfig:
     """2-layer Gemma-style decoder, fp32 activations/scales, explicit zero points."""
     return DecoderConfig("c1-2layer", layers=2, hidden=512, heads=8, kv_heads=2, head_dim=64, ffn=2048, vocab=32000,
