@@ -845,68 +845,45 @@ template <int D> __device__ void run_attn(const Ctx& c, const POpDev& op) {
     ptrace(c, 44);
 
     // 5. softmax over the visible keys (decomp.rs:174-183): max, exp of the rounded difference, the
-    // exact sum of the rounded exponentials, rounded quotient. Exponentials are multiples of 2⁻²⁴ not
-    // above 1: they are summed exactly as integers (one warp-wide reduction per head, one shared atomic
-    // per warp), which is what the interpreter's f64 sum gives.
+    // exact sum of the rounded exponentials, rounded quotient. A thread works on one head (lane mod G)
+    // and every (kCT / G)-th key; the lanes of a warp that share a head reduce among themselves.
+    // Exponentials are multiples of 2⁻²⁴ not above 1: summed exactly as integers, which is what the
+    // interpreter's f64 sum gives.
     {
-        float m[8];
-#pragma unroll
-        for (int hh = 0; hh < 8; hh++) m[hh] = -INFINITY;
-        for (int i = tid; i < ge.n; i += kCT)
-#pragma unroll
-            for (int hh = 0; hh < 8; hh++)
-                if (hh < G) m[hh] = fmaxf(m[hh], __half2float(s.p_s[hh * PS + i]));
-#pragma unroll
-        for (int hh = 0; hh < 8; hh++) {
-            if (hh < G) {
-                // order-preserving map of the float bits to a signed integer
-                const int bits = __float_as_int(m[hh]), key = bits >= 0 ? bits : bits ^ 0x7FFFFFFF;
-                const int wmax = __reduce_max_sync(0xffffffffu, key);
-                if (lane == 0) atomicMax(s.imax + hh, wmax);
-            }
+        const int hh = lane & (G - 1);  // G is a power of two
+        const unsigned peers = (0x01010101u * ((G == 1) ? 0xFFu : (G == 2) ? 0x55u : (G == 4) ? 0x11u : 0x01u)) << hh;
+        const int k0 = tid / G, kstep = kCT / G;
+        __half* row = s.p_s + hh * PS;
+        float m = -INFINITY;
+        for (int i = k0; i < ge.n; i += kstep) m = fmaxf(m, __half2float(row[i]));
+        {
+            // order-preserving map of the float bits to a signed integer
+            const int bits = __float_as_int(m), key = bits >= 0 ? bits : bits ^ 0x7FFFFFFF;
+            const int wmax = __reduce_max_sync(peers, key);
+            if (lane < G) atomicMax(s.imax + hh, wmax);
         }
-    }
-    consumer_sync();
-    ptrace(c, 51);
-    {
-        float gmax[8];
-        unsigned acc[8];
-#pragma unroll
-        for (int hh = 0; hh < 8; hh++) {
-            const int key = hh < G ? s.imax[hh] : 0;
-            gmax[hh] = __int_as_float(key >= 0 ? key : key ^ 0x7FFFFFFF);
-            acc[hh] = 0u;
+        consumer_sync();
+        ptrace(c, 51);
+        const int key = s.imax[hh];
+        const __half gmax = __float2half_rn(__int_as_float(key >= 0 ? key : key ^ 0x7FFFFFFF));  // an f16 value: exact
+        unsigned acc = 0u;  // a thread meets at most ⌈n·G / kCT⌉ ≤ 64 keys: below 2³⁰
+        for (int i = k0; i < ge.n; i += kstep) {
+            const __half d = __hsub(row[i], gmax);  // one rounding of the exact difference, as in the f64 domain
+            const __half e = g_exp_lut[__half_as_ushort(d) & 0x7FFF];
+            row[i] = e;
+            acc += (unsigned)(__half2float(e) * 16777216.f);
         }
-        // each thread meets at most ⌈n / kCT⌉ ≤ 8 keys, so its integer sums stay below 2²⁷
-        for (int i = tid; i < ge.n; i += kCT)
-#pragma unroll
-            for (int hh = 0; hh < 8; hh++)
-                if (hh < G) {
-                    const float sc = __half2float(s.p_s[hh * PS + i]);
-                    const __half d = __double2half((double)sc - (double)gmax[hh]);
-                    const __half e = g_exp_lut[__half_as_ushort(d) & 0x7FFF];
-                    s.p_s[hh * PS + i] = e;
-                    acc[hh] += (unsigned)(__half2float(e) * 16777216.f);
-                }
-#pragma unroll
-        for (int hh = 0; hh < 8; hh++) {
-            if (hh < G) {
-                const unsigned lo = __reduce_add_sync(0xffffffffu, acc[hh] & 0xFFFFu), hi = __reduce_add_sync(0xffffffffu, acc[hh] >> 16);
-                if (lane == 0) atomicAdd(s.isum + hh, ((unsigned long long)hi << 16) + lo);
-            }
+        {
+            const unsigned lo = __reduce_add_sync(peers, acc & 0xFFFFu), hi = __reduce_add_sync(peers, acc >> 16);
+            if (lane < G) atomicAdd(s.isum + hh, ((unsigned long long)hi << 16) + lo);
         }
-    }
-    consumer_sync();
-    ptrace(c, 52);
-    {
-        float total[8];
-#pragma unroll
-        for (int hh = 0; hh < 8; hh++) total[hh] = hh < G ? r16d((double)s.isum[hh] * 5.9604644775390625e-08) : 1.f;
+        consumer_sync();
+        ptrace(c, 52);
+        const unsigned long long tot = s.isum[hh];
+        const double totd = (double)(unsigned)(tot >> 32) * 4294967296.0 + (double)(unsigned)tot;
+        const float total = r16d(totd * 5.9604644775390625e-08);
         // e and Σ are f16 values: their f32 quotient rounds to the same f16 as the exact one
-        for (int i = tid; i < ge.n; i += kCT)
-#pragma unroll
-            for (int hh = 0; hh < 8; hh++)
-                if (hh < G) s.p_s[hh * PS + i] = __float2half_rn(__half2float(s.p_s[hh * PS + i]) / total[hh]);
+        for (int i = k0; i < ge.n; i += kstep) row[i] = __float2half_rn(__half2float(row[i]) / total);
     }
     consumer_sync();
     ptrace(c, 45);
@@ -1211,6 +1188,7 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
             PAttnDev& a = d.a;
             if (o.D != 64 && o.D != 128 && o.D != 256) return no("head dimension");
             if (o.KV <= 0 || o.H % o.KV != 0 || o.H / o.KV > 8) return no("more than 8 query heads per KV head");
+            if (((o.H / o.KV) & (o.H / o.KV - 1)) != 0) return no("query heads per KV head not a power of two");
             if (o.KV * (o.D / 8) > G) return no("more (KV head, column tile) pairs than SMs");
             if (att_d && att_d != (int)o.D) return no("attention operations with different head dimensions");
             if (o.span <= 0 || o.span > 4096) return no("visible span too long");
