@@ -530,13 +530,27 @@ def main():
     d2h = 8
     # the same through the native loop (`ox_llm_step`: one library call per step)
     native = llm.NativeLlmSession(backend, e2e_module, 4096)
+    native.step_greedy(prompt[:8])  # builds the plans and graphs of a prefill before the timed one
+    native.reset()
+    t0 = time.perf_counter()
     ntok = native.step_greedy(prompt)
+    prefill_s = time.perf_counter() - t0
     for _ in range(min(W, 3)):
         ntok = native.step_greedy([ntok])
+    step_s = []
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
+        t1 = time.perf_counter()
         ntok = native.step_greedy([ntok])
+        step_s.append(time.perf_counter() - t1)
     e2e_native_val = world * e2e_steps / (time.perf_counter() - t0)
+    # the fields of the reference's own benchmark report (crates/onyxia-cli/src/bench.rs:187-233, 268-288)
+    report = {"adapter": torch.cuda.get_device_name(local_rank),
+              "vram": {"resident_bytes": native.session.resident_bytes(), "peak_bytes": native.session.peak_resident_bytes()},
+              "prefill": {"tokens": len(prompt), "seconds": prefill_s, "tokens_per_sec": len(prompt) / prefill_s},
+              "decode": {"tokens": e2e_steps, "mean_ms_per_token": float(np.mean(step_s)) * 1e3, "min_ms_per_token": float(np.min(step_s)) * 1e3,
+                         "max_ms_per_token": float(np.max(step_s)) * 1e3, "stddev_ms": float(np.std(step_s)) * 1e3,
+                         "tokens_per_sec": 1.0 / float(np.mean(step_s))}}
     del native
     # the reference's own loop shape for comparison: logits to the host, argmax there
     t0 = time.perf_counter()
@@ -645,7 +659,7 @@ def main():
             "model_roofline": {"bytes_per_token": weight_bytes + kv_bytes, "tok_s_at_peak": peak * 1e9 / (weight_bytes + kv_bytes),
                                "frac": value / world / (peak * 1e9 / (weight_bytes + kv_bytes))},
             "gemv_sweep": sweep, "planner": plan_stats, "kernels": kernel_share, "resident_bytes": resident, "model_build_s": build_s,
-            "c5_tp": c5_tp,
+            "c5_tp": c5_tp, "report": report,
         }
         print(json.dumps(line))
     if world > 1:

@@ -239,6 +239,8 @@ ox_status ox_session_upload(ox_session*, int32_t dtype, const uint64_t* shape, i
  * session-owned storage; `out_tensors[i]` are new handles the caller releases. */
 ox_status ox_session_run(ox_session*, const char* const* names, ox_tensor* const* inputs, int32_t n_in,
                          const char** out_names, ox_tensor** out_tensors, int32_t out_cap, int32_t* n_out);
+/* Number of module outputs = how many entries a run returns (≙ module.outputs.len(), graph.rs:267). */
+int32_t ox_session_num_outputs(const ox_session*);
 /* ≙ Session::download: blocks until the tensor's producer has finished. */
 ox_status ox_session_download(ox_session*, const ox_tensor*, void* dst, size_t cap, size_t* written);
 

@@ -104,6 +104,7 @@ SIGNATURES = {
     "ox_session_upload": (C.c_int32, [_P, C.c_int32, _u64p, C.c_int32, _P, C.c_size_t, C.POINTER(_P)]),
     "ox_session_run": (C.c_int32, [_P, C.POINTER(C.c_char_p), C.POINTER(_P), C.c_int32, C.POINTER(C.c_char_p),
                                    C.POINTER(_P), C.c_int32, _i32p]),
+    "ox_session_num_outputs": (C.c_int32, [_P]),
     "ox_session_download": (C.c_int32, [_P, _P, _P, C.c_size_t, C.POINTER(C.c_size_t)]),
     "ox_tensor_clone": (_P, [_P]),
     "ox_tensor_release": (None, [_P]),

@@ -119,6 +119,8 @@ ox_status ox_session_run(ox_session* s, const char* const* names, ox_tensor* con
     OX_CATCH
 }
 
+int32_t ox_session_num_outputs(const ox_session* s) { return (int32_t)s->s->output_names().size(); }
+
 ox_status ox_session_download(ox_session* s, const ox_tensor* t, void* dst, size_t cap, size_t* written) {
     OX_TRY
     s->s->download(t->t, dst, cap, written);

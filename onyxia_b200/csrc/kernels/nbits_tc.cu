@@ -32,6 +32,7 @@
 // accumulator to scratch; a second kernel adds the pieces in fixed order and rounds once.
 //
 // FLOPs 2·M·N·K; bytes as for the GEMV (0.5625 per weight) once per MB rows.
+#include <cstdio>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -438,6 +439,8 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
         n_full = grid;
         tail = 0;
     }
+    static const bool debug = std::getenv("ONYXIA_GEMM_DEBUG") != nullptr;  // diagnostics
+    if (debug) std::fprintf(stderr, "nbits_gemm_tc: m %lld k_tiles %d grid %u mb %d: %d pieces over %lld of the row blocks\n", gr.m, p.k_tiles, grid, mb, splits, tail);
     p.n_full = (int)n_full;
     p.splits = splits;
     p.n_pad = tail * 128;

@@ -32,7 +32,7 @@ constexpr int kTileB = kTileW + kTileS;    // 1152: records without zero points
 constexpr int kStageB = kStTiles * kTileB; // 3456
 constexpr int kPassTiles = 128;            // tiles a CTA multiplies between two reductions
 constexpr int kMaxOps = 160;
-constexpr int kMaxPrologueK = 2048;        // the norm / residual prologue keeps ≤ 2 f16 pairs per thread
+constexpr int kMaxPrologueK = 2048;        // the norm / residual prologue keeps ≤ 8 f16 pairs per thread, in registers
 constexpr long long kWaitP = 1000000000LL; // ≈ 0.5 s: how long any wait may last before the CTA gives up
 // Arrival words (one per producing CTA, polled by a single warp before the data is read) cut the polling
 // traffic but cost a second L2 round trip per link: measured 1.4 µs slower per link than polling the tagged
@@ -176,6 +176,7 @@ __device__ __forceinline__ unsigned long long poll_finish(const Ctx& c, const un
 
 __device__ __forceinline__ bool wait_bar(const Ctx& c, unsigned bar, unsigned parity, int node) {
     if (mbar_try(bar, parity)) return true;
+    ptrace(c, 60);  // the data was not there yet
     const long long t0 = clock64();
     for (;;) {
         if (mbar_try(bar, parity)) return true;
@@ -301,6 +302,32 @@ __device__ __forceinline__ float geglu_lut(const GeluConsts& p, int form, float 
 }
 
 // ── GEMV operation (consumer side) ──────────────────────────────────────
+// The serial parts of an operation — the norm / residual prologue over a few hundred f16 pairs, the row
+// sums, the epilogue — are bound by the latency of each warp's dependent instructions, not by issue slots:
+// measured on the 1B decode step, the prologue on 4 / 8 / 16 warps gives 1032 / 933 / 902 µs per step, so it
+// runs on all of them (more loads in flight while the tagged words are polled). Warps without rows skip the
+// row sums and the epilogue.
+#ifndef OX_PW
+#define OX_PW 16
+#endif
+constexpr int kPW = OX_PW;          // warps that run a prologue
+constexpr int kPTh = kPW * 32;
+constexpr int kEP = kMaxPrologueK / 2 / kPTh;  // f16 pairs per prologue thread (8)
+
+__device__ __forceinline__ void prologue_sync() { asm volatile("bar.sync 2, %0;" ::"n"(kPTh) : "memory"); }
+
+// Sum of one double per prologue thread; every prologue thread gets the total.
+__device__ __forceinline__ double prologue_sum(const Ctx& c, double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (c.lane == 0) red[c.warp] = v;
+    prologue_sync();
+    double tot = 0.0;
+#pragma unroll
+    for (int w = 0; w < kPW; w++) tot += red[w];
+    return tot;
+}
+
 __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
     const PersistP& p = *c.p;
     const PGemvDev& g = op.g;
@@ -319,8 +346,8 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
     // ── activations → shared memory in fragment order ──
     if (flags & PF_SRC_TAGGED) wait_flags(c, g.src_flag, g.src_nflag, op.node);
     ptrace(c, 34);
-    for (int i = K + tid; i < kpad; i += kCT) acts[frag_index(i)] = __float2half(0.f);
     if (!(flags & (PF_W1 | PF_RES | PF_W2))) {
+        for (int i = K + tid; i < kpad; i += kCT) acts[frag_index(i)] = __float2half(0.f);
         if (flags & PF_SRC_TAGGED) {
             const unsigned long long* src = reinterpret_cast<const unsigned long long*>(g.src);
             for (int base = 0; base < ne; base += 4 * kCT) {
@@ -346,17 +373,17 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
             const unsigned* src = reinterpret_cast<const unsigned*>(g.src);
             for (int i = tid; i < ne; i += kCT) *reinterpret_cast<unsigned*>(acts + frag_index(2 * i)) = src[i];
         }
-    } else {
-        // Prologue: [RMS norm ·w1] [+ residual → sum_out] [RMS norm ·w2], two pairs per thread in registers.
-        // Constant operands are fetched first so that they are in flight while the activations are polled.
+    } else if (tid < kPTh) {
+        // Prologue: [RMS norm ·w1] [+ residual → sum_out] [RMS norm ·w2], up to kEP pairs per thread in
+        // registers. Constant operands are fetched first so that they are in flight while the activations are polled.
+        for (int i = K + tid; i < kpad; i += kPTh) acts[frag_index(i)] = __float2half(0.f);
         const __half2 zero2 = __float2half2_rn(0.f);
-        __half2 hw1[2], hw2[2], hres[2];
-        unsigned long long v[2];
-        int idx[2];
+        __half2 hw1[kEP], hw2[kEP], hres[kEP];
+        unsigned long long v[kEP];
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            idx[e] = tid + e * kCT;
-            const int ic = idx[e] < ne ? idx[e] : 0;
+        for (int e = 0; e < kEP; e++) {
+            const int idx = tid + e * kPTh;
+            const int ic = idx < ne ? idx : 0;
             hw1[e] = (flags & PF_W1) ? reinterpret_cast<const __half2*>(g.w1)[ic] : zero2;
             hw2[e] = (flags & PF_W2) ? reinterpret_cast<const __half2*>(g.w2)[ic] : zero2;
             hres[e] = ((flags & PF_RES) && !(flags & PF_RES_SMEM)) ? reinterpret_cast<const __half2*>(g.res)[ic] : zero2;
@@ -364,16 +391,17 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
             else if (flags & PF_SRC_RESID) v[e] = 0;
             else v[e] = reinterpret_cast<const unsigned*>(g.src)[ic];
         }
-        float x[2][2];
+        float x[kEP][2];
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-            const bool in = idx[e] < ne;
+        for (int e = 0; e < kEP; e++) {
+            const int idx = tid + e * kPTh;
+            const bool in = idx < ne;
             if (flags & PF_SRC_RESID) {
-                x[e][0] = in ? resid[2 * idx[e]] : 0.f;
-                x[e][1] = in ? resid[2 * idx[e] + 1] : 0.f;
+                x[e][0] = in ? resid[2 * idx] : 0.f;
+                x[e][1] = in ? resid[2 * idx + 1] : 0.f;
             } else {
                 if ((flags & PF_SRC_TAGGED) && in)
-                    v[e] = poll_finish(c, reinterpret_cast<const unsigned long long*>(g.src) + idx[e], v[e], op.node);
+                    v[e] = poll_finish(c, reinterpret_cast<const unsigned long long*>(g.src) + idx, v[e], op.node);
                 const float2 f = __half22float2(uh((unsigned)v[e]));
                 x[e][0] = in ? f.x : 0.f;
                 x[e][1] = in ? f.y : 0.f;
@@ -384,11 +412,11 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
         if (flags & PF_W1) {
             double ss = 0.0;
 #pragma unroll
-            for (int e = 0; e < 2; e++) ss += (double)r16(x[e][0] * x[e][0]) + (double)r16(x[e][1] * x[e][1]);
-            const double tot = consumer_sum(c, ss, red);
+            for (int e = 0; e < kEP; e++) ss += (double)r16(x[e][0] * x[e][0]) + (double)r16(x[e][1] * x[e][1]);
+            const double tot = prologue_sum(c, ss, red);
             const float msq = r16d(tot * inv_k), denom = r16(msq + g.eps1), inv = r16d(rsqrt((double)denom));
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
+            for (int e = 0; e < kEP; e++) {
                 const float2 w = __half22float2(hw1[e]);
                 x[e][0] = r16(r16(x[e][0] * inv) * w.x);
                 x[e][1] = r16(r16(x[e][1] * inv) * w.y);
@@ -397,12 +425,13 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
         ptrace(c, 36);
         if (flags & PF_RES) {
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                if (idx[e] >= ne) continue;
+            for (int e = 0; e < kEP; e++) {
+                const int idx = tid + e * kPTh;
+                if (idx >= ne) continue;
                 float r0, r1;
                 if (flags & PF_RES_SMEM) {
-                    r0 = resid[2 * idx[e]];
-                    r1 = resid[2 * idx[e] + 1];
+                    r0 = resid[2 * idx];
+                    r1 = resid[2 * idx + 1];
                 } else {
                     const float2 f = __half22float2(hres[e]);
                     r0 = f.x;
@@ -411,28 +440,30 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
                 x[e][0] = r16(x[e][0] + r0);
                 x[e][1] = r16(x[e][1] + r1);
                 if (flags & PF_SUM_OUT) {
-                    resid[2 * idx[e]] = x[e][0];
-                    resid[2 * idx[e] + 1] = x[e][1];
-                    if (blockIdx.x == 0) reinterpret_cast<unsigned*>(g.sum_out)[idx[e]] = pack_h2(x[e][0], x[e][1]);
+                    resid[2 * idx] = x[e][0];
+                    resid[2 * idx + 1] = x[e][1];
+                    if (blockIdx.x == 0) reinterpret_cast<unsigned*>(g.sum_out)[idx] = pack_h2(x[e][0], x[e][1]);
                 }
             }
         }
         if (flags & PF_W2) {
             double ss = 0.0;
 #pragma unroll
-            for (int e = 0; e < 2; e++) ss += (double)r16(x[e][0] * x[e][0]) + (double)r16(x[e][1] * x[e][1]);
-            const double tot = consumer_sum(c, ss, red + kCW);
+            for (int e = 0; e < kEP; e++) ss += (double)r16(x[e][0] * x[e][0]) + (double)r16(x[e][1] * x[e][1]);
+            const double tot = prologue_sum(c, ss, red + kPW);
             const float msq = r16d(tot * inv_k), denom = r16(msq + g.eps2), inv = r16d(rsqrt((double)denom));
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
+            for (int e = 0; e < kEP; e++) {
                 const float2 w = __half22float2(hw2[e]);
                 x[e][0] = r16(x[e][0] * inv) * w.x;  // the product is rounded when it is stored below
                 x[e][1] = r16(x[e][1] * inv) * w.y;
             }
         }
 #pragma unroll
-        for (int e = 0; e < 2; e++)
-            if (idx[e] < ne) *reinterpret_cast<unsigned*>(acts + frag_index(2 * idx[e])) = pack_h2(x[e][0], x[e][1]);
+        for (int e = 0; e < kEP; e++) {
+            const int idx = tid + e * kPTh;
+            if (idx < ne) *reinterpret_cast<unsigned*>(acts + frag_index(2 * idx)) = pack_h2(x[e][0], x[e][1]);
+        }
     }
     consumer_sync();
     ptrace(c, 31);
@@ -448,71 +479,112 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
     const uint4* ap0 = reinterpret_cast<const uint4*>(acts) + t;  // the one activation row sits at g = 0
     const unsigned long long tag = (unsigned long long)c.epoch << 32;
     const int geglu = (flags & PF_GEGLU_TANH) ? 1 : ((flags & PF_GEGLU_ERF) ? 2 : 0);
+    const unsigned slot_q = stage_q % (unsigned)R, par_q = (stage_q / (unsigned)R) & 1u;  // ring position of this operation's first stage
 
     for (int rt0 = 0; rt0 < my_rts; rt0 += rt_per_pass) {
         const int rts = my_rts - rt0 < rt_per_pass ? my_rts - rt0 : rt_per_pass;
         const int ntile = rts * kt_n;
-        // a warp takes tiles warp, warp + kCW, …; two at a time while there are two, so that their
-        // independent accumulator chains overlap
-        auto locate = [&](int j, unsigned* slot, int* kt_out) {  // waits for the tile's stage
-            const int r = j / kt_n, kt = j - r * kt_n;
-            const unsigned st = stage_q + (unsigned)((rt0 + r) * spr + kt / kStTiles);
-            *slot = st % (unsigned)R;
-            *kt_out = kt;
-            wait_bar(c, bars + *slot * 8, (st / (unsigned)R) & 1u, op.node);
-            return c.smem + (size_t)*slot * kStageB + (kt % kStTiles) * kTileB;
+        // A warp takes tiles warp, warp + kCW, …, two at a time while there are two (their independent
+        // accumulator chains overlap). Row tile, k tile, ring slot and phase of the warp's next tile are
+        // carried along incrementally: no division in the loop.
+        struct Cursor {
+            int r, kt, sg;      // row tile within the pass, k tile, stage within the row tile (kt / kStTiles)
+            unsigned slot, par; // ring slot of that stage and the phase parity to wait for
         };
-        auto finish = [&](int j, unsigned slot, int kt, const float (&ca)[4], const float (&cb)[4]) {
+        auto seek = [&](int j) {
+            Cursor q;
+            q.r = j / kt_n;
+            q.kt = j - q.r * kt_n;
+            q.sg = q.kt / kStTiles;
+            const unsigned off = (unsigned)((rt0 + q.r) * spr + q.sg);
+            const unsigned s0 = slot_q + off % (unsigned)R;
+            q.slot = s0 >= (unsigned)R ? s0 - (unsigned)R : s0;
+            q.par = (par_q + off / (unsigned)R + (s0 >= (unsigned)R ? 1u : 0u)) & 1u;
+            return q;
+        };
+        auto advance = [&](Cursor& q, int by) {  // by < kt_n + kStTiles is not required: loops handle any step
+            q.kt += by;
+            while (q.kt >= kt_n) {
+                q.kt -= kt_n;
+                q.r++;
+                // to the first stage of the next row tile
+                const unsigned step = (unsigned)(spr - q.sg);
+                q.sg = 0;
+                q.slot += step;
+                while (q.slot >= (unsigned)R) {
+                    q.slot -= (unsigned)R;
+                    q.par ^= 1u;
+                }
+            }
+            const int sg = q.kt / kStTiles;
+            const unsigned step = (unsigned)(sg - q.sg);
+            q.sg = sg;
+            q.slot += step;
+            while (q.slot >= (unsigned)R) {
+                q.slot -= (unsigned)R;
+                q.par ^= 1u;
+            }
+        };
+        auto record = [&](const Cursor& q) {
+            wait_bar(c, bars + q.slot * 8, q.par, op.node);
+            return c.smem + (size_t)q.slot * kStageB + (q.kt - q.sg * kStTiles) * kTileB;
+        };
+        auto finish = [&](int j, const Cursor& q, const float (&ca)[4], const float (&cb)[4]) {
             if (t == 0) {  // column 0 of the fragment is the activation row
                 part[j * 16 + gq] = ca[0] + cb[0];
                 part[j * 16 + gq + 8] = ca[2] + cb[2];
             }
             __syncwarp();
             if (lane == 0) {
-                const int first = (kt / kStTiles) * kStTiles;
+                const int first = q.sg * kStTiles;
                 const int cnt = kt_n - first < kStTiles ? kt_n - first : kStTiles;
                 // the warp that takes the last tile of a partly filled stage also arrives for the missing tiles
-                mbar_arrive(bars + (unsigned)(R + (int)slot) * 8, kt - first == cnt - 1 ? 1u + (unsigned)(kStTiles - cnt) : 1u);
+                mbar_arrive(bars + (unsigned)(R + (int)q.slot) * 8, q.kt - first == cnt - 1 ? 1u + (unsigned)(kStTiles - cnt) : 1u);
             }
         };
         int j = c.warp;
-        for (; j + kCW < ntile; j += 2 * kCW) {
-            unsigned slot1, slot2;
-            int kt1, kt2;
-            const unsigned char* rec1 = locate(j, &slot1, &kt1);
-            const unsigned char* rec2 = locate(j + kCW, &slot2, &kt2);
-            float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f}, cc[4] = {0.f, 0.f, 0.f, 0.f}, cd[4] = {0.f, 0.f, 0.f, 0.f};
-            tile_mma2_zp8(rec1, ap0 + kt1 * 16, rec2, ap0 + kt2 * 16, 4, lane, ca, cb, cc, cd);
-            finish(j, slot1, kt1, ca, cb);
-            finish(j + kCW, slot2, kt2, cc, cd);
-        }
         if (j < ntile) {
-            unsigned slot;
-            int kt;
-            const unsigned char* rec = locate(j, &slot, &kt);
-            float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
-            tile_mma_zp8(rec, ap0 + kt * 16, 4, lane, ca, cb);
-            finish(j, slot, kt, ca, cb);
+            Cursor q1 = seek(j);
+            for (; j + kCW < ntile; j += 2 * kCW) {
+                Cursor q2 = q1;
+                advance(q2, kCW);
+                const unsigned char* rec1 = record(q1);
+                const unsigned char* rec2 = record(q2);
+                float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f}, cc[4] = {0.f, 0.f, 0.f, 0.f}, cd[4] = {0.f, 0.f, 0.f, 0.f};
+                tile_mma2_zp8(rec1, ap0 + q1.kt * 16, rec2, ap0 + q2.kt * 16, 4, lane, ca, cb, cc, cd);
+                finish(j, q1, ca, cb);
+                finish(j + kCW, q2, cc, cd);
+                q1 = q2;
+                if (j + 2 * kCW < ntile) advance(q1, kCW);
+            }
+            if (j < ntile) {
+                const unsigned char* rec = record(q1);
+                float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
+                tile_mma_zp8(rec, ap0 + q1.kt * 16, 4, lane, ca, cb);
+                finish(j, q1, ca, cb);
+            }
         }
         consumer_sync();
         ptrace(c, 32);
-        // row sums over the k tiles in f64, rounded once; the result replaces the row's first partial
-        // (four threads share a row: each adds every fourth tile, two exchanges combine them)
+        // Row sums over the k tiles in f64, rounded once; the result replaces the row's first partial. Four
+        // threads share a row: each adds every fourth tile, two exchanges combine them. Only the warps that
+        // have rows take part.
         const int nrow = rts * 16;
         for (int base = 0; base < nrow * 4; base += kCT) {
+            if (base + (c.warp << 5) >= nrow * 4) break;  // warp-uniform: this warp has no rows (left)
             const int i = (base + tid) >> 2, q4 = tid & 3;
             const bool in = i < nrow;
             float y = 0.f;
             const int r = i >> 4, row = i & 15;
-            double s = 0.0;
+            double sum = 0.0;
             if (in) {
                 const float* pr = part + (r * kt_n) * 16 + row;
-                for (int kt = q4; kt < kt_n; kt += 4) s += (double)pr[kt * 16];
+                for (int kt = q4; kt < kt_n; kt += 4) sum += (double)pr[kt * 16];
             }
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             if (in) {
-                y = r16d(s);
+                y = r16d(sum);
                 if (q4 == 0) part[(r * kt_n) * 16 + row] = y;
             }
             if (!geglu) {
@@ -532,6 +604,7 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
             consumer_sync();
             const int npair = (rts >> 1) * 16;
             for (int base = 0; base < npair; base += kCT) {
+                if (base + (c.warp << 5) >= npair) break;  // warp-uniform
                 const int i = base + tid;
                 const bool in = i < npair;
                 const int pj = i >> 4, row = i & 15;
@@ -985,6 +1058,15 @@ __global__ void __launch_bounds__(kPT, 1) persist_step(const __grid_constant__ P
                             ok = false;
                             break;
                         }
+#ifdef OX_TRACE
+                        if ((blockIdx.x == 0 || blockIdx.x == 40) && i >= 10 && i <= 16) {
+                            unsigned long long* t = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(pk.err) + 256) + 1 + 8 * 990 + (blockIdx.x / 40) * 100;
+                            unsigned long long now;
+                            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                            const int k = (int)(q % 100u);
+                            t[k] = ((unsigned long long)i << 56) | ((unsigned long long)(q & 0xFFFF) << 40) | (now & 0xFFFFFFFFFFull);
+                        }
+#endif
                         mbar_expect(bars + slot * 8, (unsigned)cnt * kTileB);
                         bulk_load(smem_addr(smem + (size_t)slot * kStageB), src + (size_t)s * kStageB, (unsigned)cnt * kTileB, bars + slot * 8);
                     }

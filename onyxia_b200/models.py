@@ -41,6 +41,7 @@ class DecoderConfig:
     sandwich_norms: bool = False     # Gemma-3 post-attention / post-FFN norms before the residual adds
     last_logits_only: bool = False   # slice the last position before lm_head
     gelu_tanh: bool = True
+    scale_range: tuple = (0.005, 0.02)   # uniform range of the int4 block scales
 
     @property
     def np_act(self):
@@ -120,7 +121,7 @@ class _Weights:
         nb = (k + 31) // 32
         r = _rng(self.seed, name)
         packed = r.integers(0, 256, size=n * nb * 16, dtype=np.uint8)  # nibbles uniform over 0..15
-        scales = r.uniform(0.005, 0.02, size=n * nb).astype(self.cfg.np_act)
+        scales = r.uniform(self.cfg.scale_range[0], self.cfg.scale_range[1], size=n * nb).astype(self.cfg.np_act)
         w = self.b.constant(HostTensor(ir.U4, [n, nb, 32], packed), borrow=True)
         s = self.b.constant(HostTensor.from_numpy(scales), borrow=True)
         ins = [w, s]

@@ -312,24 +312,28 @@ def test_gqa_batched_decode_crosses_the_cluster_size_bucket_under_graph_replay()
     (a patched grid alone would leave keys out of the softmax). Every step is compared with the oracle."""
     from oracle import ref
     batch, heads, kv, d = 40, 4, 4, 32
-    b = ir.GraphBuilder()
-    P = b.sym("P")
-    q = b.input("q", ir.F16, [batch, 1, heads * d])
-    k = b.input("k", ir.F16, [batch, 1, kv * d])
-    v = b.input("v", ir.F16, [batch, 1, kv * d])
-    pk = b.input("past_key", ir.F16, [batch, kv, P, d])
-    pv = b.input("past_value", ir.F16, [batch, kv, P, d])
-    sl = b.input("seqlens_k", ir.I32, [batch])
-    cfg = models.DecoderConfig("t", 0, 0, heads, kv, d, 0, 0, act_dtype=ir.F16, max_positions=1100)
-    c, s = models.rope_caches(cfg)
-    outs = b.composite(GQA, {"num_heads": heads, "kv_num_heads": kv, "local_window_size": -1, "do_rotary": 1},
-                       [q, k, v, pk, pv, sl, b.constant(ht(c)), b.constant(ht(s))],
-                       [(ir.F16, [batch, 1, heads * d]), (ir.F16, [batch, kv, P + 1, d]), (ir.F16, [batch, kv, P + 1, d])])
-    b.output("out", outs[0])
-    b.output("present_key", outs[1])
-    b.output("present_value", outs[2])
-    b.output("twice", b.add(outs[0], outs[0]))  # a second launch: single-launch plans are not recorded as graphs
-    mod = b.finish()
+
+    def make(nb):
+        b = ir.GraphBuilder()
+        P = b.sym("P")
+        q = b.input("q", ir.F16, [nb, 1, heads * d])
+        k = b.input("k", ir.F16, [nb, 1, kv * d])
+        v = b.input("v", ir.F16, [nb, 1, kv * d])
+        pk = b.input("past_key", ir.F16, [nb, kv, P, d])
+        pv = b.input("past_value", ir.F16, [nb, kv, P, d])
+        sl = b.input("seqlens_k", ir.I32, [nb])
+        cfg = models.DecoderConfig("t", 0, 0, heads, kv, d, 0, 0, act_dtype=ir.F16, max_positions=1100)
+        c, s = models.rope_caches(cfg)
+        outs = b.composite(GQA, {"num_heads": heads, "kv_num_heads": kv, "local_window_size": -1, "do_rotary": 1},
+                           [q, k, v, pk, pv, sl, b.constant(ht(c)), b.constant(ht(s))],
+                           [(ir.F16, [nb, 1, heads * d]), (ir.F16, [nb, kv, P + 1, d]), (ir.F16, [nb, kv, P + 1, d])])
+        b.output("out", outs[0])
+        b.output("present_key", outs[1])
+        b.output("present_value", outs[2])
+        b.output("twice", b.add(outs[0], outs[0]))  # a second launch: single-launch plans are not recorded as graphs
+        return b.finish()
+
+    mod, mod_rows = make(batch), make(3)
     dev = cuda_backend().prepare(mod.clone())
     ref.set_threads(8)
     rows = np.array([0, 17, 39])
@@ -343,7 +347,7 @@ def test_gqa_batched_decode_crosses_the_cluster_size_bucket_under_graph_replay()
         feed = {"q": RNG.standard_normal((batch, 1, heads * d)).astype(f16), "k": RNG.standard_normal((batch, 1, kv * d)).astype(f16),
                 "v": RNG.standard_normal((batch, 1, kv * d)).astype(f16), "seqlens_k": np.full(batch, past, np.int32)}
         got = dict(dev.run({**{n: dev.upload(ht(x)) for n, x in feed.items()}, "past_key": d_pk, "past_value": d_pv}))
-        cpu = ref.RefBackend().prepare(mod.clone())
+        cpu = ref.RefBackend().prepare(mod_rows.clone())
         want = dict(cpu.run({**{n: ht(np.ascontiguousarray(x[rows])) for n, x in feed.items()}, "past_key": o_pk, "past_value": o_pv}))
         diff = float(np.abs(dev.download(got["out"]).numpy()[rows].astype(f32) - want["out"].numpy().astype(f32)).max())
         worst = max(worst, diff)

@@ -54,6 +54,37 @@ def main():
         print(f"tp={world} max abs diff vs one GPU: {diff:.5f}", flush=True)
         assert diff <= 2e-2, diff
     dist.barrier()
+
+    # the 27B-architecture block at full width (hidden 5376, 32Q/16KV heads of 128, FFN 21504), two layers, one
+    # batched decode step over a short synthetic past: partitioned vs whole
+    from onyxia_b200.ir import HostTensor
+    cfg = models.config_gemma3_27b()
+    cfg.layers, cfg.vocab, cfg.max_positions = 2, 8192, 64
+    cfg.scale_range = (0.001, 0.004)  # keeps this width inside the f16 range (the benchmark's range overflows in the interpreter too)
+    module = models.build_decoder(cfg, seed=3)
+    B, past = 16, 24
+    rng = np.random.default_rng(9)
+    ids = rng.integers(0, cfg.vocab, (B, 1)).astype(np.int64)
+    kv_full = {f"past_key_values.{l}.{part}": rng.standard_normal((B, cfg.kv_heads, past, cfg.head_dim)).astype(np.float16)
+               for l in range(cfg.layers) for part in ("key", "value")}
+
+    def run(bk, mod, kv_heads):
+        sess = bk.prepare(mod)
+        feed = {"input_ids": sess.upload(HostTensor.from_numpy(ids)),
+                "attention_mask": sess.upload(HostTensor.from_numpy(np.ones((B, past + 1), np.int64)))}
+        for name, arr in kv_full.items():
+            feed[name] = sess.upload(HostTensor.from_numpy(np.ascontiguousarray(arr[:, kv_heads])))
+        out = dict(sess.run(feed))
+        return sess.download(out["logits"]).numpy().astype(np.float32)
+
+    per = cfg.kv_heads // world
+    mine = run(backend, module.tp_partition(world, rank), slice(rank * per, (rank + 1) * per))
+    if rank == 0:
+        whole = run(be.CudaBackend((local,)), module, slice(0, cfg.kv_heads))
+        diff = float(np.abs(whole - mine).max())
+        print(f"tp={world} 27B-architecture width, 2 layers, batch {B}: max abs diff vs one GPU: {diff:.5f}", flush=True)
+        assert diff <= 2e-2, diff
+    dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok", flush=True)
 
