@@ -104,9 +104,11 @@ class ClockSampler:
         return out
 
 
-def build_model(seed=0):
+def build_model(seed=0, depth=0):
     from onyxia_b200 import models
     cfg = models.config_gemma3_1b()
+    if depth:
+        cfg.layers = depth
     t = time.time()
     module = models.build_decoder(cfg, seed=seed)
     return cfg, module, time.time() - t
@@ -386,6 +388,9 @@ def main():
     ap.add_argument("--ref-prompt-len", type=int, default=PROMPT_LEN,
                     help="prompt length of the CPU reference arm (its prefill is untimed; 512 tokens take about a minute)")
     ap.add_argument("--no-tp", action="store_true", help="with more than one rank: skip the tensor-parallel 27B-architecture slice")
+    ap.add_argument("--depth", type=int, default=0,
+                    help="decoder layers of the 1B model (default: all 26). A reduced depth is for profiler captures only: "
+                         "the line it prints says so in config.layers_run and is not a benchmark value")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     args = ap.parse_args()
@@ -452,7 +457,7 @@ def main():
     from onyxia_b200 import ir, llm
     from onyxia_b200.ir import HostTensor
 
-    cfg, module, build_s = build_model()
+    cfg, module, build_s = build_model(depth=args.depth)
     cpu_module = module.clone() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     e2e_module = module.clone()
     backend = be.CudaBackend((local_rank,))
@@ -650,7 +655,8 @@ def main():
                                    "vocab 262144, 5 local(512):1 global), fp16 activations, batch 1, 512-token prompt, "
                                    "greedy decode", "prompt_len": PROMPT_LEN, "context_at_timing": [past + W, past + W + K],
                        "replicas": world, "l2_policy": "per-token weights (562 MB) exceed the 126 MB L2",
-                       "norms": "pre + post (sandwich) RMSNorm per block, no q/k norm"},
+                       "norms": "pre + post (sandwich) RMSNorm per block, no q/k norm", "layers_run": cfg.layers,
+                       **({"reduced_depth": "profiler capture case, not a benchmark value"} if args.depth else {})},
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": max(e2e_val, e2e_native_val), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "path": "ox_llm_step: upload(ids, mask) → run → device argmax → download(token id), per step",

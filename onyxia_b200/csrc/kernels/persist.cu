@@ -1088,7 +1088,9 @@ __global__ void __launch_bounds__(kPT, 1) persist_step(const __grid_constant__ P
             if (op.kind == POP_GEMV) {
                 run_gemv(c, op, stage_q);
             } else {
-                run_attn<256>(c, op);
+                if (op.a.D == 256) run_attn<256>(c, op);
+                else if (op.a.D == 128) run_attn<128>(c, op);
+                else run_attn<64>(c, op);
                 if (op.a.next_attn >= 0) att_prefetch(c, p.ops[op.a.next_attn], false);
             }
         }

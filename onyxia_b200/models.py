@@ -111,6 +111,24 @@ def rope_caches(cfg: DecoderConfig):
     return np.cos(ang).astype(cfg.np_act), np.sin(ang).astype(cfg.np_act)
 
 
+def nbits_arrays(cfg: DecoderConfig, seed: int, name: str, k: int, n: int):
+    """The seeded int4 weight `name`: (packed nibbles u8 [n·nb·16], scales [n·nb], packed zero points u8 or None)."""
+    nb = (k + 31) // 32
+    r = _rng(seed, name)
+    packed = r.integers(0, 256, size=n * nb * 16, dtype=np.uint8)  # nibbles uniform over 0..15
+    scales = r.uniform(cfg.scale_range[0], cfg.scale_range[1], size=n * nb).astype(cfg.np_act)
+    zp = np.full((n * nb + 1) // 2, 0x88, dtype=np.uint8) if cfg.explicit_zero_points else None
+    return packed, scales, zp
+
+
+def norm_array(cfg: DecoderConfig, seed: int, name: str, width: int):
+    return (1.0 + 0.02 * _rng(seed, name).standard_normal(width)).astype(cfg.np_act)
+
+
+def embed_array(cfg: DecoderConfig, seed: int):
+    return (0.02 * _rng(seed, "embed").standard_normal((cfg.vocab, cfg.hidden), dtype=np.float32)).astype(cfg.np_act)
+
+
 class _Weights:
     """Adds seeded constants to a builder; big tensors are borrowed, not copied."""
 
@@ -119,20 +137,16 @@ class _Weights:
 
     def nbits(self, name: str, k: int, n: int):
         nb = (k + 31) // 32
-        r = _rng(self.seed, name)
-        packed = r.integers(0, 256, size=n * nb * 16, dtype=np.uint8)  # nibbles uniform over 0..15
-        scales = r.uniform(self.cfg.scale_range[0], self.cfg.scale_range[1], size=n * nb).astype(self.cfg.np_act)
+        packed, scales, zp = nbits_arrays(self.cfg, self.seed, name, k, n)
         w = self.b.constant(HostTensor(ir.U4, [n, nb, 32], packed), borrow=True)
         s = self.b.constant(HostTensor.from_numpy(scales), borrow=True)
         ins = [w, s]
-        if self.cfg.explicit_zero_points:
-            zp = np.full((n * nb + 1) // 2, 0x88, dtype=np.uint8)
+        if zp is not None:
             ins.append(self.b.constant(HostTensor(ir.U4, [n, nb], zp), borrow=True))
         return ins
 
     def norm(self, name: str, width: int):
-        w = (1.0 + 0.02 * _rng(self.seed, name).standard_normal(width)).astype(self.cfg.np_act)
-        return self.b.constant(HostTensor.from_numpy(w))
+        return self.b.constant(HostTensor.from_numpy(norm_array(self.cfg, self.seed, name, width)))
 
 
 def build_decoder(cfg: DecoderConfig, seed: int = 0) -> ir.Module:
@@ -172,8 +186,7 @@ def build_decoder(cfg: DecoderConfig, seed: int = 0) -> ir.Module:
     sin = b.constant(HostTensor.from_numpy(sin_np))
 
     b.set_loc("/model/embed_tokens/Gather", "Gather")
-    table = (0.02 * _rng(seed, "embed").standard_normal((cfg.vocab, H), dtype=np.float32)).astype(cfg.np_act)
-    x = b.gather(b.constant(HostTensor.from_numpy(table), borrow=True), ids, 0)
+    x = b.gather(b.constant(HostTensor.from_numpy(embed_array(cfg, seed)), borrow=True), ids, 0)
 
     presents = []
     for l in range(cfg.layers):

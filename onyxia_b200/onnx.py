@@ -1,0 +1,658 @@
+"""A minimal ONNX reader / writer and the lowering of the operators a quantised decoder export uses.
+
+≙ ``crates/onyxia-onnx/src/parser.rs:17-117`` (ModelProto → graph) and the rules of
+``crates/onyxia-lower/src/rules.rs`` that the decoder path needs: the four composites
+(``SimplifiedLayerNormalization``, ``Gelu``, ``com.microsoft.MatMulNBits`` :890-940,
+``com.microsoft.GroupQueryAttention`` :777-888) and the plain operators around them. There is no
+``protoc`` and no ``onnx`` package here, so the protobuf wire format is read and written by hand
+(varints, length-delimited fields); only the fields of ``onnx.proto`` that such graphs use are known.
+
+Lowering conventions taken from the reference:
+
+* shape arithmetic that an export spells with ``Shape → Gather → Cast`` is evaluated at lowering time
+  into dimension expressions (the compile-time value domain, graph.rs:71-100) instead of nodes;
+* ``MatMulNBits``: the packed ``uint8 [N, n_blocks, block/2]`` blob is reinterpreted as logical
+  ``U4 [N, n_blocks, block]``, zero points as ``U4 [N, n_blocks]`` (needs an even block count per row);
+* ``GroupQueryAttention``: inputs ``[q, k, v, past_k, past_v, seqlens_k][, cos, sin][, bias]``;
+  ``total_sequence_length`` is not an operand — when it is a compile-time value it becomes the bind-time
+  constraint *total = past + new*; ``present`` types are the past types with ``past + seq`` rows;
+  softcap and explicit position ids with ``do_rotary`` are rejected.
+"""
+from __future__ import annotations
+
+import struct
+
+import numpy as np
+
+from . import ir
+from .ir import DimExpr, HostTensor
+
+# onnx.proto TensorProto.DataType
+_ONNX_DT = {1: ir.F32, 2: ir.U8, 3: ir.I8, 6: ir.I32, 7: ir.I64, 9: ir.BOOL, 10: ir.F16, 12: ir.U32, 21: ir.U4, 22: ir.I4}
+_ONNX_DT_REV = {v: k for k, v in _ONNX_DT.items()}
+_NP_OF = {ir.F32: np.float32, ir.F16: np.float16, ir.I64: np.int64, ir.I32: np.int32, ir.U32: np.uint32, ir.U8: np.uint8,
+          ir.I8: np.int8, ir.BOOL: np.bool_}
+
+
+class OnnxError(ValueError):
+    pass
+
+
+# ── protobuf wire format ─────────────────────────────────────────────────
+def _varint(buf, i):
+    shift = val = 0
+    while True:
+        b = buf[i]
+        i += 1
+        val |= (b & 0x7F) << shift
+        if not b & 0x80:
+            return val, i
+        shift += 7
+
+
+def _fields(buf):
+    """Yields (field number, wire type, value) of one message; LEN fields as memoryview slices."""
+    buf = memoryview(buf)
+    i, n = 0, len(buf)
+    while i < n:
+        key, i = _varint(buf, i)
+        field, wire = key >> 3, key & 7
+        if wire == 0:
+            v, i = _varint(buf, i)
+        elif wire == 1:
+            v, i = struct.unpack_from("<Q", buf, i)[0], i + 8
+        elif wire == 2:
+            ln, i = _varint(buf, i)
+            v, i = buf[i:i + ln], i + ln
+        elif wire == 5:
+            v, i = struct.unpack_from("<I", buf, i)[0], i + 4
+        else:
+            raise OnnxError(f"unsupported protobuf wire type {wire}")
+        yield field, wire, v
+
+
+def _enc_varint(v: int) -> bytes:
+    v &= (1 << 64) - 1
+    out = bytearray()
+    while True:
+        b = v & 0x7F
+        v >>= 7
+        out.append(b | (0x80 if v else 0))
+        if not v:
+            return bytes(out)
+
+
+def _f_int(field, v):
+    return _enc_varint(field << 3) + _enc_varint(v)
+
+
+def _f_bytes(field, payload):
+    payload = bytes(payload)
+    return _enc_varint((field << 3) | 2) + _enc_varint(len(payload)) + payload
+
+
+def _f_str(field, s):
+    return _f_bytes(field, s.encode())
+
+
+def _f_f32(field, v):
+    return _enc_varint((field << 3) | 5) + struct.pack("<f", v)
+
+
+def _signed(v):
+    return v - (1 << 64) if v >= 1 << 63 else v
+
+
+# ── reading ──────────────────────────────────────────────────────────────
+class _Node:
+    __slots__ = ("op", "domain", "name", "inputs", "outputs", "attrs")
+
+
+def _parse_tensor(buf):
+    dims, dt, raw, name = [], 0, None, ""
+    f32, i32, i64 = [], [], []
+    for f, w, v in _fields(buf):
+        if f == 1:
+            if w == 2:  # packed
+                j = 0
+                while j < len(v):
+                    d, j = _varint(v, j)
+                    dims.append(d)
+            else:
+                dims.append(v)
+        elif f == 2:
+            dt = v
+        elif f == 4:
+            f32 += list(np.frombuffer(v, "<f4")) if w == 2 else [struct.unpack("<f", struct.pack("<I", v))[0]]
+        elif f == 5:
+            if w == 2:
+                j = 0
+                while j < len(v):
+                    d, j = _varint(v, j)
+                    i32.append(_signed(d))
+            else:
+                i32.append(_signed(v))
+        elif f == 7:
+            if w == 2:
+                j = 0
+                while j < len(v):
+                    d, j = _varint(v, j)
+                    i64.append(_signed(d))
+            else:
+                i64.append(_signed(v))
+        elif f == 8:
+            name = bytes(v).decode()
+        elif f == 9:
+            raw = bytes(v)
+    if dt not in _ONNX_DT:
+        raise OnnxError(f"initializer '{name}': unsupported ONNX data type {dt}")
+    dtype = _ONNX_DT[dt]
+    if raw is None:
+        src = f32 if dtype == ir.F32 else (i64 if dtype == ir.I64 else i32)
+        raw = np.asarray(src, dtype=_NP_OF[dtype]).tobytes()
+    return name, dtype, dims, np.frombuffer(raw, np.uint8).copy()
+
+
+def _parse_attr(buf):
+    name, out, ints, floats, typ = "", None, [], [], 0
+    for f, w, v in _fields(buf):
+        if f == 1:
+            name = bytes(v).decode()
+        elif f == 2:
+            out = struct.unpack("<f", struct.pack("<I", v))[0]
+        elif f == 3:
+            out = _signed(v)
+        elif f == 4:
+            out = bytes(v).decode()
+        elif f == 5:
+            out = _parse_tensor(v)
+        elif f == 7:
+            floats += list(np.frombuffer(v, "<f4")) if w == 2 else [struct.unpack("<f", struct.pack("<I", v))[0]]
+        elif f == 8:
+            if w == 2:
+                j = 0
+                while j < len(v):
+                    d, j = _varint(v, j)
+                    ints.append(_signed(d))
+            else:
+                ints.append(_signed(v))
+        elif f == 20:
+            typ = v
+    if typ == 7 or (out is None and ints):
+        out = ints
+    elif typ == 6 or (out is None and floats):
+        out = [float(x) for x in floats]
+    return name, out
+
+
+def _parse_value_info(buf):
+    name, elem, shape = "", 0, None
+    for f, _, v in _fields(buf):
+        if f == 1:
+            name = bytes(v).decode()
+        elif f == 2:  # TypeProto
+            for f2, _, v2 in _fields(v):
+                if f2 == 1:  # tensor_type
+                    for f3, _, v3 in _fields(v2):
+                        if f3 == 1:
+                            elem = v3
+                        elif f3 == 2:  # TensorShapeProto
+                            shape = []
+                            for f4, _, v4 in _fields(v3):
+                                if f4 == 1:
+                                    dim = None
+                                    for f5, _, v5 in _fields(v4):
+                                        if f5 == 1:
+                                            dim = _signed(v5)
+                                        elif f5 == 2:
+                                            dim = bytes(v5).decode()
+                                    shape.append(dim)
+    return name, elem, shape
+
+
+def parse_model(data: bytes):
+    """ModelProto bytes → (nodes, initializers{name: (dtype, dims, bytes)}, inputs[(name, dtype, shape)], output names)."""
+    graph = None
+    for f, _, v in _fields(data):
+        if f == 7:
+            graph = v
+    if graph is None:
+        raise OnnxError("the model has no graph")
+    nodes, inits, inputs, outputs = [], {}, [], []
+    for f, _, v in _fields(graph):
+        if f == 1:
+            n = _Node()
+            n.op, n.domain, n.name, n.inputs, n.outputs, n.attrs = "", "", "", [], [], {}
+            for f2, _, v2 in _fields(v):
+                if f2 == 1:
+                    n.inputs.append(bytes(v2).decode())
+                elif f2 == 2:
+                    n.outputs.append(bytes(v2).decode())
+                elif f2 == 3:
+                    n.name = bytes(v2).decode()
+                elif f2 == 4:
+                    n.op = bytes(v2).decode()
+                elif f2 == 5:
+                    k, a = _parse_attr(v2)
+                    n.attrs[k] = a
+                elif f2 == 7:
+                    n.domain = bytes(v2).decode()
+            nodes.append(n)
+        elif f == 5:
+            name, dtype, dims, raw = _parse_tensor(v)
+            inits[name] = (dtype, dims, raw)
+        elif f == 11:
+            inputs.append(_parse_value_info(v))
+        elif f == 12:
+            outputs.append(_parse_value_info(v)[0])
+    return nodes, inits, inputs, outputs
+
+
+# ── lowering ─────────────────────────────────────────────────────────────
+class _Val:
+    __slots__ = ("vid", "dtype", "shape", "content", "const")
+
+    def __init__(self, vid, dtype, shape, content=None, const=None):
+        self.vid, self.dtype, self.shape, self.content, self.const = vid, dtype, list(shape), content, const
+
+
+class _Lower:
+    def __init__(self, nodes, inits, inputs, outputs):
+        self.b = ir.GraphBuilder()
+        self.nodes, self.inits, self.outputs = nodes, inits, outputs
+        self.vals: dict = {}
+        self.syms: dict = {}
+        for name, elem, shape in inputs:
+            if name in inits:
+                continue
+            if elem not in _ONNX_DT or shape is None:
+                raise OnnxError(f"input '{name}' needs a tensor type with a shape")
+            dims = [self._dim(d) for d in shape]
+            self.vals[name] = _Val(self.b.input(name, _ONNX_DT[elem], dims), _ONNX_DT[elem], dims)
+
+    def _dim(self, d):
+        if isinstance(d, str):
+            if d not in self.syms:
+                self.syms[d] = self.b.sym(d)
+            return self.syms[d]
+        if d is None or d < 0:
+            raise OnnxError("input dimension without a value or a name")
+        return DimExpr.of(d)
+
+    # operands ----------------------------------------------------------
+    def has(self, node, i):
+        return i < len(node.inputs) and node.inputs[i] != ""
+
+    def const_array(self, name):
+        """Value of an initializer as a numpy array (for operands that must be compile-time constants)."""
+        if name in self.vals and self.vals[name].const is not None:
+            return self.vals[name].const
+        if name not in self.inits:
+            return None
+        dtype, dims, raw = self.inits[name]
+        if dtype not in _NP_OF:
+            return None
+        return raw.view(_NP_OF[dtype]).reshape(dims)
+
+    def val(self, name, as_type=None):
+        """Operand by name; an initializer becomes a module constant on first use. `as_type` = (dtype, dims)
+        reinterprets the initializer's bytes (packed nibbles shipped as uint8)."""
+        if name in self.vals and as_type is None:
+            return self.vals[name]
+        if name not in self.inits:
+            if name in self.vals:
+                raise OnnxError(f"'{name}' must be an initializer to be reinterpreted")
+            raise OnnxError(f"operand '{name}' is not defined")
+        dtype, dims, raw = self.inits[name]
+        if as_type is not None:
+            dtype, dims = as_type
+            if ir.storage_bytes(dtype, int(np.prod(dims))) != raw.size:
+                raise OnnxError(f"initializer '{name}' has {raw.size} bytes, not what {ir.DTYPE_NAMES[dtype]}{list(dims)} needs")
+        t = HostTensor(dtype, list(dims), raw)
+        v = _Val(self.b.constant(t, borrow=raw.size > 1 << 16), dtype, [DimExpr.of(d) for d in dims],
+                 const=self.const_array(name) if as_type is None else None)
+        if as_type is None:
+            self.vals[name] = v
+        return v
+
+    def int_list(self, node, i, attr=None):
+        """A list of integers given as a constant operand (newer opsets) or an attribute (older ones)."""
+        if self.has(node, i):
+            a = self.const_array(node.inputs[i])
+            if a is None:
+                raise OnnxError(f"{node.op} '{node.name}': operand {i} must be a constant")
+            return [int(x) for x in np.asarray(a).reshape(-1)]
+        if attr is not None and attr in node.attrs:
+            return [int(x) for x in node.attrs[attr]]
+        return None
+
+    def set(self, node, i, val):
+        if i < len(node.outputs) and node.outputs[i]:
+            self.vals[node.outputs[i]] = val
+
+    @staticmethod
+    def _broadcast(a, b):
+        ra, rb = list(a), list(b)
+        while len(ra) < len(rb):
+            ra.insert(0, DimExpr.of(1))
+        while len(rb) < len(ra):
+            rb.insert(0, DimExpr.of(1))
+        return [y if x == 1 else x for x, y in zip(ra, rb)]
+
+    # rules -------------------------------------------------------------
+    def lower(self):
+        for node in self.nodes:
+            self.b.set_loc(node.name or None, node.op)
+            rule = getattr(self, "op_" + node.op.replace(".", "_"), None)
+            if rule is None:
+                raise OnnxError(f"no lowering rule for operator '{node.op}'" + (f" (domain {node.domain})" if node.domain else ""))
+            rule(node)
+        self.b.set_loc(None)
+        for name in self.outputs:
+            if name not in self.vals:
+                raise OnnxError(f"graph output '{name}' is not produced")
+            v = self.vals[name]
+            if v.vid is None:
+                raise OnnxError(f"graph output '{name}' is a compile-time shape value")
+            self.b.output(name, v.vid)
+        return self.b.finish()
+
+    def op_Identity(self, n):
+        self.set(n, 0, self.val(n.inputs[0]))
+
+    def _binary(self, n, op):
+        a, b = self.val(n.inputs[0]), self.val(n.inputs[1])
+        if a.content is not None and b.content is not None and op in (ir.ADD, ir.SUB, ir.MUL):
+            f = {ir.ADD: lambda x, y: x + y, ir.SUB: lambda x, y: x - y, ir.MUL: lambda x, y: x * y}[op]
+            self.set(n, 0, _Val(None, a.dtype, a.shape, content=[f(x, y) for x, y in zip(a.content, b.content)]))
+            return
+        self.set(n, 0, _Val(self.b.binary(op, a.vid, b.vid), a.dtype, self._broadcast(a.shape, b.shape)))
+
+    def op_Add(self, n): self._binary(n, ir.ADD)
+    def op_Sub(self, n): self._binary(n, ir.SUB)
+    def op_Mul(self, n): self._binary(n, ir.MUL)
+    def op_Div(self, n): self._binary(n, ir.DIV)
+
+    def op_Cast(self, n):
+        x = self.val(n.inputs[0])
+        to = _ONNX_DT.get(n.attrs.get("to"))
+        if to is None:
+            raise OnnxError(f"Cast '{n.name}': unsupported target type {n.attrs.get('to')}")
+        if x.content is not None:  # shape values stay shape values whatever integer type they are cast to
+            self.set(n, 0, _Val(None, to, x.shape, content=x.content))
+        else:
+            self.set(n, 0, _Val(self.b.cast(x.vid, to), to, x.shape))
+
+    def op_Shape(self, n):
+        x = self.val(n.inputs[0])
+        self.set(n, 0, _Val(None, ir.I64, [DimExpr.of(len(x.shape))], content=list(x.shape)))
+
+    def op_Gather(self, n):
+        data, axis = self.val(n.inputs[0]), int(n.attrs.get("axis", 0))
+        if data.content is not None:
+            idx = self.const_array(n.inputs[1])
+            if idx is None:
+                raise OnnxError(f"Gather '{n.name}' on a shape value needs constant indices")
+            picks = [data.content[int(i)] for i in np.asarray(idx).reshape(-1)]
+            self.set(n, 0, _Val(None, data.dtype, [] if np.asarray(idx).ndim == 0 else [DimExpr.of(len(picks))], content=picks))
+            return
+        idx = self.val(n.inputs[1])
+        if axis < 0:
+            axis += len(data.shape)
+        ivid = idx.vid if idx.dtype == ir.I64 else self.b.cast(idx.vid, ir.I64)  # the primitive takes i64 indices (rules.rs:503-522)
+        shape = data.shape[:axis] + idx.shape + data.shape[axis + 1:]
+        self.set(n, 0, _Val(self.b.gather(data.vid, ivid, axis), data.dtype, shape))
+
+    def op_ReduceSum(self, n):
+        x = self.val(n.inputs[0])
+        axes = self.int_list(n, 1, "axes")
+        keep = bool(n.attrs.get("keepdims", 1))
+        if axes is None:
+            axes = list(range(len(x.shape)))
+        axes = sorted(a + len(x.shape) if a < 0 else a for a in axes)
+        shape = [DimExpr.of(1) if i in axes else d for i, d in enumerate(x.shape) if keep or i not in axes]
+        self.set(n, 0, _Val(self.b.reduce(ir.SUM, x.vid, axes, keep), x.dtype, shape))
+
+    def op_Slice(self, n):
+        x = self.val(n.inputs[0])
+        starts, ends = self.int_list(n, 1, "starts"), self.int_list(n, 2, "ends")
+        axes = self.int_list(n, 3, "axes") or list(range(len(starts)))
+        steps = self.int_list(n, 4) or [1] * len(starts)
+        specs, shape = [], list(x.shape)
+        for s, e, ax, st in zip(starts, ends, axes, steps):
+            if st != 1:
+                raise OnnxError(f"Slice '{n.name}': only step 1 is lowered here")
+            ax = ax + len(x.shape) if ax < 0 else ax
+            dim = x.shape[ax]
+            lo = dim + s if s < 0 else DimExpr.of(s)
+            hi = dim if e >= (1 << 31) - 1 else (dim + e if e < 0 else DimExpr.of(e))
+            specs.append((ax, lo, hi, 1))
+            shape[ax] = hi - lo
+        self.set(n, 0, _Val(self.b.slice(x.vid, specs), x.dtype, shape))
+
+    def op_SimplifiedLayerNormalization(self, n):
+        x, w = self.val(n.inputs[0]), self.val(n.inputs[1])
+        attrs = {"epsilon": float(n.attrs.get("epsilon", 1e-5)), "axis": int(n.attrs.get("axis", -1))}
+        out = self.b.composite("SimplifiedLayerNormalization", attrs, [x.vid, w.vid], [(x.dtype, x.shape)])
+        self.set(n, 0, _Val(out[0], x.dtype, x.shape))
+
+    def op_Gelu(self, n):
+        x = self.val(n.inputs[0])
+        approx = n.attrs.get("approximate", "none")
+        out = self.b.composite("Gelu", {"approximate": approx}, [x.vid], [(x.dtype, x.shape)])
+        self.set(n, 0, _Val(out[0], x.dtype, x.shape))
+
+    def op_FastGelu(self, n):  # com.microsoft: the tanh form
+        n.attrs["approximate"] = "tanh"
+        self.op_Gelu(n)
+
+    def op_Softmax(self, n):
+        x = self.val(n.inputs[0])
+        axis = int(n.attrs.get("axis", -1))
+        out = self.b.composite("Softmax", {"axis": axis + len(x.shape) if axis < 0 else axis}, [x.vid], [(x.dtype, x.shape)])
+        self.set(n, 0, _Val(out[0], x.dtype, x.shape))
+
+    def op_MatMulNBits(self, n):
+        bits = int(n.attrs.get("bits", 4))
+        if bits != 4:
+            raise OnnxError(f"MatMulNBits bits={bits}")
+        for a in ("K", "N", "block_size"):
+            if a not in n.attrs:
+                raise OnnxError(f"MatMulNBits '{n.name}': attribute '{a}' is missing")
+        k, nn, bs = int(n.attrs["K"]), int(n.attrs["N"]), int(n.attrs["block_size"])
+        nb = -(-k // bs)
+        a = self.val(n.inputs[0])
+        w = self.val(n.inputs[1], as_type=(ir.U4, [nn, nb, bs]))  # same bytes, honest logical type
+        s = self.val(n.inputs[2])
+        ins = [a.vid, w.vid, s.vid]
+        if self.has(n, 3):
+            try:
+                ins.append(self.val(n.inputs[3], as_type=(ir.U4, [nn, nb])).vid)
+            except OnnxError as e:
+                raise OnnxError(f"MatMulNBits zero_points layout not reinterpretable (odd block counts are padded per row): {e}") from None
+        shape = a.shape[:-1] + [DimExpr.of(nn)]
+        out = self.b.composite("com.microsoft.MatMulNBits", {"K": k, "N": nn, "bits": bits, "block_size": bs}, ins, [(a.dtype, shape)])
+        self.set(n, 0, _Val(out[0], a.dtype, shape))
+
+    def op_GroupQueryAttention(self, n):
+        if float(n.attrs.get("softcap", 0.0)) != 0.0:
+            raise OnnxError("GroupQueryAttention with softcap")
+        rot = int(n.attrs.get("do_rotary", 0)) != 0
+        if rot and self.has(n, 9):
+            raise OnnxError("GroupQueryAttention with do_rotary=1 and explicit position_ids")
+        if len(n.inputs) < 7 or not all(self.has(n, i) for i in range(7)):
+            raise OnnxError("GroupQueryAttention requires q/k/v, past KV, seqlens_k and total_sequence_length inputs")
+        vals = [self.val(n.inputs[i]) for i in range(6)]
+        if vals[5].dtype != ir.I32:
+            raise OnnxError(f"GroupQueryAttention seqlens_k must be int32, got {ir.DTYPE_NAMES[vals[5].dtype]}")
+        ins = [v.vid for v in vals]
+        if rot:
+            if not (self.has(n, 7) and self.has(n, 8)):
+                raise OnnxError("GroupQueryAttention with do_rotary=1 requires cos/sin caches")
+            ins += [self.val(n.inputs[7]).vid, self.val(n.inputs[8]).vid]
+        bias = len(n.inputs) > 10 and self.has(n, 10)
+        if bias:
+            ins.append(self.val(n.inputs[10]).vid)
+        for a in ("num_heads", "kv_num_heads"):
+            if a not in n.attrs:
+                raise OnnxError(f"GroupQueryAttention '{n.name}': attribute '{a}' is missing")
+        attrs = {"num_heads": int(n.attrs["num_heads"]), "kv_num_heads": int(n.attrs["kv_num_heads"]),
+                 "scale": float(n.attrs.get("scale", 0.0)), "local_window_size": int(n.attrs.get("local_window_size", -1)),
+                 "do_rotary": int(rot), "rotary_interleaved": int(n.attrs.get("rotary_interleaved", 0)), "has_attention_bias": int(bias)}
+        q, past = vals[0], vals[3]
+        seq, p_rows = q.shape[1], past.shape[2]
+        total = self.val(n.inputs[6])
+        if total.content:  # computed from shapes by the export: a bind-time constraint, not an operand
+            self.b.constrain(total.content[0], p_rows + seq,
+                             "GroupQueryAttention 'total_sequence_length' must equal the past KV length plus the new sequence length")
+        present = list(past.shape)
+        present[2] = p_rows + seq
+        outs = self.b.composite("com.microsoft.GroupQueryAttention", attrs, ins,
+                                [(q.dtype, q.shape), (past.dtype, present), (past.dtype, present)])
+        for i, o in enumerate(outs):
+            self.set(n, i, _Val(o, q.dtype if i == 0 else past.dtype, q.shape if i == 0 else present))
+
+
+def load_onnx_bytes(data: bytes) -> ir.Module:
+    return _Lower(*parse_model(data)).lower()
+
+
+def load_onnx(path: str) -> ir.Module:
+    with open(path, "rb") as f:
+        return load_onnx_bytes(f.read())
+
+
+# ── writing ──────────────────────────────────────────────────────────────
+def _tensor_proto(name, arr, onnx_dtype=None, dims=None):
+    arr = np.ascontiguousarray(arr)
+    dt = onnx_dtype if onnx_dtype is not None else _ONNX_DT_REV[{np.dtype(v): k for k, v in _NP_OF.items()}[arr.dtype]]
+    out = b"".join(_f_int(1, d) for d in (dims if dims is not None else arr.shape))
+    return out + _f_int(2, dt) + _f_str(8, name) + _f_bytes(9, arr.tobytes())
+
+
+def _attr_proto(name, v):
+    out = _f_str(1, name)
+    if isinstance(v, bool) or isinstance(v, (int, np.integer)):
+        return out + _f_int(3, int(v)) + _f_int(20, 2)
+    if isinstance(v, float):
+        return out + _f_f32(2, v) + _f_int(20, 1)
+    if isinstance(v, str):
+        return out + _f_bytes(4, v.encode()) + _f_int(20, 3)
+    if isinstance(v, (list, tuple)):
+        return out + b"".join(_f_int(8, int(x)) for x in v) + _f_int(20, 7)
+    raise OnnxError(f"attribute '{name}': unsupported value {v!r}")
+
+
+def _value_info(name, dtype, shape):
+    dims = b"".join(_f_bytes(1, _f_str(2, d) if isinstance(d, str) else _f_int(1, d)) for d in shape)
+    tensor = _f_int(1, _ONNX_DT_REV[dtype]) + _f_bytes(2, dims)
+    return _f_str(1, name) + _f_bytes(2, _f_bytes(1, tensor))
+
+
+class OnnxWriter:
+    """Collects nodes, initializers and the signature of one graph; `tobytes()` gives a ModelProto."""
+
+    def __init__(self, name="graph"):
+        self.name, self.nodes, self.inits, self.inputs, self.outputs = name, [], [], [], []
+
+    def node(self, op, inputs, outputs, name="", domain="", **attrs):
+        body = b"".join(_f_str(1, i) for i in inputs) + b"".join(_f_str(2, o) for o in outputs)
+        body += _f_str(3, name) + _f_str(4, op) + b"".join(_f_bytes(5, _attr_proto(k, v)) for k, v in attrs.items())
+        if domain:
+            body += _f_str(7, domain)
+        self.nodes.append(body)
+        return outputs[0]
+
+    def initializer(self, name, arr, onnx_dtype=None, dims=None):
+        self.inits.append(_tensor_proto(name, arr, onnx_dtype, dims))
+        return name
+
+    def input(self, name, dtype, shape):
+        self.inputs.append(_value_info(name, dtype, shape))
+        return name
+
+    def output(self, name, dtype, shape):
+        self.outputs.append(_value_info(name, dtype, shape))
+
+    def tobytes(self) -> bytes:
+        g = b"".join(_f_bytes(1, n) for n in self.nodes) + _f_str(2, self.name) + b"".join(_f_bytes(5, t) for t in self.inits)
+        g += b"".join(_f_bytes(11, i) for i in self.inputs) + b"".join(_f_bytes(12, o) for o in self.outputs)
+        opsets = _f_bytes(8, _f_str(1, "") + _f_int(2, 21)) + _f_bytes(8, _f_str(1, "com.microsoft") + _f_int(2, 1))
+        return _f_int(1, 10) + _f_str(2, "onyxia_b200") + opsets + _f_bytes(7, g)
+
+
+def export_decoder(cfg, seed: int = 0) -> bytes:
+    """The decoder of `models.build_decoder(cfg, seed)` as the ONNX graph an onnxruntime-genai style export of such
+    a model has: contrib operators for the quantised projections and the attention, the sequence lengths derived
+    from `attention_mask` by ReduceSum / Shape arithmetic. Same seeded weights, byte for byte."""
+    from . import models
+    w = OnnxWriter(cfg.name)
+    adt, npa = cfg.act_dtype, cfg.np_act
+    H, D, NH, KV = cfg.hidden, cfg.head_dim, cfg.heads, cfg.kv_heads
+    B, S, P, T = "batch_size", "sequence_length", "past_sequence_length", "total_sequence_length"
+    w.input("input_ids", ir.I64, [B, S])
+    w.input("attention_mask", ir.I64, [B, T])
+    for l in range(cfg.layers):
+        w.input(f"past_key_values.{l}.key", adt, [B, KV, P, D])
+        w.input(f"past_key_values.{l}.value", adt, [B, KV, P, D])
+
+    def nbits(x, name, k, n, out):
+        packed, scales, zp = models.nbits_arrays(cfg, seed, name, k, n)
+        nb = (k + 31) // 32
+        ins = [x, w.initializer(name + ".qweight", packed.reshape(n, nb, 16)), w.initializer(name + ".scales", scales)]
+        if zp is not None:
+            ins.append(w.initializer(name + ".qzeros", zp))
+        return w.node("MatMulNBits", ins, [out], name=name, domain="com.microsoft", K=k, N=n, bits=4, block_size=32)
+
+    def norm(x, name, out):
+        return w.node("SimplifiedLayerNormalization", [x, w.initializer(name + ".weight", models.norm_array(cfg, seed, name, H))], [out],
+                      name=name, epsilon=float(cfg.eps), axis=-1)
+
+    w.initializer("axes_1", np.array([1], np.int64))
+    w.initializer("one_i64", np.array([1], np.int64))
+    w.initializer("idx_1", np.array(1, np.int64))
+    w.node("ReduceSum", ["attention_mask", "axes_1"], ["mask_sum"], name="/model/attn_mask_reformat/seqlens", keepdims=0)
+    w.node("Sub", ["mask_sum", "one_i64"], ["seqlens_i64"])
+    w.node("Cast", ["seqlens_i64"], ["seqlens_k"], to=6)
+    w.node("Shape", ["attention_mask"], ["mask_shape"])
+    w.node("Gather", ["mask_shape", "idx_1"], ["total_i64"], axis=0)
+    w.node("Cast", ["total_i64"], ["total_seq_len"], to=6)
+    cos, sin = models.rope_caches(cfg)
+    w.initializer("cos_cache", cos)
+    w.initializer("sin_cache", sin)
+    w.initializer("embed", models.embed_array(cfg, seed))
+    x = w.node("Gather", ["embed", "input_ids"], ["x0"], name="/model/embed_tokens/Gather", axis=0)
+    for l in range(cfg.layers):
+        pre = f"/model/layers.{l}"
+        h = norm(x, f"{pre}/input_layernorm", f"h{l}")
+        q = nbits(h, f"{pre}/attn/q_proj", H, NH * D, f"q{l}")
+        k = nbits(h, f"{pre}/attn/k_proj", H, KV * D, f"k{l}")
+        v = nbits(h, f"{pre}/attn/v_proj", H, KV * D, f"v{l}")
+        w.node("GroupQueryAttention", [q, k, v, f"past_key_values.{l}.key", f"past_key_values.{l}.value", "seqlens_k", "total_seq_len",
+                                       "cos_cache", "sin_cache"], [f"attn{l}", f"present.{l}.key", f"present.{l}.value"],
+               name=f"{pre}/attn/GroupQueryAttention", domain="com.microsoft", num_heads=NH, kv_num_heads=KV, scale=0.0,
+               local_window_size=cfg.layer_window(l), do_rotary=1, rotary_interleaved=0)
+        o = nbits(f"attn{l}", f"{pre}/attn/o_proj", NH * D, H, f"o{l}")
+        if cfg.sandwich_norms:
+            o = norm(o, f"{pre}/post_attention_layernorm", f"o_n{l}")
+        x = w.node("Add", [x, o], [f"x_a{l}"], name=f"{pre}/residual_add_1")
+        h2 = norm(x, f"{pre}/pre_feedforward_layernorm", f"h2_{l}")
+        gate = nbits(h2, f"{pre}/mlp/gate_proj", H, cfg.ffn, f"gate{l}")
+        up = nbits(h2, f"{pre}/mlp/up_proj", H, cfg.ffn, f"up{l}")
+        act = w.node("Gelu", [gate], [f"act{l}"], name=f"{pre}/mlp/act_fn/Gelu", approximate="tanh" if cfg.gelu_tanh else "none")
+        m = w.node("Mul", [act, up], [f"m{l}"], name=f"{pre}/mlp/Mul")
+        down = nbits(m, f"{pre}/mlp/down_proj", cfg.ffn, H, f"down{l}")
+        if cfg.sandwich_norms:
+            down = norm(down, f"{pre}/post_feedforward_layernorm", f"down_n{l}")
+        x = w.node("Add", [x, down], [f"x_b{l}"], name=f"{pre}/residual_add_2")
+    x = norm(x, "/model/norm", "x_final")
+    if cfg.last_logits_only:
+        w.initializer("minus_1", np.array([-1], np.int64))
+        w.initializer("int_max", np.array([(1 << 63) - 1], np.int64))
+        x = w.node("Slice", [x, "minus_1", "int_max", "axes_1"], ["x_last"], name="/model/last_token/Slice")
+    nbits(x, "/lm_head", H, cfg.vocab, "logits")
+    w.output("logits", adt, [B, 1 if cfg.last_logits_only else S, cfg.vocab])
+    for l in range(cfg.layers):
+        w.output(f"present.{l}.key", adt, [B, KV, T, D])
+        w.output(f"present.{l}.value", adt, [B, KV, T, D])
+    return w.tobytes()
