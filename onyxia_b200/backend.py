@@ -176,6 +176,7 @@ class CudaBackend:
                  disable_graphs: bool = False, disable_pattern_fusion: bool = False,
                  disable_persistent_step: bool = False):
         self._lib = _ffi.cuda_lib()
+        self.devices = tuple(int(d) for d in devices)
         opts = _ffi.BackendOptions()
         opts.without_fused_kernels = int(without_fused_kernels)
         opts.disable_graphs = int(disable_graphs)

@@ -122,7 +122,7 @@ void Session::collect_node_syms() {
         if (group_of_leader_[i] >= 0) {
             const GemvGroup& g = groups_[group_of_leader_[i]];
             for (auto mem : g.members) of_node(mem, s);
-            for (int extra : {g.gelu_node, g.mul_node, g.norm2, g.add, g.norm1})
+            for (int extra : {g.gelu_node, g.mul_node, g.norm2, g.slice, g.add, g.norm1})
                 if (extra >= 0) of_node((size_t)extra, s);
         }
         std::sort(s.begin(), s.end());
@@ -256,7 +256,7 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
             for (auto v : node.inputs) ins.push_back(plan.trefs[v]);
             for (auto v : node.outputs) outs.push_back(plan.trefs[v]);
             if (group_of_leader_[nid] >= 0) {
-                lower_group(em, groups_[group_of_leader_[nid]], plan);
+                lower_group(em, groups_[group_of_leader_[nid]], plan, bindings);
             } else if (node.is_prim && node.prim.kind == PrimKind::Reshape) {
                 // a view: nothing to launch
             } else if (info_[nid].fuse_kind == FUSE_GEGLU) {
@@ -297,12 +297,11 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
 }
 
 // One launch for a group of MatMulNBits nodes with its prologue and epilogue.
-void Session::lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan) {
+void Session::lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan, const Bindings& bindings) {
     const Module& m = module_;
     oxk::NBitsGroup gr{};
     gr.k = g.k;
     gr.has_zp = g.has_zp;
-    gr.m = plan.trefs[g.src].numel() / g.k;
     gr.n_seg = (int)g.members.size();
     for (size_t i = 0; i < g.members.size(); i++) {
         const Node& n = m.nodes[g.members[i]];
@@ -311,25 +310,90 @@ void Session::lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan) {
     }
     gr.geglu = g.geglu;
     if (g.geglu) gr.y[0] = plan.trefs[m.nodes[g.mul_node].outputs[0]];
+    const TRef tiles = plan.trefs[m.nodes[g.members[0]].inputs[1]];  // the group's tile stream lives in the slot of the first member's weight constant
+    TRef src = plan.trefs[g.src];
     TRef w1, w2, res, sum;
     if (g.norm1 >= 0) {
         w1 = plan.trefs[m.nodes[g.norm1].inputs[1]];
-        gr.w1 = &w1;
         gr.eps1 = m.nodes[g.norm1].composite.attrs.float_or("epsilon", 1e-5);
     }
     if (g.add >= 0) {
         res = plan.trefs[g.res];
         sum = plan.trefs[m.nodes[g.add].outputs[0]];
-        gr.res = &res;
-        gr.sum_out = &sum;
     }
     if (g.norm2 >= 0) {
         w2 = plan.trefs[m.nodes[g.norm2].inputs[1]];
-        gr.w2 = &w2;
         gr.eps2 = m.nodes[g.norm2].composite.attrs.float_or("epsilon", 1e-5);
     }
-    // the group's tile stream lives in the slot of the first member's weight constant
-    oxk::emit_nbits_group(em, gr, plan.trefs[g.src], plan.trefs[m.nodes[g.members[0]].inputs[1]]);
+    if (g.slice >= 0) {
+        // Which rows of the chain's [rows, K] operands the slice keeps. When they are one contiguous range the prologue
+        // simply starts there; otherwise the chain runs as separate launches in front of the slice.
+        const Node& sl = m.nodes[g.slice];
+        const std::vector<int64_t>& shp = plan.trefs[sl.inputs[0]].shape;
+        const size_t rank = shp.size();
+        std::vector<int64_t> lo(rank, 0), hi(shp);
+        for (auto& sp : sl.prim.specs) {
+            lo[sp.axis] = (int64_t)sp.start.eval(bindings);
+            hi[sp.axis] = (int64_t)sp.end.eval(bindings);
+            if (lo[sp.axis] < 0 || hi[sp.axis] > shp[sp.axis] || lo[sp.axis] > hi[sp.axis]) fail(ErrKind::Runtime, "slice bounds outside the tensor");
+        }
+        size_t j = 0;
+        while (j + 1 < rank && lo[j] == 0 && hi[j] == shp[j]) j++;  // first axis that is cut (rank − 1: none)
+        bool contiguous = true;
+        for (size_t a = 0; a < j && j + 1 < rank; a++) contiguous = contiguous && shp[a] == 1;
+        for (size_t a = j + 1; a + 1 < rank; a++) contiguous = contiguous && lo[a] == 0 && hi[a] == shp[a];
+        if (contiguous) {
+            int64_t inner = 1;
+            for (size_t a = j + 1; a + 1 < rank; a++) inner *= shp[a];
+            const int64_t row0 = j + 1 < rank ? lo[j] * inner : 0;
+            int64_t rows = 1;
+            for (size_t a = 0; a + 1 < rank; a++) rows *= hi[a] - lo[a];
+            const int64_t off = row0 * g.k * 2;  // f16 rows
+            auto rows_of = [&](TRef& t) {
+                t.buf.off += off;
+                t.shape = {rows, g.k};
+            };
+            rows_of(src);
+            if (g.add >= 0) {
+                rows_of(res);
+                rows_of(sum);
+            }
+        } else {
+            TRef cur = src;
+            if (g.norm1 >= 0) {
+                const TRef out = plan.trefs[m.nodes[g.norm1].outputs[0]];
+                oxk::emit_rmsnorm(em, cur, w1, out, gr.eps1, nullptr, nullptr);
+                cur = out;
+            }
+            if (g.add >= 0) {
+                const Node& ad = m.nodes[g.add];
+                // the operands in graph order: one of them is what the step above wrote (or the plain source)
+                lower_prim(em, ad, bindings, {plan.trefs[ad.inputs[0]], plan.trefs[ad.inputs[1]]}, {sum});
+                cur = sum;
+            }
+            const TRef cut = plan.trefs[sl.outputs[0]];
+            if (g.slice_last) {  // … → norm2 → Slice → the matrices
+                const TRef normed = plan.trefs[m.nodes[g.norm2].outputs[0]];
+                oxk::emit_rmsnorm(em, cur, w2, normed, gr.eps2, nullptr, nullptr);
+                lower_prim(em, sl, bindings, {normed}, {cut});
+            } else {             // … → Slice → norm2 (as the launch's prologue) → the matrices
+                lower_prim(em, sl, bindings, {cur}, {cut});
+                if (g.norm2 >= 0) gr.w2 = &w2;
+            }
+            src = cut;
+            gr.m = src.numel() / g.k;
+            oxk::emit_nbits_group(em, gr, src, tiles);
+            return;
+        }
+    }
+    gr.m = src.numel() / g.k;
+    if (g.norm1 >= 0) gr.w1 = &w1;
+    if (g.add >= 0) {
+        gr.res = &res;
+        gr.sum_out = &sum;
+    }
+    if (g.norm2 >= 0) gr.w2 = &w2;
+    oxk::emit_nbits_group(em, gr, src, tiles);
 }
 
 void Session::finish_outputs(Plan& plan) {

@@ -372,23 +372,63 @@ void Session::find_gemv_groups() {
         }
         // the chain that produces the activations
         g.src = a;
-        const int pn = producer(a);
-        if (pn >= 0 && is_norm(pn) && uses[a] == (int)g.members.size() && !out_uses[a] && alias_root_[a] == a) {
+        // A Slice that only selects rows (the last-token slice in front of the lm_head) commutes with the row-wise
+        // chain: the prologue then works on the selected rows of the chain's operands.
+        auto row_slice = [&](ValueId v) {  // the node when `v` is such a Slice's result that nothing else reads
+            const int sn = producer(v);
+            if (sn < 0 || !m.nodes[sn].is_prim || m.nodes[sn].prim.kind != PrimKind::Slice || info_[sn].absorbed_by >= 0 ||
+                info_[sn].fuse_with >= 0 || out_uses[v] || alias_root_[v] != v)
+                return -1;
+            const Node& sl = m.nodes[sn];
+            const size_t rank = m.values[sl.inputs[0]].ty.shape.size();
+            if (rank < 2 || m.values[sl.inputs[0]].ty.dtype != DType::F16) return -1;
+            for (auto& sp : sl.prim.specs)
+                if (sp.axis + 1 >= rank || sp.step != 1) return -1;
+            return sn;
+        };
+        int pn = producer(a), slice_first = -1;
+        ValueId na = a;  // the value norm2 produces
+        if (uses[a] == (int)g.members.size() && !out_uses[a] && alias_root_[a] == a) {
+            const int sn = row_slice(a);
+            if (sn >= 0) {
+                const ValueId v = m.nodes[sn].inputs[0];
+                const int p2 = producer(v);
+                if (p2 >= 0 && is_norm(p2) && uses[v] == 1 && !out_uses[v] && alias_root_[v] == v) {
+                    slice_first = sn;
+                    pn = p2;
+                    na = v;
+                }
+            }
+        }
+        if (pn >= 0 && is_norm(pn) && (slice_first >= 0 || (uses[a] == (int)g.members.size() && !out_uses[a] && alias_root_[a] == a))) {
             const Node& n2 = m.nodes[pn];
             bool ok = true;
             GemvGroup c = g;
             c.norm2 = pn;
-            c.src = n2.inputs[0];
-            const int an = producer(n2.inputs[0]);
+            ValueId z = n2.inputs[0];
+            if (slice_first >= 0) {
+                c.slice = slice_first;
+                c.slice_last = true;
+            } else if (uses[z] == 1) {
+                const int sn = row_slice(z);
+                if (sn >= 0) {
+                    c.slice = sn;
+                    z = m.nodes[sn].inputs[0];
+                }
+            }
+            c.src = z;
+            const int an = producer(z);
             if (an >= 0 && m.nodes[an].is_prim && m.nodes[an].prim.kind == PrimKind::Binary &&
                 (BinaryOp)m.nodes[an].prim.op == BinaryOp::Add && info_[an].absorbed_by < 0 && info_[an].fuse_with < 0 &&
-                alias_root_[n2.inputs[0]] == n2.inputs[0]) {
+                alias_root_[z] == z) {
                 const Node& ad = m.nodes[an];
                 const TensorType& ts = m.values[ad.outputs[0]].ty;
                 if (m.values[ad.inputs[0]].ty == ts && m.values[ad.inputs[1]].ty == ts && ts.dtype == DType::F16) {
-                    // every other reader of the sum must run after the launch
+                    // every other reader of the sum must run after the launch; behind a slice only some rows of the
+                    // sum are formed, so there must be no other reader at all
                     for (int r : readers[ad.outputs[0]])
-                        if (r != pn && step_of_node_[r] <= step_of_node_[g.leader]) ok = false;
+                        if (r != pn && r != c.slice && (c.slice >= 0 || step_of_node_[r] <= step_of_node_[g.leader])) ok = false;
+                    if (c.slice >= 0 && out_uses[ad.outputs[0]]) ok = false;
                     if (ok) {
                         c.add = an;
                         int which = -1;  // the operand that is itself a norm nothing else reads
@@ -421,6 +461,7 @@ void Session::find_gemv_groups() {
         }
         absorb(g.gelu_node);
         absorb(g.norm2);
+        absorb(g.slice);
         absorb(g.add);
         absorb(g.norm1);
         group_of_leader_[g.leader] = gid;

@@ -139,6 +139,8 @@ private:
         int geglu = 0;                    // 0 none, 1 tanh form, 2 erf form
         int gelu_node = -1, mul_node = -1;
         int norm2 = -1, add = -1, norm1 = -1;  // prologue chain, −1 = absent
+        int slice = -1;                   // a row-selecting Slice in the chain (the last-token slice), −1 = absent
+        bool slice_last = false;          // the Slice reads norm2's result (else norm2 reads the Slice's)
         ValueId src = 0, res = 0;         // what the prologue reads (src = the members' input without a prologue)
         bool has_zp = false;
         int64_t k = 0;
@@ -146,7 +148,7 @@ private:
     std::vector<GemvGroup> groups_;
     std::vector<int> group_of_leader_;    // per node: index into groups_ or −1
     void find_gemv_groups();
-    void lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan);
+    void lower_group(oxk::Emitter& em, const GemvGroup& g, Plan& plan, const ox::Bindings& bindings);
 
     void upload_constants();
     void interleave_weights();

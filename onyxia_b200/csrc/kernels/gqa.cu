@@ -360,6 +360,12 @@ template <int DT> static void emit_gqa_t(Emitter& em, const GqaDesc& d, const TR
                {&pp.dyn_t, dyn_t}},
               "gqa_prepare", /*pdl=*/true);
 
+    if constexpr (DT == DT_F16) {
+        // many new positions: scores and P·V on the tensor cores
+        if (!bias && emit_gqa_prefill_tc(em, d, d.rot_half ? qrot : q.buf, seqlens, out, present_k, present_v, dyn_t, dyn ? 0 : T, pp.pres_cap))
+            return;
+    }
+
     GqaAttnP ap{};
     ap.B = B; ap.S = S; ap.H = H; ap.KV = KV; ap.D = D; ap.T = dyn ? 0 : T;
     ap.cap = pp.pres_cap;

@@ -255,6 +255,9 @@ void emit_gqa(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef
 // clusters; false when the shape is outside what that kernel handles. `t_size`
 // bounds the present length the launch is sized for; the true length is read
 // from `dyn_t` at run time.
+// Attention over many new positions on the tensor cores (f16, no bias; after gqa_prepare). False = shape not taken.
+bool emit_gqa_prefill_tc(Emitter&, const GqaDesc&, Buf q_rot, const TRef& seqlens, const TRef& out, const TRef& present_k,
+                         const TRef& present_v, Buf dyn_t, long long T, long long cap);
 bool emit_gqa_decode(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef& v, const TRef& seqlens,
                      const TRef* cos, const TRef* sin, const TRef& out, const TRef& present_k, const TRef& present_v,
                      Buf dyn_t, long long t_size);

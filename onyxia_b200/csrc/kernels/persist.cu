@@ -1040,43 +1040,48 @@ __global__ void __launch_bounds__(kPT, 1) persist_step(const __grid_constant__ P
 
     if (warp == kCW) {
         // ── producer: this CTA's tile records of every GEMV, in execution order ──
-        if (lane == 0) {
-            unsigned q = 0;
-            bool ok = true;
-            for (int i = 0; i < p.n_ops && ok; i++) {
-                if (p.ops[i].kind != POP_GEMV) continue;
-                const PGemvDev& g = p.ops[i].g;
-                int rt_first, my_rts;
-                gemv_share(g, &rt_first, &my_rts);
-                const int kt_n = g.k_tiles, spr = (kt_n + kStTiles - 1) / kStTiles;
-                for (int r = 0; r < my_rts && ok; r++) {
-                    const unsigned char* src = g.tiles + ((size_t)(rt_first + r) * kt_n) * kTileB;
-                    for (int s = 0; s < spr; s++, q++) {
-                        const int cnt = kt_n - s * kStTiles < kStTiles ? kt_n - s * kStTiles : kStTiles;
-                        const unsigned slot = q % (unsigned)R;
-                        if (q >= (unsigned)R && !wait_bar(c, bars + (R + slot) * 8, ((q / (unsigned)R) - 1u) & 1u, p.ops[i].node)) {
-                            ok = false;
-                            break;
-                        }
-#ifdef OX_TRACE
-                        if ((blockIdx.x == 0 || blockIdx.x == 40) && i >= 10 && i <= 16) {
-                            unsigned long long* t = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(pk.err) + 256) + 1 + 8 * 990 + (blockIdx.x / 40) * 100;
-                            unsigned long long now;
-                            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-                            const int k = (int)(q % 100u);
-                            t[k] = ((unsigned long long)i << 56) | ((unsigned long long)(q & 0xFFFF) << 40) | (now & 0xFFFFFFFFFFull);
-                        }
-#endif
+        // Eight lanes issue eight consecutive stages at a time (a lane waits for its own slot to be free, arms the
+        // slot's barrier and starts its copy): one lane alone spends ≈ 250 ns per stage on the slot arithmetic and
+        // the barrier, which bounds an SM at 14 GB/s — enough for the layers, whose weights are resident long
+        // before they are used, but not for the 170 MB of an lm_head. More lanes per round would shorten the
+        // distance the ring runs ahead (a round waits for its last slot).
+        constexpr int kIssue = 8;
+        unsigned q = 0;
+        bool ok = true;
+        for (int i = 0; i < p.n_ops && ok; i++) {
+            if (p.ops[i].kind != POP_GEMV) continue;
+            const PGemvDev& g = p.ops[i].g;
+            int rt_first, my_rts;
+            gemv_share(g, &rt_first, &my_rts);
+            const int kt_n = g.k_tiles, spr = (kt_n + kStTiles - 1) / kStTiles;
+            const int n_st = my_rts * spr;
+            const unsigned char* base = g.tiles + ((size_t)rt_first * kt_n) * kTileB;
+            for (int i0 = 0; i0 < n_st && ok; i0 += kIssue) {
+                const int idx = i0 + lane;
+                bool mine_ok = true;
+                if (lane < kIssue && idx < n_st) {
+                    const int r = idx / spr, s = idx - r * spr;
+                    const int cnt = kt_n - s * kStTiles < kStTiles ? kt_n - s * kStTiles : kStTiles;
+                    const unsigned qq = q + (unsigned)idx, round = qq / (unsigned)R, slot = qq - round * (unsigned)R;
+                    if (round == 0 || wait_bar(c, bars + (R + slot) * 8, (round - 1u) & 1u, p.ops[i].node)) {
                         mbar_expect(bars + slot * 8, (unsigned)cnt * kTileB);
-                        bulk_load(smem_addr(smem + (size_t)slot * kStageB), src + (size_t)s * kStageB, (unsigned)cnt * kTileB, bars + slot * 8);
+                        bulk_load(smem_addr(smem + (size_t)slot * kStageB), base + ((size_t)r * kt_n + (size_t)s * kStTiles) * kTileB,
+                                  (unsigned)cnt * kTileB, bars + slot * 8);
+                    } else {
+                        mine_ok = false;
                     }
                 }
+                ok = __all_sync(0xffffffffu, mine_ok);
+                if (!ok) q += (unsigned)(i0 + kIssue < n_st ? i0 + kIssue : n_st);  // an upper bound of what was started
             }
-            if (!ok) {
-                // a consumer gave up: let the copies still in flight land before the ring goes away
-                const unsigned from = q > (unsigned)R ? q - (unsigned)R : 0u;
-                for (unsigned s = from; s < q; s++) mbar_wait(bars + (s % (unsigned)R) * 8, (s / (unsigned)R) & 1u, kWaitP);
-            }
+            if (ok) q += (unsigned)n_st;
+        }
+        if (!ok && lane == 0) {
+            // a consumer gave up: let the copies still in flight land before the ring goes away (a slot whose copy
+            // was never started does not complete: the wait on it runs into its limit, once)
+            const unsigned from = q > (unsigned)R ? q - (unsigned)R : 0u;
+            for (unsigned s = from; s < q; s++)
+                if (!mbar_wait(bars + (s % (unsigned)R) * 8, (s / (unsigned)R) & 1u, kWaitP)) break;
         }
     } else {
         unsigned stage_q = 0;

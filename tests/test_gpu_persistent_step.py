@@ -92,3 +92,26 @@ def test_persistent_step_when_rows_are_shorter_than_the_cache():
                 g, w = got[f"present.{l}.{part}"].numpy(), want[f"present.{l}.{part}"].numpy()
                 assert g.shape == w.shape
                 assert np.abs(g.astype(np.float32) - w.astype(np.float32)).max() <= 2e-3, (l, part)
+
+
+@pytest.mark.parametrize("batch,seq,past", [(1, 7, 0), (2, 5, 3), (3, 1, 6), (1, 1, 9)])
+def test_last_token_slice_inside_the_lm_head_group(batch, seq, past):
+    """The last-token Slice sits between the final norm chain and the lm_head. One row of one sequence is a contiguous
+    row range (the group's prologue starts there); the last rows of several sequences are not (the chain then runs as
+    separate launches in front of the slice). Both must give the interpreter's logits."""
+    from oracle import ref
+    ref.set_threads(8)
+    cfg = _cfg(64, 4, 2, sandwich=True, layers=2)
+    module = models.build_decoder(cfg, seed=21)
+    rng = np.random.default_rng(batch * 10 + seq)
+    feed = {"input_ids": ir.HostTensor.from_numpy(rng.integers(0, cfg.vocab, (batch, seq)).astype(np.int64)),
+            "attention_mask": ir.HostTensor.from_numpy(np.ones((batch, past + seq), np.int64))}
+    for l in range(cfg.layers):
+        for part in ("key", "value"):
+            feed[f"past_key_values.{l}.{part}"] = ir.HostTensor.from_numpy(
+                rng.standard_normal((batch, cfg.kv_heads, past, cfg.head_dim)).astype(np.float16))
+    want = dict(ref.run_once(module.clone(), feed))["logits"].numpy().astype(np.float64)
+    got = dict(be.run_once(be.CudaBackend((0,)), module, feed))["logits"].numpy().astype(np.float64)
+    assert got.shape == want.shape == (batch, 1, cfg.vocab)
+    assert np.abs(got - want).max() <= 2e-2
+    assert np.array_equal(got.argmax(-1), want.argmax(-1))

@@ -81,9 +81,14 @@ def main():
     mine = run(backend, module.tp_partition(world, rank), slice(rank * per, (rank + 1) * per))
     if rank == 0:
         whole = run(be.CudaBackend((local,)), module, slice(0, cfg.kv_heads))
-        diff = float(np.abs(whole - mine).max())
-        print(f"tp={world} 27B-architecture width, 2 layers, batch {B}: max abs diff vs one GPU: {diff:.5f}", flush=True)
-        assert diff <= 2e-2, diff
+        d = np.abs(whole - mine)
+        diff, mean = float(d.max()), float(d.mean())
+        print(f"tp={world} 27B-architecture width, 2 layers, batch {B}: vs one GPU max abs diff {diff:.5f}, mean {mean:.6f}", flush=True)
+        # Same bounds as the single-GPU check of this width against the interpreter: the two runs add their f32
+        # tensor-core partial sums in different orders (K is cut between the ranks), which moves single logits by a
+        # few f16 spacings; the greedy ids must not move.
+        assert np.array_equal(whole.argmax(-1), mine.argmax(-1)), "greedy ids differ between the partitioned and the whole model"
+        assert mean <= 1e-2 and diff <= 0.125, (mean, diff)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank} ok", flush=True)
