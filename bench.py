@@ -559,7 +559,7 @@ def main():
     d2h = 8
     # the same through the native loop (`ox_llm_step`: one library call per step)
     native = llm.NativeLlmSession(backend, e2e_module, 4096)
-    native.step_greedy(prompt[:8])  # builds the plans and graphs of a prefill before the timed one
+    native.step_greedy(prompt)  # warm-up: plans, kernel attributes and lookup tables of a prefill of this length (bench.rs:140-150)
     native.reset()
     t0 = time.perf_counter()
     ntok = native.step_greedy(prompt)

@@ -285,6 +285,22 @@ void ox_session_plan_stats(const ox_session*, uint64_t out[9]);
  * crates/onyxia-cli/src/sampling.rs:71-80, which keeps the last maximum).
  * Returns an I64 tensor shaped like `logits` without its last axis. */
 ox_status ox_session_argmax_last(ox_session*, const ox_tensor* logits, ox_tensor** out);
+/* Temperature / top-k / top-p sampling on the device ≙ sampling::sample
+ * (crates/onyxia-cli/src/sampling.rs:36-195): the logits of every row are divided
+ * by `temperature`; `top_k` > 0 keeps the k largest (k at or above the vocabulary:
+ * all of them), otherwise 0 < `top_p` < 1 keeps the shortest prefix of the
+ * descending order whose cumulative probability reaches p, otherwise all are kept;
+ * the token is the first index at which the running sum of exp(l - max) over the
+ * kept entries reaches uniform[row] * sum. The random generator stays with the
+ * caller: `uniform` holds one number in [0, 1] per row (the reference uses
+ * next_u32 / u32::MAX). A temperature at or below 1e-6 selects greedily, like the
+ * reference. Sums are exact and ties among equal logits are kept in index order,
+ * so a draw is reproducible; it can differ from the reference's f32 running sums
+ * only when uniform * sum falls within rounding of a boundary between two tokens.
+ * Rows without a finite logit are reported as OX_ERR_RUNTIME at the next
+ * synchronising call. Returns an I64 tensor shaped like `logits` without its last axis. */
+ox_status ox_session_sample_last(ox_session*, const ox_tensor* logits, float temperature, int64_t top_k, float top_p,
+                                 const float* uniform, size_t n_uniform, ox_tensor** out);
 /* The same argmax written into a tensor the caller already holds, without
  * allocating anything: no device allocation, no buffer from the session's pool,
  * no new tensor handle. One kernel is enqueued on the session's stream; its
@@ -318,6 +334,11 @@ int32_t ox_llm_logits_dtype(const ox_llm*); /* ox_dtype code of the logits `ox_l
 void ox_llm_reset(ox_llm*);
 ox_status ox_llm_step(ox_llm*, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
                       size_t* logits_written);
+/* The same step with the next token drawn on the device from the last position's logits by temperature /
+ * top-k / top-p sampling (see ox_session_sample_last; crates/onyxia-cli/src/sampling.rs:36-65); `uniform` is
+ * the caller's random number in [0, 1]. */
+ox_status ox_llm_step_sampled(ox_llm*, const int64_t* ids, int32_t n_ids, float temperature, int64_t top_k, float top_p, float uniform,
+                              int64_t* token_out);
 
 #ifdef __cplusplus
 }

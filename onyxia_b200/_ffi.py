@@ -122,6 +122,7 @@ SIGNATURES = {
     "ox_session_plan_stats": (None, [_P, _u64p]),
     "ox_session_argmax_last": (C.c_int32, [_P, _P, C.POINTER(_P)]),
     "ox_session_argmax_last_into": (C.c_int32, [_P, _P, _P]),
+    "ox_session_sample_last": (C.c_int32, [_P, _P, C.c_float, C.c_int64, C.c_float, C.POINTER(C.c_float), C.c_size_t, C.POINTER(_P)]),
     "ox_llm_create": (C.c_int32, [_P, C.c_int64, C.POINTER(_P)]),
     "ox_llm_free": (None, [_P]),
     "ox_llm_sequence_length": (C.c_int64, [_P]),
@@ -129,6 +130,8 @@ SIGNATURES = {
     "ox_llm_reset": (None, [_P]),
     "ox_llm_step": (C.c_int32, [_P, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int64), C.c_void_p, C.c_size_t,
                                 C.POINTER(C.c_size_t)]),
+    "ox_llm_step_sampled": (C.c_int32, [_P, C.POINTER(C.c_int64), C.c_int32, C.c_float, C.c_int64, C.c_float, C.c_float,
+                                        C.POINTER(C.c_int64)]),
     "ox_tp_unique_id": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint8)]),
     "ox_backend_join_tp": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint8), C.c_char_p]),
 }

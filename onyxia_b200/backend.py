@@ -98,6 +98,15 @@ class CudaSession:
         check(self._lib.ox_session_argmax_last(self._h, t.handle, C.byref(out)))
         return DeviceTensor(out)
 
+    def sample_last(self, t: DeviceTensor, temperature: float, top_k: int, top_p: float, uniform) -> DeviceTensor:
+        """One token per row by temperature / top-k / top-p sampling on the device (≙ sampling::sample,
+        crates/onyxia-cli/src/sampling.rs:36-65); `uniform` holds one number in [0, 1] per row."""
+        u = np.ascontiguousarray(np.asarray(uniform, dtype=np.float32).reshape(-1))
+        out = C.c_void_p()
+        check(self._lib.ox_session_sample_last(self._h, t.handle, float(temperature), int(top_k), float(top_p),
+                                               u.ctypes.data_as(C.POINTER(C.c_float)), u.size, C.byref(out)))
+        return DeviceTensor(out)
+
     def argmax_last_into(self, t: DeviceTensor, out: DeviceTensor) -> None:
         """Argmax over the last axis written into `out` (I64, one element per row); allocates nothing."""
         check(self._lib.ox_session_argmax_last_into(self._h, t.handle, out.handle))

@@ -219,6 +219,21 @@ ox_status ox_session_argmax_last(ox_session* s, const ox_tensor* logits, ox_tens
     OX_CATCH
 }
 
+ox_status ox_session_sample_last(ox_session* s, const ox_tensor* logits, float temperature, int64_t top_k, float top_p,
+                                 const float* uniform, size_t n_uniform, ox_tensor** out) {
+    OX_TRY
+    auto* t = new ox_tensor();
+    try {
+        t->t = s->s->sample_last(logits->t, temperature, (long long)top_k, top_p, uniform, n_uniform);
+    } catch (...) {
+        delete t;
+        throw;
+    }
+    *out = t;
+    return OX_OK;
+    OX_CATCH
+}
+
 ox_status ox_session_argmax_last_into(ox_session* s, const ox_tensor* logits, ox_tensor* out) {
     OX_TRY
     s->s->argmax_last_into(logits->t, out->t);

@@ -75,8 +75,31 @@ void ox_llm_reset(ox_llm* l) {
 // One forward pass over `n_ids` new tokens. With `token_out` the argmax of the last position's logits is
 // taken on the device and returned; with `logits_out` the last position's logits are copied out in their
 // stored dtype (`logits_cap` bytes available, `logits_written` set).
+namespace {
+struct SamplingArgs {
+    float temperature, top_p, uniform;
+    int64_t top_k;
+};
+ox_status llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
+                   size_t* logits_written, const SamplingArgs* sampling);
+}  // namespace
+
 ox_status ox_llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
                       size_t* logits_written) {
+    return llm_step(l, ids, n_ids, token_out, logits_out, logits_cap, logits_written, nullptr);
+}
+
+// The same step with the next token drawn on the device by temperature / top-k / top-p sampling
+// (crates/onyxia-cli/src/sampling.rs:36-65) from the caller's uniform number in [0, 1].
+ox_status ox_llm_step_sampled(ox_llm* l, const int64_t* ids, int32_t n_ids, float temperature, int64_t top_k, float top_p, float uniform,
+                              int64_t* token_out) {
+    const SamplingArgs a{temperature, top_p, uniform, top_k};
+    return llm_step(l, ids, n_ids, token_out, nullptr, 0, nullptr, &a);
+}
+
+namespace {
+ox_status llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
+                   size_t* logits_written, const SamplingArgs* sampling) {
     OX_TRY
     if (n_ids <= 0) fail(ErrKind::Shape, "Cannot step with empty input_ids");
     if (l->past + n_ids > l->max_seq_len)
@@ -129,7 +152,16 @@ ox_status ox_llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* tok
     l->past += n_ids;
     const oxrt::DTensor& logits = outs[(size_t)l->logits_out].second;
     oxrt::DTensor tok;
-    if (token_out) tok = s.argmax_last(logits);
+    if (token_out && sampling) {
+        // the last position's row of a [1, S, V] tensor
+        const int64_t vocab = logits.shape.back(), rows = logits.numel() / vocab;
+        oxrt::DTensor last = logits;
+        last.shape = {1, vocab};
+        last.offset += (size_t)(rows - 1) * dtype_storage_bytes(logits.dtype, (uint64_t)vocab);
+        tok = s.sample_last(last, sampling->temperature, (long long)sampling->top_k, sampling->top_p, &sampling->uniform, 1);
+    } else if (token_out) {
+        tok = s.argmax_last(logits);
+    }
     // While the device works on this step, get the plan of the next one-token step ready.
     if (l->past + 1 <= l->max_seq_len) {
         std::vector<std::pair<std::string, oxrt::DTensor>> next;
@@ -168,5 +200,6 @@ ox_status ox_llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* tok
     return OX_OK;
     OX_CATCH
 }
+}  // namespace
 
 }  // extern "C"

@@ -711,6 +711,7 @@ void Session::check_device_error() {
         case oxk::ERR_INT_DIV_ZERO: what = "integer division by zero"; break;
         case oxk::ERR_INT_POW_NEG: what = "integer pow with negative exponent"; break;
         case oxk::ERR_WAIT_TIMEOUT: what = "a bounded device-side wait gave up"; break;
+        case oxk::ERR_SAMPLE_NO_FINITE: what = "All logits are NaN or Inf, cannot sample (row " + std::to_string(e.a) + ")"; break;
         default: what = "device error code " + std::to_string(e.code);
     }
     fail(ErrKind::Runtime, kind + " (node '" + node + "'): " + what);
@@ -788,6 +789,35 @@ DTensor Session::argmax_last(const DTensor& logits) {
     BufferRef part = pool_->alloc(oxk::argmax_scratch_bytes(rows));
     oxk::emit_argmax_last(em, x, y, Buf{2, 0}, Buf{3, 0});
     launch_now(em, {logits.ptr(), out.ptr(), part->ptr, (void*)d_counters_});
+    return out;
+}
+
+// Temperature / top-k / top-p sampling of one token per row (crates/onyxia-cli/src/sampling.rs:36-65); `u` holds one
+// uniform number in [0, 1] per row. A temperature at or below 1e-6 selects greedily, like the reference.
+DTensor Session::sample_last(const DTensor& logits, float temperature, long long top_k, float top_p, const float* u, size_t n_u) {
+    if (temperature <= 0.f || temperature < 1e-6f) return argmax_last(logits);
+    OX_CUDA(cudaSetDevice(device_));
+    if (!dtype_is_float(logits.dtype) || logits.shape.empty() || logits.shape.back() == 0)
+        fail(ErrKind::DType, "sampling needs a float tensor with a non-empty last axis");
+    if (logits.cap != 0) fail(ErrKind::Shape, "sampling: logits must be densely packed");
+    if (top_k < 0) fail(ErrKind::Attribute, "top_k must not be negative");
+    DTensor out;
+    out.dtype = DType::I64;
+    out.shape.assign(logits.shape.begin(), logits.shape.end() - 1);
+    const int64_t rows = out.numel();
+    if ((int64_t)n_u != rows) fail(ErrKind::Shape, "sampling needs one uniform number per row of the logits: " + std::to_string(rows));
+    out.buf = pool_->alloc(std::max<size_t>(out.nbytes(), 8));
+    DTensor ud = upload(DType::F32, {rows}, u, sizeof(float) * (size_t)rows);
+    oxk::Emitter em;
+    TRef x{Buf{0, 0}, (int)logits.dtype, logits.shape, 0}, y{Buf{1, 0}, (int)DType::I64, out.shape, 0};
+    oxk::emit_sample_rows(em, x, y, Buf{2, 0}, temperature, top_k, top_p);
+    // slot kSlotErr resolves through launch_now's slot table only for small indices: patch the error word by hand
+    for (auto& r : em.recs)
+        for (auto& rl : r.relocs)
+            if (rl.buf.slot == oxk::kSlotErr) rl.buf = Buf{3, rl.buf.off};
+    launch_now(em, {logits.ptr(), out.ptr(), ud.ptr(), (void*)d_err_});
+    OX_CUDA(cudaMemcpyAsync(h_err_, d_err_, sizeof(oxk::ErrWord), cudaMemcpyDeviceToHost, stream_));
+    err_pending_ = true;
     return out;
 }
 

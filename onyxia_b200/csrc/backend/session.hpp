@@ -95,6 +95,7 @@ public:
     void preplan(const std::vector<std::pair<std::string, DTensor>>& next_inputs);
     void download(const DTensor& t, void* dst, size_t cap, size_t* written);
     DTensor argmax_last(const DTensor& logits);
+    DTensor sample_last(const DTensor& logits, float temperature, long long top_k, float top_p, const float* u, size_t n_u);
     void argmax_last_into(const DTensor& logits, const DTensor& out);
     void wait_idle();
     void timer_start();

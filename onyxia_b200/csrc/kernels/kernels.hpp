@@ -29,6 +29,7 @@ enum : int {
     ERR_INT_POW_NEG = 4,
     ERR_SLICE_OOB = 5,
     ERR_WAIT_TIMEOUT = 6,
+    ERR_SAMPLE_NO_FINITE = 7,
 };
 
 struct ErrWord {
@@ -255,6 +256,9 @@ void emit_gqa(Emitter&, const GqaDesc&, const TRef& q, const TRef& k, const TRef
 // clusters; false when the shape is outside what that kernel handles. `t_size`
 // bounds the present length the launch is sized for; the true length is read
 // from `dyn_t` at run time.
+// One token per row of `logits` by temperature / top-k / top-p sampling (crates/onyxia-cli/src/sampling.rs:36-195);
+// `u` holds one uniform number in [0, 1] per row.
+void emit_sample_rows(Emitter&, const TRef& logits, const TRef& out, Buf u, float temperature, long long top_k, float top_p);
 // Attention over many new positions on the tensor cores (f16, no bias; after gqa_prepare). False = shape not taken.
 bool emit_gqa_prefill_tc(Emitter&, const GqaDesc&, Buf q_rot, const TRef& seqlens, const TRef& out, const TRef& present_k,
                          const TRef& present_v, Buf dyn_t, long long T, long long cap);

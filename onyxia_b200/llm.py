@@ -147,6 +147,17 @@ class NativeLlmSession:
         _ffi.check(self._lib.ox_llm_step(self._h, arr, len(ids), C.byref(tok), None, 0, None))
         return tok.value
 
+    def step_sampled(self, ids, temperature: float, top_k: int, top_p: float, uniform: float) -> int:
+        """The step with the next token drawn on the device (≙ sampling::sample, crates/onyxia-cli/src/sampling.rs:36-65);
+        `uniform` is the caller's random number in [0, 1]."""
+        C = self._C
+        from . import _ffi
+        arr = (C.c_int64 * len(ids))(*ids)
+        tok = C.c_int64()
+        _ffi.check(self._lib.ox_llm_step_sampled(self._h, arr, len(ids), float(temperature), int(top_k), float(top_p), float(uniform),
+                                                 C.byref(tok)))
+        return tok.value
+
     def step_logits(self, ids) -> np.ndarray:
         C = self._C
         from . import _ffi

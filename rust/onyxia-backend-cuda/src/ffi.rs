@@ -181,6 +181,8 @@ unsafe extern "C" {
     pub fn ox_session_take_timings(s: *mut ox_session, out: *mut ox_kernel_timing, cap: i32) -> i32;
     pub fn ox_session_launch_count(s: *const ox_session) -> u64;
     pub fn ox_session_argmax_last(s: *mut ox_session, logits: *const ox_tensor, out: *mut *mut ox_tensor) -> i32;
+    pub fn ox_session_sample_last(s: *mut ox_session, logits: *const ox_tensor, temperature: f32, top_k: i64, top_p: f32,
+                                  uniform: *const f32, n_uniform: usize, out: *mut *mut ox_tensor) -> i32;
     pub fn ox_session_argmax_last_into(s: *mut ox_session, logits: *const ox_tensor, out: *mut ox_tensor) -> i32;
 
     pub fn ox_llm_create(s: *mut ox_session, max_seq_len: i64, out: *mut *mut ox_llm) -> i32;
@@ -190,4 +192,6 @@ unsafe extern "C" {
     pub fn ox_llm_reset(l: *mut ox_llm);
     pub fn ox_llm_step(l: *mut ox_llm, ids: *const i64, n_ids: i32, token_out: *mut i64, logits_out: *mut c_void, logits_cap: usize,
                        logits_written: *mut usize) -> i32;
+    pub fn ox_llm_step_sampled(l: *mut ox_llm, ids: *const i64, n_ids: i32, temperature: f32, top_k: i64, top_p: f32, uniform: f32,
+                               token_out: *mut i64) -> i32;
 }

@@ -536,6 +536,15 @@ impl CudaSession {
         check(unsafe { ffi::ox_session_argmax_last(self.raw, logits.raw(), &mut out) })?;
         Ok(CudaTensor(Arc::new(Handle(out))))
     }
+    /// Temperature / top-k / top-p choice on the device ≙ `sample` (crates/onyxia-cli/src/sampling.rs:36-65). The caller
+    /// keeps the generator: `uniform` holds one `next_u32() as f32 / u32::MAX as f32` per row of the logits.
+    pub fn sample_last(&mut self, logits: &CudaTensor, temperature: f32, top_k: usize, top_p: f32, uniform: &[f32]) -> Result<CudaTensor> {
+        let mut out = ptr::null_mut();
+        check(unsafe {
+            ffi::ox_session_sample_last(self.raw, logits.raw(), temperature, top_k as i64, top_p, uniform.as_ptr(), uniform.len(), &mut out)
+        })?;
+        Ok(CudaTensor(Arc::new(Handle(out))))
+    }
 }
 
 #[async_trait::async_trait(?Send)]
@@ -605,6 +614,13 @@ impl<'s> CudaLlm<'s> {
     pub fn step_greedy(&mut self, ids: &[i64]) -> Result<i64> {
         let mut tok = 0i64;
         check(unsafe { ffi::ox_llm_step(self.raw, ids.as_ptr(), ids.len() as i32, &mut tok, ptr::null_mut(), 0, ptr::null_mut()) })?;
+        Ok(tok)
+    }
+    /// The same step with the next token drawn on the device ≙ `sample` (crates/onyxia-cli/src/sampling.rs:36-65);
+    /// `uniform` is `rng.next_u32() as f32 / u32::MAX as f32` from the caller's generator.
+    pub fn step_sampled(&mut self, ids: &[i64], temperature: f32, top_k: usize, top_p: f32, uniform: f32) -> Result<i64> {
+        let mut tok = 0i64;
+        check(unsafe { ffi::ox_llm_step_sampled(self.raw, ids.as_ptr(), ids.len() as i32, temperature, top_k as i64, top_p, uniform, &mut tok) })?;
         Ok(tok)
     }
     pub fn sequence_length(&self) -> i64 {
