@@ -175,6 +175,10 @@ ox_status ox_module_validate(const ox_module*);
 /* ≙ decomp::inline_composites (crates/onyxia-ir/src/decomp.rs:73-133) with
  * `supports(name) = name ∈ keep`. Rewrites the module in place. */
 ox_status ox_module_inline_composites(ox_module*, const char* const* keep, int32_t n_keep);
+/* ≙ fold::fold_transpose_into_matmul followed by eliminate_dead (crates/onyxia-ir/src/fold.rs:129-204): a
+ * Transpose of the last two axes feeding a MatMul operand becomes the MatMul's trans flag. Returns 1 when
+ * something was folded, 0 when not, -1 on an internal error. */
+int32_t ox_module_fold_transposes(ox_module*);
 
 /* Introspection used by callers such as LlmSession (crates/onyxia-cli/src/llm.rs:47-61,232-246). */
 int32_t ox_module_num_nodes(const ox_module*);

@@ -85,6 +85,7 @@ SIGNATURES = {
     "ox_module_set_loc": (None, [_P, C.c_char_p, C.c_char_p]),
     "ox_module_validate": (C.c_int32, [_P]),
     "ox_module_inline_composites": (C.c_int32, [_P, C.POINTER(C.c_char_p), C.c_int32]),
+    "ox_module_fold_transposes": (C.c_int32, [_P]),
     "ox_module_num_nodes": (C.c_int32, [_P]),
     "ox_module_num_values": (C.c_int32, [_P]),
     "ox_module_num_inputs": (C.c_int32, [_P]),

@@ -571,6 +571,35 @@ void Module::remove_nodes(const std::unordered_set<NodeId>& dead) {
     values = std::move(kept_values);
 }
 
+// A Transpose that swaps the last two axes of a MatMul operand (identity on the batch axes) becomes the
+// MatMul's trans flag; the orphaned Transpose is left to eliminate_dead (crates/onyxia-ir/src/fold.rs:129-178).
+// Tied-embedding exports feed the lm_head as MatMul(h, Transpose(W)): without the fold every run would
+// materialise the transposed weight again.
+bool fold_transpose_into_matmul(Module& m) {
+    auto swaps_last_two = [](const std::vector<size_t>& perm) {
+        const size_t r = perm.size();
+        if (r < 2) return false;
+        for (size_t i = 0; i + 2 < r; i++)
+            if (perm[i] != i) return false;
+        return perm[r - 2] == r - 1 && perm[r - 1] == r - 2;
+    };
+    bool changed = false;
+    for (auto& n : m.nodes) {
+        if (!n.is_prim || n.prim.kind != PrimKind::MatMul) continue;
+        for (int side = 0; side < 2; side++) {
+            const Origin& o = m.values[n.inputs[side]].origin;
+            if (o.kind != Origin::Node) continue;
+            const Node& prod = m.nodes[o.id];
+            if (!prod.is_prim || prod.prim.kind != PrimKind::Transpose || !swaps_last_two(prod.prim.axes)) continue;
+            n.inputs[side] = prod.inputs[0];
+            if (side == 0) n.prim.trans_a = !n.prim.trans_a;
+            else n.prim.trans_b = !n.prim.trans_b;
+            changed = true;
+        }
+    }
+    return changed;
+}
+
 size_t eliminate_dead(Module& m) {
     size_t removed = 0;
     for (;;) {

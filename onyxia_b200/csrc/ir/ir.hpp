@@ -328,6 +328,7 @@ void tp_partition_stats(const Module& m, int tp, size_t* col, size_t* row, size_
 
 // Remove nodes none of whose outputs are consumed; returns how many.
 size_t eliminate_dead(Module& m);
+bool fold_transpose_into_matmul(Module& m);
 
 // ───────────────────────── inference / validation ──────────────────────
 // Total over the primitive set (crates/onyxia-ir/src/infer.rs:26-318).

@@ -225,6 +225,18 @@ ox_status ox_module_inline_composites(ox_module* m, const char* const* keep, int
     OX_CATCH
 }
 
+// fold_transpose_into_matmul followed by eliminate_dead; returns 1 when a Transpose was folded, −1 on error.
+int32_t ox_module_fold_transposes(ox_module* m) {
+    try {
+        Module& mod = m->b.module();
+        const bool changed = fold_transpose_into_matmul(mod);
+        if (changed) eliminate_dead(mod);
+        return changed ? 1 : 0;
+    } catch (...) {
+        return -1;
+    }
+}
+
 int32_t ox_module_num_nodes(const ox_module* m) { return (int32_t) const_cast<ox_module*>(m)->b.module().nodes.size(); }
 int32_t ox_module_num_values(const ox_module* m) { return (int32_t) const_cast<ox_module*>(m)->b.module().values.size(); }
 int32_t ox_module_num_inputs(const ox_module* m) { return (int32_t) const_cast<ox_module*>(m)->b.module().inputs.size(); }

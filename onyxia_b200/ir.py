@@ -217,6 +217,13 @@ class Module:
         check(_ffi.ir_lib().ox_module_inline_composites(self.handle, arr, len(names)))
         return self
 
+    def fold_transposes(self) -> bool:
+        """Transposes of the last two axes that feed a MatMul become its trans flags (fold.rs:129-178)."""
+        r = _ffi.ir_lib().ox_module_fold_transposes(self.handle)
+        if r < 0:
+            raise RuntimeError("fold_transposes failed")
+        return r > 0
+
     @property
     def num_nodes(self) -> int:
         return _ffi.ir_lib().ox_module_num_nodes(self.handle)

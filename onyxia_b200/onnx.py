@@ -348,6 +348,12 @@ class _Lower:
                 raise OnnxError(f"no lowering rule for operator '{node.op}'" + (f" (domain {node.domain})" if node.domain else ""))
             rule(node)
         self.b.set_loc(None)
+        self._finish_outputs()
+        m = self.b.finish()
+        m.fold_transposes()  # MatMul(h, Transpose(W)) of tied-embedding exports (fold.rs:129-178)
+        return m
+
+    def _finish_outputs(self):
         for name in self.outputs:
             if name not in self.vals:
                 raise OnnxError(f"graph output '{name}' is not produced")
@@ -355,7 +361,6 @@ class _Lower:
             if v.vid is None:
                 raise OnnxError(f"graph output '{name}' is a compile-time shape value")
             self.b.output(name, v.vid)
-        return self.b.finish()
 
     def op_Identity(self, n):
         self.set(n, 0, self.val(n.inputs[0]))
@@ -429,6 +434,89 @@ class _Lower:
             specs.append((ax, lo, hi, 1))
             shape[ax] = hi - lo
         self.set(n, 0, _Val(self.b.slice(x.vid, specs), x.dtype, shape))
+
+    def op_Transpose(self, n):
+        x = self.val(n.inputs[0])
+        perm = [int(p) for p in n.attrs.get("perm", list(range(len(x.shape)))[::-1])]
+        self.set(n, 0, _Val(self.b.transpose(x.vid, perm), x.dtype, [x.shape[p] for p in perm]))
+
+    def op_MatMul(self, n):
+        # rank-1 operands are promoted in lowering, not in the primitive (rules.rs:171-213)
+        a, b = self.val(n.inputs[0]), self.val(n.inputs[1])
+        av, ash, bv, bsh = a.vid, list(a.shape), b.vid, list(b.shape)
+        if len(ash) == 1:
+            ash = [DimExpr.of(1)] + ash
+            av = self.b.reshape(av, ash)
+        if len(bsh) == 1:
+            bsh = bsh + [DimExpr.of(1)]
+            bv = self.b.reshape(bv, bsh)
+        out = self.b.matmul(av, bv)
+        shape = self._broadcast(ash[:-2], bsh[:-2]) + [ash[-2], bsh[-1]]
+        if len(a.shape) == 1:
+            shape = shape[:-2] + shape[-1:]
+        if len(b.shape) == 1:
+            shape = shape[:-1]
+        if len(a.shape) == 1 or len(b.shape) == 1:
+            out = self.b.reshape(out, shape)
+        self.set(n, 0, _Val(out, a.dtype, shape))
+
+    def op_Reshape(self, n):
+        x = self.val(n.inputs[0])
+        tgt = self.val(n.inputs[1])
+        if tgt.content is not None:
+            dims = list(tgt.content)
+        else:
+            arr = self.const_array(n.inputs[1])
+            if arr is None:
+                raise OnnxError(f"Reshape '{n.name}': the target shape must be a constant or shape arithmetic")
+            dims = [int(v) for v in np.asarray(arr).reshape(-1)]
+        out, unknown = [], -1
+        for i, d in enumerate(dims):
+            if isinstance(d, DimExpr):
+                out.append(d)
+            elif d == 0 and not int(n.attrs.get("allowzero", 0)):
+                out.append(x.shape[i])  # 0 copies the input's dimension
+            elif d == -1:
+                unknown = i
+                out.append(None)
+            else:
+                out.append(DimExpr.of(d))
+        if unknown >= 0:  # the one free dimension: only when every other extent is a constant
+            known = [d.as_const() for j, d in enumerate(out) if j != unknown]
+            total = [d.as_const() for d in x.shape]
+            if None in known or None in total:
+                raise OnnxError(f"Reshape '{n.name}': -1 beside symbolic dimensions is not lowered here")
+            rest = int(np.prod(known)) if known else 1
+            out[unknown] = DimExpr.of(int(np.prod(total)) // max(rest, 1))
+        self.set(n, 0, _Val(self.b.reshape(x.vid, out), x.dtype, out))
+
+    def op_Unsqueeze(self, n):
+        x = self.val(n.inputs[0])
+        axes = self.int_list(n, 1, "axes")
+        rank = len(x.shape) + len(axes)
+        axes = sorted(a + rank if a < 0 else a for a in axes)
+        if x.content is not None:  # shape arithmetic: a scalar becomes a one-element vector
+            self.set(n, 0, _Val(None, x.dtype, [DimExpr.of(len(x.content))], content=list(x.content)))
+            return
+        shape, it = [], iter(x.shape)
+        for i in range(rank):
+            shape.append(DimExpr.of(1) if i in axes else next(it))
+        self.set(n, 0, _Val(self.b.reshape(x.vid, shape), x.dtype, shape))
+
+    def op_Concat(self, n):
+        vals = [self.val(i) for i in n.inputs]
+        axis = int(n.attrs.get("axis", 0))
+        if all(v.content is not None or v.const is not None for v in vals) and any(v.content is not None for v in vals):
+            content = []
+            for v in vals:  # shape arithmetic: pieces of a target shape
+                content += list(v.content) if v.content is not None else [int(c) for c in np.asarray(v.const).reshape(-1)]
+            self.set(n, 0, _Val(None, ir.I64, [DimExpr.of(len(content))], content=content))
+            return
+        axis = axis + len(vals[0].shape) if axis < 0 else axis
+        shape = list(vals[0].shape)
+        for v in vals[1:]:
+            shape[axis] = shape[axis] + v.shape[axis]
+        self.set(n, 0, _Val(self.b.concat([v.vid for v in vals], axis), vals[0].dtype, shape))
 
     def op_SimplifiedLayerNormalization(self, n):
         x, w = self.val(n.inputs[0]), self.val(n.inputs[1])

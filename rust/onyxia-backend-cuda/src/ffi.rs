@@ -151,6 +151,7 @@ unsafe extern "C" {
     pub fn ox_module_add_output(m: *mut ox_module, name: *const c_char, value: i32) -> i32;
     pub fn ox_module_add_constraint(m: *mut ox_module, left: *const ox_dimexpr, right: *const ox_dimexpr, context: *const c_char) -> i32;
     pub fn ox_module_set_loc(m: *mut ox_module, node_name: *const c_char, op_type: *const c_char);
+    pub fn ox_module_fold_transposes(m: *mut ox_module) -> i32;
     pub fn ox_module_validate(m: *const ox_module) -> i32;
 
     pub fn ox_backend_create(devices: *const i32, n_devices: i32, out: *mut *mut ox_backend) -> i32;

@@ -205,3 +205,68 @@ def test_decoder_from_an_onnx_file_on_the_device(tmp_path):
 
     for a, b in zip(loop(onnx.load_onnx(str(path))), loop(models.build_decoder(cfg, seed=1))):
         assert np.array_equal(a, b)
+
+
+def test_transpose_of_a_matmul_operand_is_folded_into_the_flag():
+    """MatMul(h, Transpose(W)) of a tied-embedding lm_head: the Transpose disappears (fold.rs:129-178), the value stays."""
+    rng = np.random.default_rng(0)
+    wt = rng.standard_normal((7, 5)).astype(np.float32)   # [vocab, hidden]
+    w = onnx.OnnxWriter()
+    w.input("h", ir.F32, ["batch", "seq", 5])
+    w.initializer("embed", wt)
+    w.node("Transpose", ["embed"], ["embed_t"], perm=[1, 0])
+    w.node("MatMul", ["h", "embed_t"], ["logits"])
+    w.output("logits", ir.F32, ["batch", "seq", 7])
+    module = onnx.load_onnx_bytes(w.tobytes())
+    assert module.node_ops() == ["matmul"]
+    h = rng.standard_normal((2, 3, 5)).astype(np.float32)
+    got = _run(module, {"h": HostTensor.from_numpy(h)})["logits"].numpy()
+    assert np.abs(got - h @ wt.T).max() < 1e-5
+
+
+def test_transpose_of_batch_axes_is_not_folded():
+    b = ir.GraphBuilder()
+    x = b.input("x", ir.F32, [2, 3, 4])
+    y = b.input("y", ir.F32, [4, 3, 2])
+    b.output("o", b.matmul(x, b.transpose(y, [2, 0, 1])))   # not a swap of the last two axes
+    m = b.finish()
+    assert m.fold_transposes() is False and m.node_ops() == ["transpose", "matmul"]
+    # both operands, flags toggle
+    b = ir.GraphBuilder()
+    x = b.input("x", ir.F32, [4, 3])
+    y = b.input("y", ir.F32, [5, 4])
+    b.output("o", b.matmul(b.transpose(x, [1, 0]), b.transpose(y, [1, 0])))
+    m = b.finish()
+    assert m.fold_transposes() is True and m.node_ops() == ["matmul"]
+    rng = np.random.default_rng(1)
+    xv, yv = rng.standard_normal((4, 3)).astype(np.float32), rng.standard_normal((5, 4)).astype(np.float32)
+    got = _run(m, {"x": HostTensor.from_numpy(xv), "y": HostTensor.from_numpy(yv)})["o"].numpy()
+    assert np.abs(got - xv.T @ yv.T).max() < 1e-5
+
+
+def test_reshape_with_shape_arithmetic_and_rank_one_matmul():
+    # Reshape whose target is Concat(Shape(x)[0:1], [-1 → constant]) style arithmetic, and a vector · matrix product
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["n", 6])
+    w.initializer("idx0", np.array(0, np.int64))
+    w.initializer("axes0", np.array([0], np.int64))
+    w.initializer("tail", np.array([2, 3], np.int64))
+    w.node("Shape", ["x"], ["xs"])
+    w.node("Gather", ["xs", "idx0"], ["n_scalar"], axis=0)
+    w.node("Unsqueeze", ["n_scalar", "axes0"], ["n_vec"])
+    w.node("Concat", ["n_vec", "tail"], ["target"], axis=0)
+    w.node("Reshape", ["x", "target"], ["y"])
+    w.output("y", ir.F32, ["n", 2, 3])
+    module = onnx.load_onnx_bytes(w.tobytes())
+    assert module.node_ops() == ["reshape"]
+    xv = np.arange(24, dtype=np.float32).reshape(4, 6)
+    assert np.array_equal(_run(module, {"x": HostTensor.from_numpy(xv)})["y"].numpy(), xv.reshape(4, 2, 3))
+
+    w = onnx.OnnxWriter()
+    w.input("v", ir.F32, [3])
+    w.initializer("m", np.arange(12, dtype=np.float32).reshape(3, 4))
+    w.node("MatMul", ["v", "m"], ["o"])
+    w.output("o", ir.F32, [4])
+    vv = np.array([1, 2, 3], np.float32)
+    got = _run(onnx.load_onnx_bytes(w.tobytes()), {"v": HostTensor.from_numpy(vv)})["o"].numpy()
+    assert got.shape == (4,) and np.array_equal(got, vv @ np.arange(12, dtype=np.float32).reshape(3, 4))
