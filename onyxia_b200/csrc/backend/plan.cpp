@@ -95,6 +95,11 @@ bool same_bindings(const Bindings& a, const Bindings& b) {
     return true;
 }
 
+inline bool moves_elements(PrimKind k) {
+    return k == PrimKind::Transpose || k == PrimKind::Broadcast || k == PrimKind::Concat || k == PrimKind::Slice ||
+           k == PrimKind::Gather || k == PrimKind::Scatter;
+}
+
 }  // namespace
 
 // Which symbols can change a node's launch records: those in the types of its
@@ -268,6 +273,27 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
                 double eps = node.composite.attrs.float_or("epsilon", 1e-5);
                 TRef sum = plan.trefs[a.outputs[0]];
                 oxk::emit_rmsnorm(em, plan.trefs[a.inputs[0]], ins[1], outs[0], eps, &plan.trefs[a.inputs[1]], &sum);
+            } else if (node.is_prim && moves_elements(node.prim.kind) && !outs.empty() && dtype_is_packed((DType)outs[0].dtype)) {
+                // Packed nibbles have no address of their own: the interpreter moves them through its integer domain
+                // (crates/onyxia-ir/src/interp.rs:579-748, types.rs:7-11). Here: widen every packed operand to bytes,
+                // move the bytes, pack the result. Bit-exact; two extra launches per operand.
+                const DType byte_dt = (DType)outs[0].dtype == DType::U4 ? DType::U8 : DType::I8;
+                auto bytes_like = [&](const TRef& t) {
+                    TRef b;
+                    b.dtype = (int)byte_dt;
+                    b.shape = t.shape;
+                    b.buf = em.scratch((size_t)std::max<int64_t>(t.numel(), 1));
+                    return b;
+                };
+                std::vector<TRef> wide = ins;
+                for (size_t i = 0; i < ins.size(); i++)
+                    if (dtype_is_packed((DType)ins[i].dtype)) {
+                        wide[i] = bytes_like(ins[i]);
+                        if (ins[i].numel()) oxk::emit_cast(em, ins[i], wide[i]);
+                    }
+                TRef moved = bytes_like(outs[0]);
+                lower_prim(em, node, bindings, wide, {moved});
+                if (outs[0].numel()) oxk::emit_cast(em, moved, outs[0]);
             } else if (node.is_prim) {
                 lower_prim(em, node, bindings, ins, outs);
             } else {

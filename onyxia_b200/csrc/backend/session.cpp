@@ -180,17 +180,8 @@ void Session::analyse() {
             info_[i].label = n.composite.name;
         }
         if (n.loc_name) info_[i].label = *n.loc_name;
-        // movement primitives cannot interpret packed nibbles
         if (n.is_prim) {
             PrimKind k = n.prim.kind;
-            bool moves = k == PrimKind::Transpose || k == PrimKind::Broadcast || k == PrimKind::Concat || k == PrimKind::Slice ||
-                         k == PrimKind::Gather || k == PrimKind::Scatter || k == PrimKind::Select;
-            if (moves && !n.inputs.empty()) {
-                DType dt = m.values[n.inputs[k == PrimKind::Select ? 1 : 0]].ty.dtype;
-                if (dtype_is_packed(dt))
-                    fail(ErrKind::Unsupported, std::string(n.prim.name()) + " on packed dtype " + dtype_name(dt) +
-                                                   ": cast or dequantize first");
-            }
             if (k == PrimKind::DimValues && n.prim.shape.size() > 32) fail(ErrKind::Unsupported, "dim_values with more than 32 expressions");
         }
         for (auto v : n.outputs)

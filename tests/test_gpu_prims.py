@@ -378,3 +378,30 @@ def test_pool_reuses_buffers_across_runs():
     sess.wait_idle()
     fresh, reuses = sess.pool_stats()
     assert reuses >= 3, (fresh, reuses)
+
+
+# ── movement primitives on packed nibbles ────────────────────────────────
+@pytest.mark.parametrize("qdt", [ir.U4, ir.I4])
+def test_movement_primitives_move_packed_nibbles_bit_exact(qdt):
+    """The interpreter moves U4 / I4 elements through its integer domain (interp.rs:579-748, types.rs:7-11); the device
+    widens to bytes, moves, packs again. Odd element counts exercise the half-filled last byte."""
+    def q(shape):
+        return HostTensor.packed_u4(RNG.integers(0, 16, int(np.prod(shape))), list(shape), qdt)
+
+    m, feed = single_prim_module(ir.P_TRANSPOSE, [q((3, 5, 7))], axes=[2, 0, 1])
+    differential(m, feed)
+    m, feed = single_prim_module(ir.P_SLICE, [q((6, 9))], specs=[(0, 1, 6, 2), (1, 8, 1, -3)])
+    differential(m, feed)
+    m, feed = single_prim_module(ir.P_CONCAT, [q((2, 3)), q((5, 3)), q((1, 3))], axis=0)
+    differential(m, feed)
+    m, feed = single_prim_module(ir.P_BROADCAST, [q((1, 5))], shape=[3, 5])
+    differential(m, feed)
+    idx = ht(np.array([[2, 0], [-1, 3]], i64))
+    m, feed = single_prim_module(ir.P_GATHER, [q((4, 5)), idx], axis=0)
+    differential(m, feed)
+    upd_idx = ht(np.array([[1], [3], [1]], i64))
+    m, feed = single_prim_module(ir.P_SCATTER, [q((4, 5)), upd_idx, q((3, 5))])
+    differential(m, feed)
+    # Select is not among them: type inference rejects packed operands there (infer.rs:447-461)
+    with pytest.raises(OnyxiaError, match="packed dtype"):
+        single_prim_module(ir.P_SELECT, [ht(np.ones((3, 5), np.bool_)), q((3, 5)), q((3, 5))])
