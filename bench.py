@@ -343,7 +343,8 @@ def run_c5(args, rank, local_rank, world, group=None):
                    "layers_run": cfg.layers, "layers_full": full_layers, "vocab_run": cfg.vocab, "tp_split": list(stats)},
         "ms_per_layer": per_layer_ms, "extrapolated_full_depth_tok_s": B / (per_layer_ms * full_layers / 1e3),
         "layer_roofline_frac": (layer_bytes + kv_bytes) / world / (peak * 1e9) / (per_layer_ms / 1e3),
-        "clocks": clocks, "gpu_launches": sess.launch_count(), "peak_gbs": peak, "peak_source": peak_kind}
+        "clocks": clocks, "gpu_launches": sess.launch_count(), "peak_gbs": peak, "peak_source": peak_kind,
+        "allreduce": None if world == 1 else ("own kernel over peer memory (CUDA IPC, peer loads)" if backend.peer_allreduce() else "ncclAllReduce")}
     del sess, kv
     return result
 
@@ -665,7 +666,7 @@ def main():
             c5_tp = run_c5(tp_args, rank, local_rank, world, gloo)
             c5_tp["tp_vs_single_max_abs"] = tp_agreement(rank, local_rank, world, gloo)
             c5_tp["note"] = ("8 of the 62 layers at full width and a 32k vocabulary; strong scaling: the same 64 sequences on "
-                             "every rank count; one ncclAllReduce after the attention block and one after the FFN block")
+                             "every rank count; one all-reduce after the attention block and one after the FFN block")
         except Exception as e:  # never lose the headline measurement to the side measurement
             c5_tp = {"error": str(e)[:300]}
 

@@ -228,6 +228,10 @@ void ox_backend_free(ox_backend*);
  * runtime shuts down was seen to block). */
 ox_status ox_tp_unique_id(const char* nccl_library_path, uint8_t out[128]);
 ox_status ox_backend_join_tp(ox_backend*, int32_t rank, int32_t world, const uint8_t id[128], const char* nccl_library_path);
+/* 1 when the joined group reduces f16 messages of up to 1 MiB with the library's own kernel over peer memory
+ * (regions exchanged with CUDA IPC at join time, ordinary peer loads, bounded waits), 0 when every all-reduce
+ * goes to ncclAllReduce (no group, more than 8 ranks, the mapping failed, or ONYXIA_DISABLE_PEER_ALLREDUCE=1). */
+int32_t ox_backend_peer_allreduce(const ox_backend*);
 /* ≙ Backend::supports (backend.rs:28-31): 1 if a fused kernel is registered under this name. */
 int32_t ox_backend_supports(const ox_backend*, const char* composite_name);
 /* ≙ Backend::prepare (backend.rs:33-34). Consumes `module` (also on failure). */

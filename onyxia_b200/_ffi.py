@@ -134,6 +134,7 @@ SIGNATURES = {
     "ox_llm_step_sampled": (C.c_int32, [_P, C.POINTER(C.c_int64), C.c_int32, C.c_float, C.c_int64, C.c_float, C.c_float,
                                         C.POINTER(C.c_int64)]),
     "ox_tp_unique_id": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint8)]),
+    "ox_backend_peer_allreduce": (C.c_int32, [_P]),
     "ox_backend_join_tp": (C.c_int32, [_P, C.c_int32, C.c_int32, C.POINTER(C.c_uint8), C.c_char_p]),
 }
 

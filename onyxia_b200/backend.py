@@ -217,6 +217,10 @@ class CudaBackend:
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         check(self._lib.ox_backend_join_tp(self._h, rank, world, buf, nccl_path.encode() if nccl_path else None))
 
+    def peer_allreduce(self) -> bool:
+        """True when the joined group's f16 all-reduces run as the library's own kernel over peer memory."""
+        return bool(self._lib.ox_backend_peer_allreduce(self._h))
+
     def join_tp_torch(self, group=None) -> tuple:
         """Join the group formed by a torch.distributed process group (used only to pass the id around)."""
         import torch.distributed as dist

@@ -58,6 +58,11 @@ ox_status ox_backend_join_tp(ox_backend* b, int32_t rank, int32_t world, const u
     OX_CATCH
 }
 
+int32_t ox_backend_peer_allreduce(const ox_backend* b) {
+    const oxrt::Communicator* c = b->b->communicator();
+    return c && c->peer_path_ready() ? 1 : 0;
+}
+
 void ox_backend_free(ox_backend* b) { delete b; }
 
 int32_t ox_backend_supports(const ox_backend* b, const char* name) { return b->b->supports(name) ? 1 : 0; }

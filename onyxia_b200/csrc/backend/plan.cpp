@@ -716,7 +716,7 @@ void Session::launch_rec(const oxk::LaunchRec& r, void* param_bytes, bool allow_
         std::memcpy(&c, param_bytes, sizeof(c));
         Communicator* comm = backend_.communicator();
         if (!comm) fail(ErrKind::Runtime, "all-reduce without a tensor-parallel group");
-        comm->allreduce_sum(c.send, c.recv, (size_t)c.count, (DType)c.dtype, stream_);
+        comm->allreduce_sum(c.send, c.recv, (size_t)c.count, (DType)c.dtype, stream_, d_err_, r.node);
         return;
     }
     cudaLaunchConfig_t cfg{};

@@ -149,12 +149,26 @@ public:
     Communicator& operator=(const Communicator&) = delete;
     int rank() const { return rank_; }
     int world() const { return world_; }
-    // Enqueues the sum over all ranks on `stream` (capturable into a CUDA graph).
-    void allreduce_sum(const void* send, void* recv, size_t count, DType dtype, cudaStream_t stream);
+    // Enqueues the sum over all ranks on `stream` (capturable into a CUDA graph). f16 messages that fit a
+    // staging slot run as one kernel over peer memory (each rank copies its addend into a buffer its peers
+    // have mapped, raises a flag in their memory, waits — bounded — for theirs, and adds all addends in rank
+    // order in f32); everything else goes to ncclAllReduce. `err_word` / `node` tell the kernel where to
+    // report a wait that ran out.
+    void allreduce_sum(const void* send, void* recv, size_t count, DType dtype, cudaStream_t stream, void* err_word = nullptr,
+                       int node = -1);
+    bool peer_path_ready() const { return peer_ok_; }
+    const std::string& peer_path_note() const { return peer_note_; }
+    static constexpr int kMaxPeers = 8;
 
 private:
+    void setup_peer_path(int device);
     void* comm_ = nullptr;
     int rank_, world_;
+    // peer path: one region per rank (flags, counters, staging slots), mapped into every other rank
+    bool peer_ok_ = false;
+    std::string peer_note_;
+    char* region_ = nullptr;
+    char* peer_region_[kMaxPeers] = {};
 };
 // The id rank 0 creates and hands to every rank of a new group (by whatever channel the host has).
 void tp_unique_id(const char* nccl_path, uint8_t out[128]);

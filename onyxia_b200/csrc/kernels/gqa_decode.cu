@@ -368,6 +368,11 @@ template <int DT, int DPL, int GT> __global__ void __launch_bounds__(kThreads, 1
 // copied one row per bulk copy into rows padded by 16 bytes, so that the 8×8
 // matrix loads touch every bank once.
 constexpr int kRowPad = 8;  // f16 elements
+// Keys per staged block and blocks in flight. A block is consumed between two CTA barriers and the score
+// pass gives a warp 16 keys: with 32-key blocks two of the eight warps worked and a 1 024-key range paid 64
+// barrier pairs; 64-key blocks halve both (batched decode at a 2 048-token context: the kernel is the layer).
+constexpr int kKeyBlockH = 64;
+constexpr int kRingH = 4;
 
 __device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -389,7 +394,7 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], unsigned a0, unsigned a1,
 template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_decode_h(const GqaDecP p) {
     constexpr int DT = DT_F16;
     constexpr int D = 32 * DPL, RS = D + kRowPad;      // row stride in elements
-    constexpr int kBlockBytes = kKeyBlock * RS * 2;
+    constexpr int kBlockBytes = kKeyBlockH * RS * 2;
     constexpr int NW = kThreads / 32;
     cg::cluster_group cluster = cg::this_cluster();
     const int CX = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
@@ -398,8 +403,8 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
     const int kpad = (p.chunk_max + 15) & ~15;  // keys per CTA rounded up to whole MMA tiles
 
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* ring = smem;                                             // kRing blocks of kKeyBlock padded rows
-    __half* q_h = reinterpret_cast<__half*>(ring + kRing * kBlockBytes);    // [8][RS] rotated q, zero rows beyond the group
+    unsigned char* ring = smem;                                             // kRingH blocks of kKeyBlockH padded rows
+    __half* q_h = reinterpret_cast<__half*>(ring + kRingH * kBlockBytes);    // [8][RS] rotated q, zero rows beyond the group
     float* sc = reinterpret_cast<float*>(q_h + 8 * RS);                     // [GT][kpad] scores → exponentials
     __half* p_h = reinterpret_cast<__half*>(sc + GT * kpad);                // [8][kpad + 8] probabilities (A operand of P·V)
     float* part = reinterpret_cast<float*>(p_h + 8 * (kpad + 8));           // [GT][D] this CTA's partial output (read by the cluster)
@@ -439,23 +444,23 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             if (tid == 0) report(p.err, ERR_SLICE_OOB, p.node, my_n, p.chunk_max);
             my_n = p.chunk_max;
         }
-        n_blocks = (my_n + kKeyBlock - 1) / kKeyBlock;
+        n_blocks = (my_n + kKeyBlockH - 1) / kKeyBlockH;
         owns_new = qpos <= T - 1 && n > 0 && (int)((hi - lo) / chunk) == rank;
     };
     set_range(T - 1 > 0 ? T - 1 : 0);
 
-    // Block i of 2·n_blocks (K blocks, then V blocks) → ring slot i % kRing, as 16-byte asynchronous
+    // Block i of 2·n_blocks (K blocks, then V blocks) → ring slot i % kRingH, as 16-byte asynchronous
     // copies into padded rows; every thread commits one group per block (empty beyond the last block).
     // The newest key's row is not fetched: its owner writes it into the slot directly.
     auto fetch = [&](int i) {
         if (i < 2 * n_blocks) {
             const bool is_v = i >= n_blocks;
             const int blk = is_v ? i - n_blocks : i;
-            int rows = my_n - blk * kKeyBlock;
-            rows = rows > kKeyBlock ? kKeyBlock : rows;
-            const __half* src = (is_v ? cv : ck) + (my_lo + (long long)blk * kKeyBlock) * D;
-            const unsigned dst = sm_addr(ring + (i % kRing) * kBlockBytes);
-            const long long skip = owns_new ? qpos - (my_lo + (long long)blk * kKeyBlock) : -1;
+            int rows = my_n - blk * kKeyBlockH;
+            rows = rows > kKeyBlockH ? kKeyBlockH : rows;
+            const __half* src = (is_v ? cv : ck) + (my_lo + (long long)blk * kKeyBlockH) * D;
+            const unsigned dst = sm_addr(ring + (i % kRingH) * kBlockBytes);
+            const long long skip = owns_new ? qpos - (my_lo + (long long)blk * kKeyBlockH) : -1;
             for (int c = tid; c < rows * (D / 8); c += kThreads) {
                 const int r = c / (D / 8), col = c % (D / 8);
                 if (r == skip) continue;
@@ -465,7 +470,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    for (int i = 0; i < kRing; i++) fetch(i);
+    for (int i = 0; i < kRingH; i++) fetch(i);
     ox_trace(p.err, 13);
     pdl_wait();
     ox_trace(p.err, 12);
@@ -475,7 +480,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
             set_range(q);
-            for (int i = 0; i < kRing; i++) fetch(i);
+            for (int i = 0; i < kRingH; i++) fetch(i);
         }
     }
     long long rope_row = qpos;
@@ -547,16 +552,16 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         qb[j][1] = *reinterpret_cast<const unsigned*>(q_h + g * RS + 16 * j + 2 * t + 8);
     }
     for (int blk = 0; blk < n_blocks; blk++) {
-        const int slot = blk % kRing;
-        asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");  // this thread's copies of the oldest block landed
+        const int slot = blk % kRingH;
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRingH - 1) : "memory");  // this thread's copies of the oldest block landed
         __half* rows = reinterpret_cast<__half*>(ring + slot * kBlockBytes);
-        const int first = blk * kKeyBlock;  // index within this CTA's keys
+        const int first = blk * kKeyBlockH;  // index within this CTA's keys
         const long long first_pos = my_lo + first;
-        if (owns_new && qpos >= first_pos && qpos < first_pos + kKeyBlock && tid < D)
+        if (owns_new && qpos >= first_pos && qpos < first_pos + kKeyBlockH && tid < D)
             rows[(qpos - first_pos) * RS + tid] = __float2half_rn(new_k);
         __syncthreads();
         int here = my_n - first;
-        here = here > kKeyBlock ? kKeyBlock : here;
+        here = here > kKeyBlockH ? kKeyBlockH : here;
         for (int kt = warp; kt * 16 < here; kt += NW) {  // 16 keys per MMA tile
             float c[4] = {0.f, 0.f, 0.f, 0.f};
             const int m = lane >> 3, r = lane & 7;
@@ -575,7 +580,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             }
         }
         __syncthreads();  // the block is consumed: its slot takes the next one
-        fetch(blk + kRing);
+        fetch(blk + kRingH);
     }
 
     ox_trace(p.err, 15);
@@ -648,14 +653,14 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
 #pragma unroll
     for (int i = 0; i < (NT > 0 ? NT : 1); i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     for (int blk = 0; blk < n_blocks; blk++) {
-        const int i = n_blocks + blk, slot = i % kRing;
-        asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
+        const int i = n_blocks + blk, slot = i % kRingH;
+        asm volatile("cp.async.wait_group %0;" ::"n"(kRingH - 1) : "memory");
         __half* rows = reinterpret_cast<__half*>(ring + slot * kBlockBytes);
-        const int first = blk * kKeyBlock;
+        const int first = blk * kKeyBlockH;
         const long long first_pos = my_lo + first;
         int here = my_n - first;
-        here = here > kKeyBlock ? kKeyBlock : here;
-        if (owns_new && qpos >= first_pos && qpos < first_pos + kKeyBlock && tid < D)
+        here = here > kKeyBlockH ? kKeyBlockH : here;
+        if (owns_new && qpos >= first_pos && qpos < first_pos + kKeyBlockH && tid < D)
             rows[(qpos - first_pos) * RS + tid] = __float2half_rn(new_v);
         // rows beyond the last key of a partly filled tile hold stale bytes: clear them (their p is 0, but 0·NaN is NaN)
         for (int z = here * D + tid; z < ((here + 15) & ~15) * D; z += kThreads) rows[(z / D) * RS + z % D] = __float2half(0.f);
@@ -677,7 +682,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             }
         }
         __syncthreads();
-        fetch(i + kRing);
+        fetch(i + kRingH);
     }
     ox_trace(p.err, 19);
     // c0: (head g, dim n0 + 2t)  c1: (head g, dim n0 + 2t + 1); rows 8-15 of the tile are padding.
@@ -705,7 +710,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
 template <int DPL, int GT> size_t decode_h_smem(int chunk_max) {
     constexpr int D = 32 * DPL, RS = D + kRowPad;
     const int kpad = (chunk_max + 15) & ~15;
-    return (size_t)kRing * kKeyBlock * RS * 2 + (size_t)8 * RS * 2 + (size_t)GT * kpad * 4 + (size_t)8 * (kpad + 8) * 2 +
+    return (size_t)kRingH * kKeyBlockH * RS * 2 + (size_t)8 * RS * 2 + (size_t)GT * kpad * 4 + (size_t)8 * (kpad + 8) * 2 +
            (size_t)GT * D * 4 + (size_t)GT * (kThreads / 32) * 8 + (size_t)8 * GT * 4 + (size_t)8 * GT * 8 +
            (size_t)8 * GT * D * 4 + 128;
 }

@@ -158,6 +158,7 @@ unsafe extern "C" {
     pub fn ox_backend_create_ex(devices: *const i32, n_devices: i32, options: *const ox_backend_options, out: *mut *mut ox_backend) -> i32;
     pub fn ox_backend_free(b: *mut ox_backend);
     pub fn ox_tp_unique_id(nccl_library_path: *const c_char, out: *mut u8) -> i32;
+    pub fn ox_backend_peer_allreduce(b: *const ox_backend) -> i32;
     pub fn ox_backend_join_tp(b: *mut ox_backend, rank: i32, world: i32, id: *const u8, nccl_library_path: *const c_char) -> i32;
     pub fn ox_backend_supports(b: *const ox_backend, composite_name: *const c_char) -> i32;
     pub fn ox_backend_prepare(b: *mut ox_backend, module: *mut ox_module, out: *mut *mut ox_session) -> i32;

@@ -28,7 +28,27 @@ def main():
 
     backend = be.CudaBackend((local,))
     backend.join_tp_torch()
-    print(f"rank {rank}: joined the tensor-parallel group", flush=True)
+    print(f"rank {rank}: joined the tensor-parallel group, peer all-reduce {'on' if backend.peer_allreduce() else 'off'}", flush=True)
+    if os.environ.get("ONYXIA_DISABLE_PEER_ALLREDUCE", "0") in ("", "0"):
+        assert backend.peer_allreduce(), "the peer-memory all-reduce did not come up (CUDA IPC between the ranks' GPUs)"
+    # the all-reduce by itself on integer-valued data (sums are exact in f16): messages that take the peer-memory
+    # kernel (16 B … 1 MB), one beyond its staging slot (NCCL), repeated so that the staging slots rotate and a
+    # CUDA graph replays the launch
+    from onyxia_b200.ir import HostTensor
+    for n_elem in (8, 1000 * 8, 64 * 5376, 524288 + 64):
+        b = ir.GraphBuilder()
+        x = b.input("x", ir.F16, [n_elem])
+        y = b.composite("onyxia.AllReduce", {}, [x], [(ir.F16, [n_elem])])[0]
+        b.output("y", b.add(y, y))  # a second launch, so that the plan is replayed as a graph
+        sess = backend.prepare(b.finish())
+        base = (np.arange(n_elem) % 7).astype(np.float16)
+        want = 2.0 * base * sum(r + 1 for r in range(world))
+        for it in range(9):
+            feed = {"x": sess.upload(HostTensor.from_numpy((base * (rank + 1) + it).astype(np.float16)))}
+            out = sess.download(dict(sess.run(feed))["y"]).numpy().astype(np.float32)
+            assert np.array_equal(out, want + 2.0 * it * world), (n_elem, it, np.abs(out - want - 2.0 * it * world).max())
+    print(f"rank {rank}: all-reduce sizes ok", flush=True)
+
     lm = llm.LlmSession(backend, module.tp_partition(world, rank), 256)
     got = [lm.prefill(prompt)]
     print(f"rank {rank}: prefill done", flush=True)
