@@ -24,7 +24,10 @@ namespace {
 
 using namespace tile;
 
-constexpr int kCW = 16;                    // consumer warps
+#ifndef OX_CW
+#define OX_CW 16
+#endif
+constexpr int kCW = OX_CW;                 // consumer warps
 constexpr int kCT = kCW * 32;              // consumer threads
 constexpr int kPT = kCT + 32;              // + the producer warp
 constexpr int kStTiles = 3;                // tile records per ring stage
@@ -308,11 +311,11 @@ __device__ __forceinline__ float geglu_lut(const GeluConsts& p, int form, float 
 // runs on all of them (more loads in flight while the tagged words are polled). Warps without rows skip the
 // row sums and the epilogue.
 #ifndef OX_PW
-#define OX_PW 16
+#define OX_PW OX_CW
 #endif
 constexpr int kPW = OX_PW;          // warps that run a prologue
 constexpr int kPTh = kPW * 32;
-constexpr int kEP = kMaxPrologueK / 2 / kPTh;  // f16 pairs per prologue thread (8)
+constexpr int kEP = (kMaxPrologueK / 2 + kPTh - 1) / kPTh;  // f16 pairs per prologue thread
 
 __device__ __forceinline__ void prologue_sync() { asm volatile("bar.sync 2, %0;" ::"n"(kPTh) : "memory"); }
 
