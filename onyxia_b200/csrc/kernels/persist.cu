@@ -42,7 +42,19 @@ constexpr long long kWaitP = 1000000000LL; // ≈ 0.5 s: how long any wait may l
 // data directly, while the traffic they save never was the bottleneck. Kept for experiments.
 constexpr bool kUseArrivalWords = false;
 constexpr unsigned kPollPauseNs = 40;      // pause between two reads of a word that has not arrived yet
+#ifndef OX_POLL_SPIN
+#define OX_POLL_SPIN 40
+#endif
+constexpr int kPollSpinCycles = OX_POLL_SPIN;  // > 0: pause by watching the clock for this many cycles instead of nanosleep
 constexpr int kRowPad = 8;                 // f16 elements of padding per staged K row (bank spread for ldmatrix)
+// Copies of every tagged vector that other CTAs wait for. All 148 CTAs poll the words of one small vector: with one
+// copy, a cache line is read by 148 × 16 threads in a loop and both their loads and the producer's store queue
+// in that line's L2 slice — a link of the chain took 2.5–5 µs in situ against ≈ 1 µs on an idle GPU.
+#ifndef OX_REPS
+#define OX_REPS 1
+#endif
+constexpr int kReps = OX_REPS;
+constexpr int kRepMaxEntries = 8192;       // longer vectors (an lm_head's) are not copied: nothing in the run waits for them
 
 enum : int {
     PF_SRC_TAGGED = 1,   // activations arrive as tagged pairs (else a plain f16 array)
@@ -73,6 +85,9 @@ struct PGemvDev {
     int k, k_tiles, row_tiles, sub, rot;  // sub: row tiles per unit (2: gate/up pairs)
     int src_nflag;
     float eps1, eps2;
+    // Tagged vectors exist in several copies (entries apart by the stride): CTA c reads copy c mod reps, so the
+    // CTAs that poll one cache line are 1 / reps of the grid.
+    int src_reps, src_rstride, out_reps, out_rstride;
 };
 
 struct PAttnDev {
@@ -94,7 +109,10 @@ struct PAttnDev {
     int H, KV, D, half, window, cache_rows, n_cap, cap;
     float scale;
     int next_attn;               // index of the next attention operation of the run, or −1
-    int src_nflag, pad;
+    int src_nflag;
+    int src_reps, src_rstride;   // copies of q / k / v (see PGemvDev)
+    int out_reps, out_rstride;   // copies of the tagged output
+    int pad;
 };
 
 struct POpDev {
@@ -165,7 +183,13 @@ __device__ __forceinline__ unsigned long long poll_finish(const Ctx& c, const un
     for (;;) {
         // Thousands of threads poll a handful of cache lines: without a pause between the reads the
         // producer's store queues behind them in the L2 slice and every link of the chain slows down.
-        __nanosleep(kPollPauseNs);
+        if (kPollSpinCycles > 0) {
+            const long long s0 = clock64();
+            while (clock64() - s0 < kPollSpinCycles) {
+            }
+        } else {
+            __nanosleep(kPollPauseNs);
+        }
         v = ld_tagged(src);
         if ((unsigned)(v >> 32) == c.epoch) return v;
         if (*c.dead) return v;
@@ -352,7 +376,7 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
     if (!(flags & (PF_W1 | PF_RES | PF_W2))) {
         for (int i = K + tid; i < kpad; i += kCT) acts[frag_index(i)] = __float2half(0.f);
         if (flags & PF_SRC_TAGGED) {
-            const unsigned long long* src = reinterpret_cast<const unsigned long long*>(g.src);
+            const unsigned long long* src = reinterpret_cast<const unsigned long long*>(g.src) + (size_t)((int)blockIdx.x % g.src_reps) * g.src_rstride;
             for (int base = 0; base < ne; base += 4 * kCT) {
                 unsigned long long v[4];
 #pragma unroll
@@ -383,6 +407,8 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
         const __half2 zero2 = __float2half2_rn(0.f);
         __half2 hw1[kEP], hw2[kEP], hres[kEP];
         unsigned long long v[kEP];
+        const unsigned long long* tsrc = reinterpret_cast<const unsigned long long*>(g.src) +
+                                         ((flags & PF_SRC_TAGGED) ? (size_t)((int)blockIdx.x % g.src_reps) * g.src_rstride : 0);
 #pragma unroll
         for (int e = 0; e < kEP; e++) {
             const int idx = tid + e * kPTh;
@@ -390,7 +416,7 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
             hw1[e] = (flags & PF_W1) ? reinterpret_cast<const __half2*>(g.w1)[ic] : zero2;
             hw2[e] = (flags & PF_W2) ? reinterpret_cast<const __half2*>(g.w2)[ic] : zero2;
             hres[e] = ((flags & PF_RES) && !(flags & PF_RES_SMEM)) ? reinterpret_cast<const __half2*>(g.res)[ic] : zero2;
-            if (flags & PF_SRC_TAGGED) v[e] = ld_tagged(reinterpret_cast<const unsigned long long*>(g.src) + ic);
+            if (flags & PF_SRC_TAGGED) v[e] = ld_tagged(tsrc + ic);
             else if (flags & PF_SRC_RESID) v[e] = 0;
             else v[e] = reinterpret_cast<const unsigned*>(g.src)[ic];
         }
@@ -404,7 +430,7 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
                 x[e][1] = in ? resid[2 * idx + 1] : 0.f;
             } else {
                 if ((flags & PF_SRC_TAGGED) && in)
-                    v[e] = poll_finish(c, reinterpret_cast<const unsigned long long*>(g.src) + idx, v[e], op.node);
+                    v[e] = poll_finish(c, tsrc + idx, v[e], op.node);
                 const float2 f = __half22float2(uh((unsigned)v[e]));
                 x[e][0] = in ? f.x : 0.f;
                 x[e][1] = in ? f.y : 0.f;
@@ -599,7 +625,10 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
                     if (rtg >= g.seg_rt0[2]) seg = 2;
                     const int rowg = (rtg - g.seg_rt0[seg]) * 16 + row;
                     if (rowg < g.seg_n[seg]) g.y[seg][rowg] = __float2half_rn(y);
-                    if (!(row & 1)) st_tagged(g.xout + ((rtg * 16 + row) >> 1), tag | pack_h2(y, yo));
+                    if (!(row & 1)) {
+                        const unsigned long long word = tag | pack_h2(y, yo);
+                        for (int r = 0; r < g.out_reps; r++) st_tagged(g.xout + (size_t)r * g.out_rstride + ((rtg * 16 + row) >> 1), word);
+                    }
                 }
             }
         }
@@ -620,7 +649,10 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
                 if (in) {
                     const int rowg = (((rt_first + rt0) >> 1) + pj) * 16 + row;
                     if (rowg < g.seg_n[0]) g.y[0][rowg] = __float2half_rn(h);
-                    if (!(row & 1)) st_tagged(g.xout + (rowg >> 1), tag | pack_h2(h, ho));
+                    if (!(row & 1)) {
+                        const unsigned long long word = tag | pack_h2(h, ho);
+                        for (int r = 0; r < g.out_reps; r++) st_tagged(g.xout + (size_t)r * g.out_rstride + (rowg >> 1), word);
+                    }
                 }
             }
         }
@@ -812,7 +844,7 @@ template <int D> __device__ void run_attn(const Ctx& c, const POpDev& op) {
                     dst[e] = ic;
                 }
                 if (op.flags & PF_Q_TAGGED) {
-                    src[e] = reinterpret_cast<const unsigned long long*>(b) + elem;
+                    src[e] = reinterpret_cast<const unsigned long long*>(b) + (size_t)((int)blockIdx.x % a.src_reps) * a.src_rstride + elem;
                     v[e] = ld_tagged(reinterpret_cast<const unsigned long long*>(src[e]));
                 } else {
                     src[e] = nullptr;
@@ -992,7 +1024,10 @@ template <int D> __device__ void run_attn(const Ctx& c, const POpDev& op) {
             if (head < G) {
                 const int idx = (h0 + head) * D + ge.dt * 8 + col;
                 a.out[idx] = __float2half_rn(v);
-                if (!(col & 1)) st_tagged(a.xout + (idx >> 1), tag | pack_h2(v, vo));
+                if (!(col & 1)) {
+                    const unsigned long long word = tag | pack_h2(v, vo);
+                    for (int r = 0; r < a.out_reps; r++) st_tagged(a.xout + (size_t)r * a.out_rstride + (idx >> 1), word);
+                }
             }
         }
     }
@@ -1139,6 +1174,13 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
         long long elems;
         size_t flag_entry;  // the producing operation's arrival words
         int nflag;          // how many CTAs produce it
+        int reps, rstride;  // copies of the vector and their distance in entries
+    };
+    // entries of one copy rounded to whole cache lines, so that two copies never share one
+    auto rep_layout = [&](size_t entries, int* reps, int* rstride) {
+        *reps = entries <= (size_t)kRepMaxEntries ? kReps : 1;
+        *rstride = (int)((entries + 15) / 16 * 16);
+        return (size_t)*reps * (size_t)*rstride;
     };
     std::map<uint32_t, Made> made;
     std::map<uint32_t, int> written;  // every slot some operation of the run stores to (plain)
@@ -1190,6 +1232,8 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
             } else if (it != made.end()) {
                 if (it->second.elems != o.k) return no("producer and consumer disagree on a vector's length");
                 d.flags |= PF_SRC_TAGGED;
+                g.src_reps = it->second.reps;
+                g.src_rstride = it->second.rstride;
                 ptr(&g.src, Buf{kSlotXbuf, (int64_t)(it->second.entry * 8)});
                 ptr(&g.src_flag, Buf{kSlotXbuf, (int64_t)(it->second.flag_entry * 8)});
                 g.src_nflag = it->second.nflag;
@@ -1231,7 +1275,8 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
             // results
             const size_t entry0 = xentries;
             const int out_tiles = o.geglu ? rt / 2 : rt;
-            xentries += (size_t)out_tiles * 8;
+            xentries += rep_layout((size_t)out_tiles * 8, &g.out_reps, &g.out_rstride);
+            if (g.src_reps < 1) g.src_reps = 1;
             ptr(&g.xout, Buf{kSlotXbuf, (int64_t)(entry0 * 8)});
             const size_t flag0 = xentries;
             xentries += (size_t)(G + 1) / 2;
@@ -1243,7 +1288,7 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
                 ptr(&g.y[s], has ? o.y[s] : null);
                 if (!has) continue;
                 if (o.y[s].off != 0) return no("result operand with an offset");
-                made[o.y[s].slot] = Made{entry0 + (size_t)(o.geglu ? 0 : g.seg_rt0[s]) * 8, o.seg_n[s], flag0, std::min(n_units, G)};
+                made[o.y[s].slot] = Made{entry0 + (size_t)(o.geglu ? 0 : g.seg_rt0[s]) * 8, o.seg_n[s], flag0, std::min(n_units, G), g.out_reps, g.out_rstride};
                 written[o.y[s].slot] = 1;
             }
             // spread the units over the CTAs: rotate the assignment to where the run has streamed least so far
@@ -1308,8 +1353,14 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
             for (int s = 0; s < 3; s++)
                 if (made.count(qkv[s].slot) && qkv[s].off == 0 && made[qkv[s].slot].elems == want[s]) tagged++;
             const void* fields[3] = {&a.q, &a.k, &a.v};
+            a.src_reps = 1;
             if (tagged == 3) {
                 d.flags |= PF_Q_TAGGED;
+                a.src_reps = made[qkv[0].slot].reps;
+                a.src_rstride = made[qkv[0].slot].rstride;
+                if (made[qkv[1].slot].reps != a.src_reps || made[qkv[2].slot].reps != a.src_reps || made[qkv[1].slot].rstride != a.src_rstride ||
+                    made[qkv[2].slot].rstride != a.src_rstride)
+                    return no("q, k and v copied differently");
                 for (int s = 0; s < 3; s++) ptr(fields[s], Buf{kSlotXbuf, (int64_t)(made[qkv[s].slot].entry * 8)});
                 // the three must come from one operation: its arrival words cover them all
                 if (made[qkv[1].slot].flag_entry != made[qkv[0].slot].flag_entry || made[qkv[2].slot].flag_entry != made[qkv[0].slot].flag_entry)
@@ -1332,7 +1383,7 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
             ptr(&a.out, o.out);
             ptr(&a.dyn_t, o.dyn_t);
             const size_t entry0 = xentries;
-            xentries += (size_t)(o.H * o.D / 2);
+            xentries += rep_layout((size_t)(o.H * o.D / 2), &a.out_reps, &a.out_rstride);
             ptr(&a.xout, Buf{kSlotXbuf, (int64_t)(entry0 * 8)});
             const int HP = (int)((o.H / o.KV + 1) / 2);
             ptr(&a.xsc, Buf{kSlotXbuf, (int64_t)(xentries * 8)});
@@ -1342,7 +1393,7 @@ bool build_persist_launch(const std::vector<const PersistOp*>& ops, Buf epoch, P
             xentries += (size_t)(G + 1) / 2 * 2;
             ptr(&a.xflag, Buf{kSlotXbuf, (int64_t)(flag0 * 8)});
             ptr(&a.xflag_sc, Buf{kSlotXbuf, (int64_t)((flag0 + (size_t)(G + 1) / 2) * 8)});
-            made[o.out.slot] = Made{entry0, o.H * o.D, flag0, (int)(o.KV * (o.D / 8))};
+            made[o.out.slot] = Made{entry0, o.H * o.D, flag0, (int)(o.KV * (o.D / 8)), a.out_reps, a.out_rstride};
             written[o.out.slot] = 1;
             written[o.cache_k.slot] = 1;
             written[o.cache_v.slot] = 1;
