@@ -613,6 +613,8 @@ def main():
         per_launch["persist_step"] = weight_bytes - lm_head_bytes + kv_now + layer_act_bytes
         if "nbits_stream" in by_kernel:
             per_launch["nbits_stream"] = lm_head_bytes + 2 * (cfg.hidden + cfg.vocab)
+        else:  # the lm_head is one of the launch's operations
+            per_launch["persist_step"] += lm_head_bytes + 2 * (cfg.hidden + cfg.vocab)
     elif "nbits_stream" in by_kernel:
         n_l = by_kernel["nbits_stream"][0] / prof_steps
         per_launch["nbits_stream"] = (weight_bytes + layer_act_bytes + 2 * (cfg.hidden + cfg.vocab)) / n_l

@@ -135,9 +135,24 @@ struct PersistP {
     POpDev ops[kMaxOps];
 };
 
+#ifndef OX_LD_MODE
+#define OX_LD_MODE 0
+#endif
 __device__ __forceinline__ unsigned long long ld_tagged(const unsigned long long* p) {
     unsigned long long v;
+#if OX_LD_MODE == 1
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+#elif OX_LD_MODE == 2
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+#elif OX_LD_MODE == 3
+    asm volatile("ld.global.cv.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+#elif OX_LD_MODE == 4
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+#elif OX_LD_MODE == 5
+    asm volatile("atom.relaxed.gpu.global.or.b64 %0, [%1], 0;" : "=l"(v) : "l"(p) : "memory");
+#else
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+#endif
     return v;
 }
 __device__ __forceinline__ void st_tagged(unsigned long long* p, unsigned long long v) {
@@ -438,11 +453,20 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
         }
         const double inv_k = 1.0 / (double)K;
         ptrace(c, 35);
+#ifdef OX_TRACE
+        if (c.lane == 0 && blockIdx.x == 60 && c.op_index >= 50 && c.op_index < 55) {  // when each warp of one CTA had its words
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(c.err) + 256)[1 + 8 * 990 + (c.op_index - 50) * 16 + c.warp] = now;
+        }
+#endif
         if (flags & PF_W1) {
             double ss = 0.0;
 #pragma unroll
             for (int e = 0; e < kEP; e++) ss += (double)r16(x[e][0] * x[e][0]) + (double)r16(x[e][1] * x[e][1]);
+            ptrace(c, 37);
             const double tot = prologue_sum(c, ss, red);
+            ptrace(c, 38);
             const float msq = r16d(tot * inv_k), denom = r16(msq + g.eps1), inv = r16d(rsqrt((double)denom));
 #pragma unroll
             for (int e = 0; e < kEP; e++) {
@@ -496,6 +520,14 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
     }
     consumer_sync();
     ptrace(c, 31);
+#ifdef OX_TRACE
+    unsigned t_acts = 0;
+    if (c.tid == 0 && c.op_index == 52) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        t_acts = (unsigned)now;
+    }
+#endif
     if (my_rts == 0) return;
 
     // ── tiles ──
@@ -665,6 +697,13 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
         st_flag(g.xflag + cp, c.epoch);
     }
     ptrace(c, 33);
+#ifdef OX_TRACE
+    if (c.tid == 0 && c.op_index == 52) {  // every producer of one operation: when it had its inputs, when it was done
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(c.err) + 256)[1 + 8 * 990 + 100 + blockIdx.x] = (now << 32) | t_acts;
+    }
+#endif
 }
 
 // ── attention operation ─────────────────────────────────────────────────
@@ -1094,6 +1133,15 @@ __global__ void __launch_bounds__(kPT, 1) persist_step(const __grid_constant__ P
             const int kt_n = g.k_tiles, spr = (kt_n + kStTiles - 1) / kStTiles;
             const int n_st = my_rts * spr;
             const unsigned char* base = g.tiles + ((size_t)rt_first * kt_n) * kTileB;
+            // The norm weights of the operation's prologue are read once per step: from HBM (≈ 2 µs) unless somebody
+            // asked for them first. The producer is a layer or so ahead of the consumers: its idle lanes pull them into L2.
+            if (lane >= kIssue) {
+                const int lines = (g.k * 2 + 127) >> 7;
+                for (int ln = lane - kIssue; ln < 2 * lines; ln += 32 - kIssue) {
+                    const __half* w = ln < lines ? g.w1 : g.w2;
+                    if (w) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(w) + (size_t)(ln < lines ? ln : ln - lines) * 128));
+                }
+            }
             for (int i0 = 0; i0 < n_st && ok; i0 += kIssue) {
                 const int idx = i0 + lane;
                 bool mine_ok = true;
