@@ -619,9 +619,9 @@ def main():
         n_l = by_kernel["nbits_stream"][0] / prof_steps
         per_launch["nbits_stream"] = (weight_bytes + layer_act_bytes + 2 * (cfg.hidden + cfg.vocab)) / n_l
     dom = max(per_launch, key=lambda k: by_kernel[k][1], default=None)
-    # DRAM traffic per launch: ncu captures of these kernels read 1.01× (streaming GEMV) and 1.01× (persistent
-    # step, a 4-layer model) their algorithmic bytes; the figure here is that ratio applied to this launch.
-    traffic_ratio = {"persist_step": 1.01, "nbits_stream": 1.01}
+    # DRAM traffic per launch: ncu captures of these kernels read 1.01× (streaming GEMV) and 1.02× (persistent
+    # step, a 4-layer model with its lm_head) their algorithmic bytes; the figure here is that ratio applied to this launch.
+    traffic_ratio = {"persist_step": 1.02, "nbits_stream": 1.01}
     roofline = {"bound": "hbm", "achieved": None, "peak": peak, "unit": "GB/s", "frac": None, "traffic": None,
                 "kernel": dom, "peak_source": peak_kind,
                 "traffic_source": "static: ratio of DRAM bytes to algorithmic bytes from the ncu capture summarised under profiles/"}
