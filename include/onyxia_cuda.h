@@ -342,6 +342,13 @@ int32_t ox_llm_logits_dtype(const ox_llm*); /* ox_dtype code of the logits `ox_l
 void ox_llm_reset(ox_llm*);
 ox_status ox_llm_step(ox_llm*, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
                       size_t* logits_written);
+/* `n_new` greedy tokens in one call: the first step runs `ids` (a prompt, or one token), every later step takes its
+ * input id from the previous step's argmax on the device. Every step still uploads its attention mask from host
+ * memory and sends its token id to (pinned) host memory, but the host does not wait in between: the steps are
+ * enqueued back to back and the call returns when `tokens_out[0 .. n_new)` is complete. It does not stop at an
+ * end-of-sequence id; the caller truncates. ≙ the decode loop of crates/onyxia-cli/src/bench.rs:152-174 without
+ * its per-token host round trip. */
+ox_status ox_llm_generate(ox_llm*, const int64_t* ids, int32_t n_ids, int32_t n_new, int64_t* tokens_out);
 /* The same step with the next token drawn on the device from the last position's logits by temperature /
  * top-k / top-p sampling (see ox_session_sample_last; crates/onyxia-cli/src/sampling.rs:36-65); `uniform` is
  * the caller's random number in [0, 1]. */

@@ -131,6 +131,7 @@ SIGNATURES = {
     "ox_llm_reset": (None, [_P]),
     "ox_llm_step": (C.c_int32, [_P, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int64), C.c_void_p, C.c_size_t,
                                 C.POINTER(C.c_size_t)]),
+    "ox_llm_generate": (C.c_int32, [_P, C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.POINTER(C.c_int64)]),
     "ox_llm_step_sampled": (C.c_int32, [_P, C.POINTER(C.c_int64), C.c_int32, C.c_float, C.c_int64, C.c_float, C.c_float,
                                         C.POINTER(C.c_int64)]),
     "ox_tp_unique_id": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint8)]),

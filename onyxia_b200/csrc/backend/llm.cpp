@@ -18,6 +18,11 @@ struct ox_llm {
     std::vector<oxrt::DTensor> cache;           // per input: the tensor to feed (KV inputs)
     int logits_out = -1;
     std::vector<int64_t> ones;
+    int64_t* pinned_tokens = nullptr;           // generate(): where the device drops the tokens
+    size_t pinned_cap = 0;
+    ~ox_llm() {
+        if (pinned_tokens) cudaFreeHost(pinned_tokens);
+    }
 };
 
 namespace {
@@ -81,7 +86,8 @@ struct SamplingArgs {
     int64_t top_k;
 };
 ox_status llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
-                   size_t* logits_written, const SamplingArgs* sampling);
+                   size_t* logits_written, const SamplingArgs* sampling, const oxrt::DTensor* ids_dev = nullptr,
+                   oxrt::DTensor* token_dev = nullptr);
 }  // namespace
 
 ox_status ox_llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
@@ -97,9 +103,41 @@ ox_status ox_llm_step_sampled(ox_llm* l, const int64_t* ids, int32_t n_ids, floa
     return llm_step(l, ids, n_ids, token_out, nullptr, 0, nullptr, &a);
 }
 
+// `n_new` greedy tokens in one call: the first step runs `ids` (a prompt, or one token), every later step takes
+// its input id from the previous step's argmax without leaving the device. Per step the host still uploads the
+// step's attention mask and the device still sends the step's token to (pinned) host memory, but nothing waits for
+// the host in between: the steps are enqueued back to back and the call returns when the last token has arrived.
+// Generation does not stop at an end-of-sequence id (the caller truncates).
+ox_status ox_llm_generate(ox_llm* l, const int64_t* ids, int32_t n_ids, int32_t n_new, int64_t* tokens_out) {
+    OX_TRY
+    if (n_new <= 0) return OX_OK;
+    if (l->past + n_ids + n_new - 1 > l->max_seq_len)
+        fail(ErrKind::Shape, "Sequence length " + std::to_string(l->past + n_ids + n_new - 1) + " would exceed max_seq_len " + std::to_string(l->max_seq_len));
+    if (l->pinned_cap < (size_t)n_new) {
+        if (l->pinned_tokens) cudaFreeHost(l->pinned_tokens);
+        l->pinned_tokens = nullptr;
+        l->pinned_cap = 0;
+        if (cudaMallocHost((void**)&l->pinned_tokens, sizeof(int64_t) * (size_t)n_new) != cudaSuccess) fail(ErrKind::Runtime, "cannot pin host memory for the tokens");
+        l->pinned_cap = (size_t)n_new;
+    }
+    oxrt::DTensor tok;
+    for (int32_t i = 0; i < n_new; i++) {
+        oxrt::DTensor next;
+        const ox_status st = i == 0 ? llm_step(l, ids, n_ids, nullptr, nullptr, 0, nullptr, nullptr, nullptr, &next)
+                                    : llm_step(l, nullptr, 1, nullptr, nullptr, 0, nullptr, nullptr, &tok, &next);
+        if (st != OX_OK) return st;
+        tok = next;
+        l->s->download_async(tok, l->pinned_tokens + i);
+    }
+    l->s->wait_idle();
+    std::memcpy(tokens_out, l->pinned_tokens, sizeof(int64_t) * (size_t)n_new);
+    return OX_OK;
+    OX_CATCH
+}
+
 namespace {
 ox_status llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_out, void* logits_out, size_t logits_cap,
-                   size_t* logits_written, const SamplingArgs* sampling) {
+                   size_t* logits_written, const SamplingArgs* sampling, const oxrt::DTensor* ids_dev, oxrt::DTensor* token_dev) {
     OX_TRY
     if (n_ids <= 0) fail(ErrKind::Shape, "Cannot step with empty input_ids");
     if (l->past + n_ids > l->max_seq_len)
@@ -122,7 +160,8 @@ ox_status llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_
         const DType dt = m.values[m.inputs[i].second].ty.dtype;
         oxrt::DTensor t;
         if (name == "input_ids") {
-            t = s.upload(DType::I64, {1, (int64_t)n_ids}, ids, sizeof(int64_t) * (size_t)n_ids);
+            if (ids_dev) t = *ids_dev;  // the previous step's token, still on the device
+            else t = s.upload(DType::I64, {1, (int64_t)n_ids}, ids, sizeof(int64_t) * (size_t)n_ids);
         } else if (name == "position_ids") {
             std::vector<int64_t> pos((size_t)n_ids);
             for (int j = 0; j < n_ids; j++) pos[j] = l->past + j;
@@ -159,8 +198,14 @@ ox_status llm_step(ox_llm* l, const int64_t* ids, int32_t n_ids, int64_t* token_
         last.shape = {1, vocab};
         last.offset += (size_t)(rows - 1) * dtype_storage_bytes(logits.dtype, (uint64_t)vocab);
         tok = s.sample_last(last, sampling->temperature, (long long)sampling->top_k, sampling->top_p, &sampling->uniform, 1);
-    } else if (token_out) {
+    } else if (token_out || token_dev) {
         tok = s.argmax_last(logits);
+    }
+    if (token_dev) {  // the last position's id as a [1, 1] tensor: the next step's input_ids
+        *token_dev = tok;
+        const int64_t n = tok.numel();
+        token_dev->offset += (size_t)(n - 1) * sizeof(int64_t);
+        token_dev->shape = {1, 1};
     }
     // While the device works on this step, get the plan of the next one-token step ready.
     if (l->past + 1 <= l->max_seq_len) {

@@ -766,6 +766,12 @@ void Session::download(const DTensor& t, void* dst, size_t cap, size_t* written)
     check_device_error();
 }
 
+void Session::download_async(const DTensor& t, void* pinned_dst) {
+    OX_CUDA(cudaSetDevice(device_));
+    if (t.cap) fail(ErrKind::Shape, "download_async: the tensor must be densely packed");
+    if (t.nbytes()) OX_CUDA(cudaMemcpyAsync(pinned_dst, t.ptr(), t.nbytes(), cudaMemcpyDeviceToHost, stream_));
+}
+
 DTensor Session::argmax_last(const DTensor& logits) {
     OX_CUDA(cudaSetDevice(device_));
     if (!dtype_is_float(logits.dtype) || logits.shape.empty() || logits.shape.back() == 0)

@@ -94,6 +94,9 @@ public:
     std::vector<std::pair<std::string, DTensor>> run(const std::vector<std::pair<std::string, DTensor>>& inputs);
     void preplan(const std::vector<std::pair<std::string, DTensor>>& next_inputs);
     void download(const DTensor& t, void* dst, size_t cap, size_t* written);
+    // Enqueues the copy of a densely packed tensor into pinned host memory and returns at once; the bytes are there
+    // after the next wait_idle().
+    void download_async(const DTensor& t, void* pinned_dst);
     DTensor argmax_last(const DTensor& logits);
     DTensor sample_last(const DTensor& logits, float temperature, long long top_k, float top_p, const float* u, size_t n_u);
     void argmax_last_into(const DTensor& logits, const DTensor& out);

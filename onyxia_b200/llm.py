@@ -147,6 +147,15 @@ class NativeLlmSession:
         _ffi.check(self._lib.ox_llm_step(self._h, arr, len(ids), C.byref(tok), None, 0, None))
         return tok.value
 
+    def generate(self, ids, n_new: int) -> list:
+        """`n_new` greedy tokens after `ids`; the token id travels from step to step on the device (ox_llm_generate)."""
+        C = self._C
+        from . import _ffi
+        arr = (C.c_int64 * len(ids))(*ids)
+        out = (C.c_int64 * max(n_new, 1))()
+        _ffi.check(self._lib.ox_llm_generate(self._h, arr, len(ids), int(n_new), out))
+        return [int(out[i]) for i in range(n_new)]
+
     def step_sampled(self, ids, temperature: float, top_k: int, top_p: float, uniform: float) -> int:
         """The step with the next token drawn on the device (≙ sampling::sample, crates/onyxia-cli/src/sampling.rs:36-65);
         `uniform` is the caller's random number in [0, 1]."""

@@ -194,6 +194,7 @@ unsafe extern "C" {
     pub fn ox_llm_reset(l: *mut ox_llm);
     pub fn ox_llm_step(l: *mut ox_llm, ids: *const i64, n_ids: i32, token_out: *mut i64, logits_out: *mut c_void, logits_cap: usize,
                        logits_written: *mut usize) -> i32;
+    pub fn ox_llm_generate(l: *mut ox_llm, ids: *const i64, n_ids: i32, n_new: i32, tokens_out: *mut i64) -> i32;
     pub fn ox_llm_step_sampled(l: *mut ox_llm, ids: *const i64, n_ids: i32, temperature: f32, top_k: i64, top_p: f32, uniform: f32,
                                token_out: *mut i64) -> i32;
 }

@@ -616,6 +616,12 @@ impl<'s> CudaLlm<'s> {
         check(unsafe { ffi::ox_llm_step(self.raw, ids.as_ptr(), ids.len() as i32, &mut tok, ptr::null_mut(), 0, ptr::null_mut()) })?;
         Ok(tok)
     }
+    /// `n_new` greedy tokens after `ids`, the token id passed from step to step on the device.
+    pub fn generate(&mut self, ids: &[i64], n_new: usize) -> Result<Vec<i64>> {
+        let mut out = vec![0i64; n_new];
+        check(unsafe { ffi::ox_llm_generate(self.raw, ids.as_ptr(), ids.len() as i32, n_new as i32, out.as_mut_ptr()) })?;
+        Ok(out)
+    }
     /// The same step with the next token drawn on the device ≙ `sample` (crates/onyxia-cli/src/sampling.rs:36-65);
     /// `uniform` is `rng.next_u32() as f32 / u32::MAX as f32` from the caller's generator.
     pub fn step_sampled(&mut self, ids: &[i64], temperature: f32, top_k: usize, top_p: f32, uniform: f32) -> Result<i64> {

@@ -176,3 +176,22 @@ def test_long_decode_crosses_length_buckets_and_cache_growth():
     full = whole.prefill(prompt + toks)
     assert np.isfinite(inc).all()
     assert np.abs(full - inc).max() <= 2e-2, float(np.abs(full - inc).max())
+
+
+def test_generate_hands_the_token_over_on_the_device():
+    """ox_llm_generate (ids never leave the device between steps) gives the tokens of the one-call-per-step loop."""
+    cfg = models.DecoderConfig("generate", layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1024,
+                               act_dtype=ir.F16, max_positions=128, last_logits_only=True)
+    prompt = np.random.default_rng(8).integers(0, cfg.vocab, 10).tolist()
+    backend = be.CudaBackend((0,))
+    a = llm.NativeLlmSession(backend, models.build_decoder(cfg, seed=6), 128)
+    b = llm.NativeLlmSession(backend, models.build_decoder(cfg, seed=6), 128)
+    want = [a.step_greedy(prompt)]
+    for _ in range(19):
+        want.append(a.step_greedy([want[-1]]))
+    got = b.generate(prompt, 12)
+    got += b.generate([got[-1]], 8)      # continues from where the first call stopped
+    assert got == want
+    assert a.sequence_length() == b.sequence_length()
+    with pytest.raises(Exception, match="max_seq_len"):
+        b.generate([got[-1]], 200)
