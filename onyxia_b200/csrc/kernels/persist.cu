@@ -606,6 +606,15 @@ __device__ void run_gemv(const Ctx& c, const POpDev& op, unsigned& stage_q) {
         int j = c.warp;
         if (j < ntile) {
             Cursor q1 = seek(j);
+#ifdef OX_NO_PAIR
+            for (; j < ntile; j += kCW) {
+                const unsigned char* rec = record(q1);
+                float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
+                tile_mma_zp8(rec, ap0 + q1.kt * 16, 4, lane, ca, cb);
+                finish(j, q1, ca, cb);
+                if (j + kCW < ntile) advance(q1, kCW);
+            }
+#endif
             for (; j + kCW < ntile; j += 2 * kCW) {
                 Cursor q2 = q1;
                 advance(q2, kCW);
