@@ -347,26 +347,49 @@ struct TcReduceP {
     long long row0;  // first weight row (in stream order) of the tail blocks
 };
 
+// Adds the pieces of the row blocks that were cut along K, in piece order, in f64; one rounding. blockIdx.y is the
+// activation row, a thread owns four consecutive weight rows (one 16-byte load per piece, the loads of four pieces in
+// flight together).
 __global__ void __launch_bounds__(256) nbits_gemm_reduce(const TcReduceP p) {
-    const long long rows = (long long)p.row_tiles * 16 - p.row0;
-    const long long m_here = min((long long)p.mb, p.m_total - p.m0);
-    for (long long i = global_tid(); i < rows * m_here; i += global_threads()) {
-        const long long rl = i % rows, m = i / rows, r = p.row0 + rl;
-        double acc = 0.0;
-        for (int sp = 0; sp < p.splits; sp++) acc += (double)p.partial[((size_t)sp * p.mb + m) * p.n_pad + rl];
-        const int rtg = (int)(r >> 4);
-        int seg = 0;
-        long long row;
-        if (p.interleave2) {
-            seg = rtg & 1;
-            row = (long long)(rtg >> 1) * 16 + (r & 15);
-        } else {
-            if (p.n_seg > 1 && rtg >= p.seg_rt0[1]) seg = 1;
-            if (p.n_seg > 2 && rtg >= p.seg_rt0[2]) seg = 2;
-            row = (long long)(rtg - p.seg_rt0[seg]) * 16 + (r & 15);
-        }
-        if (row < p.seg_n[seg]) p.y[seg][(p.m0 + m) * p.seg_n[seg] + row] = __double2half(acc);
+    pdl_enter();
+    const int rows = (int)((long long)p.row_tiles * 16 - p.row0);  // a multiple of 16
+    const int m = (int)blockIdx.y;
+    const int rl = (int)(blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (rl >= rows) return;
+    const float4* src = reinterpret_cast<const float4*>(p.partial + (size_t)m * p.n_pad + rl);
+    const size_t piece = (size_t)p.mb * p.n_pad / 4;  // float4s between two pieces
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};
+    int sp = 0;
+    for (; sp + 4 <= p.splits; sp += 4) {
+        const float4 a = src[(size_t)sp * piece], b = src[(size_t)(sp + 1) * piece], c = src[(size_t)(sp + 2) * piece], d = src[(size_t)(sp + 3) * piece];
+        acc[0] = (((acc[0] + (double)a.x) + (double)b.x) + (double)c.x) + (double)d.x;
+        acc[1] = (((acc[1] + (double)a.y) + (double)b.y) + (double)c.y) + (double)d.y;
+        acc[2] = (((acc[2] + (double)a.z) + (double)b.z) + (double)c.z) + (double)d.z;
+        acc[3] = (((acc[3] + (double)a.w) + (double)b.w) + (double)c.w) + (double)d.w;
     }
+    for (; sp < p.splits; sp++) {
+        const float4 a = src[(size_t)sp * piece];
+        acc[0] += (double)a.x;
+        acc[1] += (double)a.y;
+        acc[2] += (double)a.z;
+        acc[3] += (double)a.w;
+    }
+    const long long r = p.row0 + rl;
+    const int rtg = (int)(r >> 4);
+    int seg = 0;
+    long long row;
+    if (p.interleave2) {
+        seg = rtg & 1;
+        row = (long long)(rtg >> 1) * 16 + (r & 15);
+    } else {
+        if (p.n_seg > 1 && rtg >= p.seg_rt0[1]) seg = 1;
+        if (p.n_seg > 2 && rtg >= p.seg_rt0[2]) seg = 2;
+        row = (long long)(rtg - p.seg_rt0[seg]) * 16 + (r & 15);
+    }
+    __half* y = p.y[seg] + (size_t)(p.m0 + m) * p.seg_n[seg];
+#pragma unroll
+    for (int e = 0; e < 4; e++)
+        if (row + e < p.seg_n[seg]) y[row + e] = __double2half(acc[e]);
 }
 
 }  // namespace
@@ -467,11 +490,11 @@ void emit_nbits_gemm_tc(Emitter& em, const NBitsGroup& gr, const TRef& x, const 
             q.row0 = n_full * 128;
             for (int i = 0; i < 3; i++) q.seg_n[i] = p.seg_n[i];
             for (int i = 0; i < 4; i++) q.seg_rt0[i] = p.seg_rt0[i];
-            const long long work = ((long long)p.row_tiles * 16 - q.row0) * std::min<long long>(mb, gr.m - m0);
-            em.launch(nbits_gemm_reduce, dim3(grid_for(work, 256)), dim3(256), 0, q,
+            const long long rows = (long long)p.row_tiles * 16 - q.row0, m_here = std::min<long long>(mb, gr.m - m0);
+            em.launch(nbits_gemm_reduce, dim3((unsigned)((rows / 4 + 255) / 256), (unsigned)m_here), dim3(256), 0, q,
                       {{&q.partial, partial}, {&q.y[0], gr.y[0].buf}, {&q.y[1], gr.n_seg > 1 ? gr.y[1].buf : null},
                        {&q.y[2], gr.n_seg > 2 ? gr.y[2].buf : null}},
-                      "nbits_gemm_reduce");
+                      "nbits_gemm_reduce", /*pdl=*/true);
         }
     }
 }
