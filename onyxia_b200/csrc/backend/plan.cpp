@@ -73,9 +73,16 @@ struct OffsetAlloc {
     }
 };
 
-int64_t grow_capacity(int64_t rows) {
-    // room for the next appends: +50 %, at least 256 rows, multiple of 64
+// Rows a new KV buffer gets room for. Outgrowing it costs a step that copies every cache of the model into new
+// buffers, through plans and graphs of their own (measured: 20–460 ms on the 1B model), so small caches get room for
+// at least 1 024 more tokens and double; large ones (a batch of long sequences) grow by half.
+int64_t grow_capacity(int64_t rows, int64_t row_bytes) {
     int64_t extra = std::max<int64_t>(256, rows / 2);
+    if ((rows + std::max<int64_t>(1024, rows)) * row_bytes <= (int64_t)64 << 20) extra = std::max<int64_t>(1024, rows);
+    if (const char* e = std::getenv("ONYXIA_KV_ROOM")) {  // tests: a fixed number of spare rows, so that growth happens soon
+        const long long v = std::atoll(e);
+        if (v > 0) extra = v;
+    }
     return (rows + extra + 63) / 64 * 64;
 }
 
@@ -231,7 +238,7 @@ bool Session::lower_step(Plan& plan, oxk::Emitter& em, size_t step, Bindings& bi
                         ob.alias_input = in_idx;
                         tr.cap = inputs[in_idx].cap;
                     } else {
-                        tr.cap = grow_capacity(tr.shape[2]);
+                        tr.cap = grow_capacity(tr.shape[2], (int64_t)dtype_storage_bytes(dt, (uint64_t)(tr.shape[0] * tr.shape[1] * tr.shape[3])));
                         ob.kv_cap = tr.cap;
                         ob.bytes = dtype_storage_bytes(dt, (uint64_t)(tr.shape[0] * tr.shape[1] * tr.cap * tr.shape[3]));
                     }

@@ -156,11 +156,12 @@ def test_native_generation_loop_matches_the_python_loop():
         llm.NativeLlmSession(cuda_backend(), module.clone(), 4).step_greedy(prompt)
 
 
-def test_long_decode_crosses_length_buckets_and_cache_growth():
+def test_long_decode_crosses_length_buckets_and_cache_growth(monkeypatch):
     """300 greedy steps after a 500-token prompt on a 2-layer 1B-architecture model: the attention launches are
-    re-sized when the length leaves its 256-row bucket, the caches outgrow their capacity and move, the plan is
-    patched every step and replayed as a CUDA graph — and the last logits still equal those of one prefill over
-    the whole sequence."""
+    re-sized when the length leaves its 256-row bucket, the caches outgrow their capacity and move (the spare
+    room is cut to 256 rows here so that this happens within the test), the plan is patched every step and
+    replayed as a CUDA graph — and the last logits still equal those of one prefill over the whole sequence."""
+    monkeypatch.setenv("ONYXIA_KV_ROOM", "256")
     cfg = models.config_gemma3_1b()
     cfg.layers, cfg.vocab = 2, 8192
     module = models.build_decoder(cfg, seed=21)
