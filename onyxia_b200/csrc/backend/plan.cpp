@@ -75,10 +75,11 @@ struct OffsetAlloc {
 
 // Rows a new KV buffer gets room for. Outgrowing it costs a step that copies every cache of the model into new
 // buffers, through plans and graphs of their own (measured: 20–460 ms on the 1B model), so small caches get room for
-// at least 1 024 more tokens and double; large ones (a batch of long sequences) grow by half.
+// at least 4 096 more tokens and double; large ones (a batch of long sequences) grow by half.
 int64_t grow_capacity(int64_t rows, int64_t row_bytes) {
     int64_t extra = std::max<int64_t>(256, rows / 2);
-    if ((rows + std::max<int64_t>(1024, rows)) * row_bytes <= (int64_t)64 << 20) extra = std::max<int64_t>(1024, rows);
+    if ((rows + std::max<int64_t>(4096, rows)) * row_bytes <= (int64_t)64 << 20) extra = std::max<int64_t>(4096, rows);
+    else if ((rows + std::max<int64_t>(1024, rows)) * row_bytes <= (int64_t)64 << 20) extra = std::max<int64_t>(1024, rows);
     if (const char* e = std::getenv("ONYXIA_KV_ROOM")) {  // tests: a fixed number of spare rows, so that growth happens soon
         const long long v = std::atoll(e);
         if (v > 0) extra = v;
