@@ -1,9 +1,10 @@
 """A minimal ONNX reader / writer and the lowering of the operators a quantised decoder export uses.
 
 ≙ ``crates/onyxia-onnx/src/parser.rs:17-117`` (ModelProto → graph) and the rules of
-``crates/onyxia-lower/src/rules.rs`` that the decoder path needs: the four composites
-(``SimplifiedLayerNormalization``, ``Gelu``, ``com.microsoft.MatMulNBits`` :890-940,
-``com.microsoft.GroupQueryAttention`` :777-888) and the plain operators around them. There is no
+``crates/onyxia-lower/src/rules.rs:18-96``: one ``op_<Name>`` method per registered operator — the composites
+(``Softmax``, ``Gelu``, ``Trilu``, ``SimplifiedLayerNormalization``, ``com.microsoft.MatMulNBits`` :890-940,
+``com.microsoft.GroupQueryAttention`` :777-888, the two rotary embeddings) and the plain element-wise,
+structural and reduction operators, plus ``Constant`` nodes (initializers spelled as nodes). There is no
 ``protoc`` and no ``onnx`` package here, so the protobuf wire format is read and written by hand
 (varints, length-delimited fields); only the fields of ``onnx.proto`` that such graphs use are known.
 
@@ -330,6 +331,43 @@ class _Lower:
         if i < len(node.outputs) and node.outputs[i]:
             self.vals[node.outputs[i]] = val
 
+    def vid(self, v):
+        """The module value of an operand; a compile-time shape value consumed by a tensor operation is
+        materialised as a DimValues node evaluated at run time (lib.rs value(): Content → DimValues)."""
+        if v.vid is None:
+            out = self.b.dim_values(list(v.content))
+            if not v.shape:
+                out = self.b.reshape(out, [])
+            if v.dtype != ir.I64:
+                out = self.b.cast(out, v.dtype)
+            v.vid = out
+        return v.vid
+
+    def content_of(self, name):
+        """Compile-time integer content of an operand: a shape value, or a small integer initializer. None otherwise."""
+        v = self.val(name)
+        if v.content is not None:
+            return list(v.content)
+        if v.const is not None and v.dtype in (ir.I64, ir.I32) and v.const.ndim <= 1 and v.const.size <= 64:
+            return [int(c) for c in np.asarray(v.const).reshape(-1)]
+        return None
+
+    @staticmethod
+    def _signed_const(d):
+        """A dimension expression or an integer as a Python int when it has no symbols (negative values included)."""
+        if isinstance(d, DimExpr):
+            if not d.terms:
+                return 0
+            return d.terms[()] if list(d.terms) == [()] else None
+        return int(d)
+
+    @staticmethod
+    def _div_exact(d, k):
+        d = DimExpr.of(d)
+        if k == 0 or any(c % k for c in d.terms.values()):
+            return None
+        return DimExpr({s: c // k for s, c in d.terms.items()})
+
     @staticmethod
     def _broadcast(a, b):
         ra, rb = list(a), list(b)
@@ -365,18 +403,94 @@ class _Lower:
     def op_Identity(self, n):
         self.set(n, 0, self.val(n.inputs[0]))
 
-    def _binary(self, n, op):
+    def _binary(self, n, op, out_dtype=None):
         a, b = self.val(n.inputs[0]), self.val(n.inputs[1])
-        if a.content is not None and b.content is not None and op in (ir.ADD, ir.SUB, ir.MUL):
-            f = {ir.ADD: lambda x, y: x + y, ir.SUB: lambda x, y: x - y, ir.MUL: lambda x, y: x * y}[op]
-            self.set(n, 0, _Val(None, a.dtype, a.shape, content=[f(x, y) for x, y in zip(a.content, b.content)]))
-            return
-        self.set(n, 0, _Val(self.b.binary(op, a.vid, b.vid), a.dtype, self._broadcast(a.shape, b.shape)))
+        if op in (ir.ADD, ir.SUB, ir.MUL, ir.DIV) and (a.content is not None or b.content is not None):
+            ca, cb = self.content_of(n.inputs[0]), self.content_of(n.inputs[1])
+            if ca is not None and cb is not None and (len(ca) == len(cb) or 1 in (len(ca), len(cb))):
+                m = max(len(ca), len(cb))
+                ca, cb = ca * (m // len(ca)), cb * (m // len(cb))
+                f = {ir.ADD: lambda x, y: DimExpr.of(x) + y, ir.SUB: lambda x, y: DimExpr.of(x) - y, ir.MUL: lambda x, y: DimExpr.of(x) * y,
+                     ir.DIV: lambda x, y: self._div_exact(x, self._signed_const(y) or 0)}[op]
+                out = [f(x, y) for x, y in zip(ca, cb)]
+                if None not in out:
+                    shape = a.shape if len(a.shape) >= len(b.shape) else b.shape
+                    self.set(n, 0, _Val(None, a.dtype, shape, content=out))
+                    return
+        self.set(n, 0, _Val(self.b.binary(op, self.vid(a), self.vid(b)), out_dtype or a.dtype, self._broadcast(a.shape, b.shape)))
 
     def op_Add(self, n): self._binary(n, ir.ADD)
     def op_Sub(self, n): self._binary(n, ir.SUB)
     def op_Mul(self, n): self._binary(n, ir.MUL)
     def op_Div(self, n): self._binary(n, ir.DIV)
+    def op_And(self, n): self._binary(n, ir.AND)
+    def op_Or(self, n): self._binary(n, ir.OR)
+    def op_Xor(self, n): self._binary(n, ir.XOR)
+
+    def op_Pow(self, n):
+        # ONNX lets the exponent have another type; the primitive wants the base's (rules.rs:116-125)
+        a, b = self.val(n.inputs[0]), self.val(n.inputs[1])
+        bv = self.vid(b) if b.dtype == a.dtype else self.b.cast(self.vid(b), a.dtype)
+        self.set(n, 0, _Val(self.b.binary(ir.POW, self.vid(a), bv), a.dtype, self._broadcast(a.shape, b.shape)))
+
+    def _variadic(self, n, op):
+        # Max / Min take any number of operands: folded from the left (rules.rs:127-136)
+        acc = self.val(n.inputs[0])
+        out, shape = self.vid(acc), list(acc.shape)
+        for name in n.inputs[1:]:
+            r = self.val(name)
+            out, shape = self.b.binary(op, out, self.vid(r)), self._broadcast(shape, r.shape)
+        self.set(n, 0, _Val(out, acc.dtype, shape))
+
+    def op_Max(self, n): self._variadic(n, ir.MAX)
+    def op_Min(self, n): self._variadic(n, ir.MIN)
+
+    def _compare(self, n, op):
+        a, b = self.val(n.inputs[0]), self.val(n.inputs[1])
+        self.set(n, 0, _Val(self.b.cmp(op, self.vid(a), self.vid(b)), ir.BOOL, self._broadcast(a.shape, b.shape)))
+
+    def op_Equal(self, n): self._compare(n, ir.EQ)
+    def op_Greater(self, n): self._compare(n, ir.GT)
+    def op_GreaterOrEqual(self, n): self._compare(n, ir.GE)
+    def op_Less(self, n): self._compare(n, ir.LT)
+    def op_LessOrEqual(self, n): self._compare(n, ir.LE)
+
+    def _unary(self, n, op):
+        x = self.val(n.inputs[0])
+        self.set(n, 0, _Val(self.b.unary(op, self.vid(x)), x.dtype, x.shape))
+
+    def op_Neg(self, n): self._unary(n, ir.NEG)
+    def op_Abs(self, n): self._unary(n, ir.ABS)
+    def op_Sqrt(self, n): self._unary(n, ir.SQRT)
+    def op_Exp(self, n): self._unary(n, ir.EXP)
+    def op_Log(self, n): self._unary(n, ir.LOG)
+    def op_Sin(self, n): self._unary(n, ir.SIN)
+    def op_Cos(self, n): self._unary(n, ir.COS)
+    def op_Tanh(self, n): self._unary(n, ir.TANH)
+    def op_Erf(self, n): self._unary(n, ir.ERF)
+    def op_Floor(self, n): self._unary(n, ir.FLOOR)
+    def op_Ceil(self, n): self._unary(n, ir.CEIL)
+    def op_Not(self, n): self._unary(n, ir.NOT)
+
+    def op_Where(self, n):
+        c, a, b = (self.val(i) for i in n.inputs[:3])
+        shape = self._broadcast(self._broadcast(c.shape, a.shape), b.shape)
+        self.set(n, 0, _Val(self.b.select(self.vid(c), self.vid(a), self.vid(b)), a.dtype, shape))
+
+    def op_Constant(self, n):
+        """A Constant node is an initializer spelled as a node (parser.rs:81-100)."""
+        a = n.attrs
+        if "value" in a:
+            _, dtype, dims, raw = a["value"]
+        elif "value_int" in a or "value_ints" in a:
+            arr = np.asarray(a.get("value_ints", a.get("value_int")), np.int64)
+            dtype, dims, raw = ir.I64, list(arr.shape), np.frombuffer(arr.tobytes(), np.uint8).copy()
+        elif "value_float" in a or "value_floats" in a:
+            arr = np.asarray(a.get("value_floats", a.get("value_float")), np.float32)
+            dtype, dims, raw = ir.F32, list(arr.shape), np.frombuffer(arr.tobytes(), np.uint8).copy()
+        else:
+            raise OnnxError(f"Constant '{n.name}' carries no tensor, integer or float value")
+        self.inits[n.outputs[0]] = (dtype, list(dims), raw)
 
     def op_Cast(self, n):
         x = self.val(n.inputs[0])
@@ -404,46 +518,92 @@ class _Lower:
         idx = self.val(n.inputs[1])
         if axis < 0:
             axis += len(data.shape)
-        ivid = idx.vid if idx.dtype == ir.I64 else self.b.cast(idx.vid, ir.I64)  # the primitive takes i64 indices (rules.rs:503-522)
+        ivid = self.vid(idx) if idx.dtype == ir.I64 else self.b.cast(self.vid(idx), ir.I64)  # the primitive takes i64 indices (rules.rs:503-522)
         shape = data.shape[:axis] + idx.shape + data.shape[axis + 1:]
         self.set(n, 0, _Val(self.b.gather(data.vid, ivid, axis), data.dtype, shape))
 
-    def op_ReduceSum(self, n):
+    def _reduce(self, n, op):
         x = self.val(n.inputs[0])
         axes = self.int_list(n, 1, "axes")
         keep = bool(n.attrs.get("keepdims", 1))
-        if axes is None:
+        if x.content is not None and axes in (None, [0], [-1]) and op in (ir.SUM, ir.PROD):
+            acc = DimExpr.of(0 if op == ir.SUM else 1)  # e.g. ReduceProd over a shape vector = element count
+            for c in x.content:
+                acc = acc + c if op == ir.SUM else acc * c
+            self.set(n, 0, _Val(None, x.dtype, [DimExpr.of(1)] if keep else [], content=[acc]))
+            return
+        if not axes:
+            if int(n.attrs.get("noop_with_empty_axes", 0)):
+                self.set(n, 0, x)
+                return
             axes = list(range(len(x.shape)))
-        axes = sorted(a + len(x.shape) if a < 0 else a for a in axes)
+        axes = sorted({self._axis(n, a, len(x.shape)) for a in axes})
         shape = [DimExpr.of(1) if i in axes else d for i, d in enumerate(x.shape) if keep or i not in axes]
-        self.set(n, 0, _Val(self.b.reduce(ir.SUM, x.vid, axes, keep), x.dtype, shape))
+        self.set(n, 0, _Val(self.b.reduce(op, self.vid(x), axes, keep), x.dtype, shape))
+
+    def op_ReduceSum(self, n): self._reduce(n, ir.SUM)
+    def op_ReduceMean(self, n): self._reduce(n, ir.MEAN)
+    def op_ReduceMax(self, n): self._reduce(n, ir.RMAX)
+    def op_ReduceMin(self, n): self._reduce(n, ir.RMIN)
+    def op_ReduceProd(self, n): self._reduce(n, ir.PROD)
+
+    def _axis(self, n, a, rank):
+        if not -rank <= a < max(rank, 1):
+            raise OnnxError(f"{n.op} '{n.name}': axis {a} is outside rank {rank}")
+        return a + rank if a < 0 else a
 
     def op_Slice(self, n):
+        """Bounds may be shape arithmetic; axes and steps are constants (rules.rs:421-501). An end of INT32_MAX or
+        more means "to the end", negative constants count from the end, constants are clamped to constant extents."""
         x = self.val(n.inputs[0])
-        starts, ends = self.int_list(n, 1, "starts"), self.int_list(n, 2, "ends")
+        starts = self.content_of(n.inputs[1]) if self.has(n, 1) else n.attrs.get("starts")
+        ends = self.content_of(n.inputs[2]) if self.has(n, 2) else n.attrs.get("ends")
+        if starts is None or ends is None:
+            raise OnnxError(f"Slice '{n.name}': starts / ends are not resolvable when the graph is lowered")
+        dims = [DimExpr.of(len(x.content))] if x.content is not None else list(x.shape)
         axes = self.int_list(n, 3, "axes") or list(range(len(starts)))
         steps = self.int_list(n, 4) or [1] * len(starts)
-        specs, shape = [], list(x.shape)
+        specs, shape = [], list(dims)
         for s, e, ax, st in zip(starts, ends, axes, steps):
-            if st != 1:
-                raise OnnxError(f"Slice '{n.name}': only step 1 is lowered here")
-            ax = ax + len(x.shape) if ax < 0 else ax
-            dim = x.shape[ax]
-            lo = dim + s if s < 0 else DimExpr.of(s)
-            hi = dim if e >= (1 << 31) - 1 else (dim + e if e < 0 else DimExpr.of(e))
-            specs.append((ax, lo, hi, 1))
-            shape[ax] = hi - lo
+            ax = self._axis(n, ax, len(dims))
+            dim = dims[ax]
+
+            def norm(bound, is_end):
+                v = self._signed_const(bound)
+                if v is None:
+                    return DimExpr.of(bound)
+                if is_end and v >= (1 << 31) - 1:
+                    return dim
+                if v < 0:
+                    return dim + v
+                return DimExpr.of(min(v, dim.as_const()) if dim.as_const() is not None else v)
+            lo, hi = norm(s, False), norm(e, True)
+            if st == 1:
+                shape[ax] = hi - lo
+            elif st == -1:
+                shape[ax] = lo - hi
+            else:
+                a, b = self._signed_const(lo), self._signed_const(hi)
+                if st == 0 or a is None or b is None:
+                    raise OnnxError(f"Slice '{n.name}': step {st} needs constant bounds")
+                shape[ax] = DimExpr.of(max(0, -(-(b - a) // st) if st > 0 else -(-(a - b) // -st)))
+            specs.append((ax, lo, hi, int(st)))
+        if x.content is not None:  # a piece of a shape vector
+            (ax, lo, hi, st), = specs
+            a, b = self._signed_const(lo), self._signed_const(hi)
+            self.set(n, 0, _Val(None, x.dtype, [DimExpr.of(len(x.content[a:b:st]))], content=x.content[a:b:st]))
+            return
         self.set(n, 0, _Val(self.b.slice(x.vid, specs), x.dtype, shape))
 
     def op_Transpose(self, n):
         x = self.val(n.inputs[0])
         perm = [int(p) for p in n.attrs.get("perm", list(range(len(x.shape)))[::-1])]
-        self.set(n, 0, _Val(self.b.transpose(x.vid, perm), x.dtype, [x.shape[p] for p in perm]))
+        self.set(n, 0, _Val(self.b.transpose(self.vid(x), perm), x.dtype, [x.shape[p] for p in perm]))
 
     def op_MatMul(self, n):
         # rank-1 operands are promoted in lowering, not in the primitive (rules.rs:171-213)
         a, b = self.val(n.inputs[0]), self.val(n.inputs[1])
-        av, ash, bv, bsh = a.vid, list(a.shape), b.vid, list(b.shape)
+        av, ash, bv, bsh = self.vid(a), list(a.shape), self.vid(b), list(b.shape)
         if len(ash) == 1:
             ash = [DimExpr.of(1)] + ash
             av = self.b.reshape(av, ash)
@@ -488,7 +648,7 @@ class _Lower:
                 raise OnnxError(f"Reshape '{n.name}': -1 beside symbolic dimensions is not lowered here")
             rest = int(np.prod(known)) if known else 1
             out[unknown] = DimExpr.of(int(np.prod(total)) // max(rest, 1))
-        self.set(n, 0, _Val(self.b.reshape(x.vid, out), x.dtype, out))
+        self.set(n, 0, _Val(self.b.reshape(self.vid(x), out), x.dtype, out))
 
     def op_Unsqueeze(self, n):
         x = self.val(n.inputs[0])
@@ -516,7 +676,95 @@ class _Lower:
         shape = list(vals[0].shape)
         for v in vals[1:]:
             shape[axis] = shape[axis] + v.shape[axis]
-        self.set(n, 0, _Val(self.b.concat([v.vid for v in vals], axis), vals[0].dtype, shape))
+        self.set(n, 0, _Val(self.b.concat([self.vid(v) for v in vals], axis), vals[0].dtype, shape))
+
+    def op_Squeeze(self, n):
+        x = self.val(n.inputs[0])
+        axes = self.int_list(n, 1, "axes")
+        if x.content is not None:  # a one-element shape vector becomes a scalar shape value
+            self.set(n, 0, _Val(None, x.dtype, [], content=list(x.content)))
+            return
+        drop = ([self._axis(n, a, len(x.shape)) for a in axes] if axes is not None
+                else [i for i, d in enumerate(x.shape) if d.as_const() == 1])
+        shape = [d for i, d in enumerate(x.shape) if i not in drop]
+        self.set(n, 0, _Val(self.b.reshape(x.vid, shape), x.dtype, shape))
+
+    def op_Expand(self, n):
+        x = self.val(n.inputs[0])
+        target = self.content_of(n.inputs[1])
+        if target is None:
+            raise OnnxError(f"Expand '{n.name}': the shape is not resolvable when the graph is lowered")
+        shape = self._broadcast(x.shape, [DimExpr.of(d) for d in target])  # ONNX Expand broadcasts both ways
+        self.set(n, 0, _Val(self.b.broadcast(self.vid(x), shape), x.dtype, shape))
+
+    def op_ScatterND(self, n):
+        if n.attrs.get("reduction", "none") != "none":
+            raise OnnxError(f"ScatterND reduction='{n.attrs['reduction']}'")
+        data, idx, upd = (self.val(i) for i in n.inputs[:3])
+        ivid = self.vid(idx) if idx.dtype == ir.I64 else self.b.cast(self.vid(idx), ir.I64)
+        self.set(n, 0, _Val(self.b.scatter(self.vid(data), ivid, self.vid(upd)), data.dtype, data.shape))
+
+    def op_Range(self, n):
+        """Iota plus element-wise arithmetic; start and delta are constants, the limit may be a shape value
+        (rules.rs:566-606)."""
+        parts = []
+        for i in range(3):
+            v = self.val(n.inputs[i])
+            c = self.content_of(n.inputs[i])
+            if c is None and v.const is not None and v.const.size == 1 and v.dtype in (ir.I64, ir.I32):
+                c = [int(np.asarray(v.const).reshape(-1)[0])]
+            if not c:
+                raise OnnxError(f"Range '{n.name}': bounds are not resolvable when the graph is lowered")
+            parts.append(c[0])
+        start, delta = self._signed_const(parts[0]), self._signed_const(parts[2])
+        if start is None or delta is None:
+            raise OnnxError(f"Range '{n.name}' with a symbolic start or delta")
+        if delta <= 0:
+            raise OnnxError(f"Range with delta {delta}")
+        length = self._div_exact(DimExpr.of(parts[1]) - start, delta)
+        if length is None:
+            raise OnnxError(f"Range '{n.name}': the length is not exactly divisible by delta")
+        dtype = self.val(n.inputs[0]).dtype
+        out = self.b.iota(length, ir.I64)
+        if delta != 1:
+            out = self.b.mul(out, self.b.const_i64([delta], []))
+        if start != 0:
+            out = self.b.add(out, self.b.const_i64([start], []))
+        if dtype != ir.I64:
+            out = self.b.cast(out, dtype)
+        self.set(n, 0, _Val(out, dtype, [length]))
+
+    def op_ConstantOfShape(self, n):
+        target = self.content_of(n.inputs[0])
+        if target is None:
+            raise OnnxError(f"ConstantOfShape '{n.name}': the shape is not resolvable when the graph is lowered")
+        if "value" in n.attrs:
+            _, dtype, _, raw = n.attrs["value"]
+        else:  # the operator's default fill: one f32 zero
+            dtype, raw = ir.F32, np.zeros(4, np.uint8)
+        scalar = self.b.constant(HostTensor(dtype, [], raw))
+        shape = [DimExpr.of(d) for d in target]
+        self.set(n, 0, _Val(self.b.broadcast(scalar, shape), dtype, shape))
+
+    def op_Trilu(self, n):
+        x = self.val(n.inputs[0])
+        k = 0
+        if self.has(n, 1):
+            ks = self.int_list(n, 1)
+            k = ks[0] if ks else 0
+        out = self.b.composite("Trilu", {"upper": int(n.attrs.get("upper", 1)), "k": int(k)}, [self.vid(x)], [(x.dtype, x.shape)])
+        self.set(n, 0, _Val(out[0], x.dtype, x.shape))
+
+    def _rotary(self, n, name):
+        ins = [self.val(n.inputs[i]) for i in range(4)]  # input, position_ids, cos_cache, sin_cache
+        attrs = {"interleaved": int(n.attrs.get("interleaved", 0)), "num_heads": max(int(n.attrs.get("num_heads", 0)), 0),
+                 "rotary_embedding_dim": int(n.attrs.get("rotary_embedding_dim", 0))}
+        x = ins[0]
+        out = self.b.composite(name, attrs, [self.vid(v) for v in ins], [(x.dtype, x.shape)])
+        self.set(n, 0, _Val(out[0], x.dtype, x.shape))
+
+    def op_RotaryEmbedding(self, n): self._rotary(n, "com.microsoft.RotaryEmbedding")
+    def op_GemmaRotaryEmbedding(self, n): self._rotary(n, "com.microsoft.GemmaRotaryEmbedding")
 
     def op_SimplifiedLayerNormalization(self, n):
         x, w = self.val(n.inputs[0]), self.val(n.inputs[1])
@@ -628,6 +876,8 @@ def _attr_proto(name, v):
         return out + _f_bytes(4, v.encode()) + _f_int(20, 3)
     if isinstance(v, (list, tuple)):
         return out + b"".join(_f_int(8, int(x)) for x in v) + _f_int(20, 7)
+    if isinstance(v, np.ndarray):  # an attribute tensor (ConstantOfShape 'value', Constant 'value')
+        return out + _f_bytes(5, _tensor_proto("", v)) + _f_int(20, 4)
     raise OnnxError(f"attribute '{name}': unsupported value {v!r}")
 
 

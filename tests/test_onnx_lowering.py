@@ -270,3 +270,333 @@ def test_reshape_with_shape_arithmetic_and_rank_one_matmul():
     vv = np.array([1, 2, 3], np.float32)
     got = _run(onnx.load_onnx_bytes(w.tobytes()), {"v": HostTensor.from_numpy(vv)})["o"].numpy()
     assert got.shape == (4,) and np.array_equal(got, vv @ np.arange(12, dtype=np.float32).reshape(3, 4))
+
+
+# ── the remaining rules of the reference's registry (crates/onyxia-lower/src/rules.rs:18-96) ──────────────────
+def _lower_and_run(w, feed):
+    module = onnx.load_onnx_bytes(w.tobytes())
+    return module, {k: v.numpy() for k, v in _run(module.clone(), {k: HostTensor.from_numpy(np.ascontiguousarray(v)) for k, v in feed.items()}).items()}
+
+
+def test_simple_graph_evaluates():
+    # out = (x + w) * x — lower_test.rs:113-129
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [2, 2])
+    w.initializer("w", np.array([[10, 20], [30, 40]], np.float32))
+    w.node("Add", ["x", "w"], ["sum"])
+    w.node("Mul", ["sum", "x"], ["out"])
+    w.output("out", ir.F32, [2, 2])
+    module, out = _lower_and_run(w, {"x": np.array([[1, 2], [3, 4]], np.float32)})
+    assert module.num_nodes == 2
+    assert out["out"].reshape(-1).tolist() == [11.0, 44.0, 99.0, 176.0]
+
+
+_UNARY = {"Neg": np.negative, "Abs": np.abs, "Sqrt": lambda x: np.sqrt(np.abs(x)), "Exp": np.exp, "Log": lambda x: np.log(np.abs(x) + 1),
+          "Sin": np.sin, "Cos": np.cos, "Tanh": np.tanh, "Floor": np.floor, "Ceil": np.ceil}
+
+
+@pytest.mark.parametrize("op", sorted(_UNARY) + ["Erf", "Not"])
+def test_unary_rules(op):
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((3, 5)) * 2).astype(np.float32)
+    w = onnx.OnnxWriter()
+    if op == "Not":
+        xb = rng.random((3, 5)) > 0.5
+        w.input("x", ir.BOOL, [3, 5])
+        w.node("Not", ["x"], ["out"])
+        w.output("out", ir.BOOL, [3, 5])
+        _, out = _lower_and_run(w, {"x": xb})
+        assert np.array_equal(out["out"].astype(bool), ~xb)
+        return
+    if op == "Sqrt":
+        x = np.abs(x)
+    if op == "Log":
+        x = np.abs(x) + 1
+    w.input("x", ir.F32, [3, 5])
+    w.node(op, ["x"], ["out"])
+    w.output("out", ir.F32, [3, 5])
+    _, out = _lower_and_run(w, {"x": x})
+    if op == "Erf":
+        import math
+        want = np.vectorize(math.erf)(x.astype(np.float64))
+    else:
+        want = {"Sqrt": np.sqrt, "Log": np.log}.get(op, _UNARY[op])(x.astype(np.float64))
+    assert (np.abs(out["out"] - want) / np.maximum(1.0, np.abs(want))).max() < 2e-6  # one f32 rounding, relative above 1
+
+
+def test_binary_variadic_compare_and_where_rules():
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((2, 4)).astype(np.float32)
+    b = rng.standard_normal((4,)).astype(np.float32)
+    c = rng.standard_normal((2, 1)).astype(np.float32)
+    w = onnx.OnnxWriter()
+    w.input("a", ir.F32, [2, 4])
+    w.input("b", ir.F32, [4])
+    w.input("c", ir.F32, [2, 1])
+    w.initializer("two", np.array(2, np.int64))
+    w.node("Max", ["a", "b", "c"], ["mx"])
+    w.node("Min", ["a", "b", "c"], ["mn"])
+    w.node("Max", ["a"], ["same"])
+    w.node("Pow", ["a", "two"], ["sq"])          # integer exponent beside a float base
+    for op in ("Equal", "Greater", "GreaterOrEqual", "Less", "LessOrEqual"):
+        w.node(op, ["a", "b"], [op])
+    w.node("And", ["Greater", "Less"], ["and"])
+    w.node("Or", ["Greater", "Equal"], ["or"])
+    w.node("Xor", ["GreaterOrEqual", "LessOrEqual"], ["xor"])
+    w.node("Where", ["Greater", "a", "c"], ["pick"])
+    for name, dt in (("mx", ir.F32), ("mn", ir.F32), ("same", ir.F32), ("sq", ir.F32), ("and", ir.BOOL), ("or", ir.BOOL), ("xor", ir.BOOL),
+                     ("pick", ir.F32), ("Equal", ir.BOOL), ("LessOrEqual", ir.BOOL)):
+        w.output(name, dt, [2, 4])
+    b[1] = a[0, 1]  # one exact tie
+    _, out = _lower_and_run(w, {"a": a, "b": b, "c": c})
+    assert np.array_equal(out["mx"], np.maximum(np.maximum(a, b), c))
+    assert np.array_equal(out["mn"], np.minimum(np.minimum(a, b), c))
+    assert np.array_equal(out["same"], a)
+    assert np.abs(out["sq"] - a * a).max() < 1e-6
+    assert np.array_equal(out["Equal"].astype(bool), a == b) and (a == b).any()
+    assert np.array_equal(out["LessOrEqual"].astype(bool), a <= b)
+    assert np.array_equal(out["and"].astype(bool), (a > b) & (a < b))
+    assert np.array_equal(out["or"].astype(bool), (a > b) | (a == b))
+    assert np.array_equal(out["xor"].astype(bool), (a >= b) ^ (a <= b))
+    assert np.array_equal(out["pick"], np.where(a > b, a, np.broadcast_to(c, a.shape)))
+
+
+def test_reduce_axes_as_attribute_and_as_operand():
+    # lower_test.rs:180-216
+    x = np.array([[1, 2, 3], [4, 5, 6]], np.float32)
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [2, 3])
+    w.node("ReduceMean", ["x"], ["out"], axes=[-1], keepdims=0)
+    w.output("out", ir.F32, [2])
+    assert _lower_and_run(w, {"x": x})[1]["out"].tolist() == [2.0, 5.0]
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [2, 3])
+    w.initializer("axes", np.array([0], np.int64))
+    w.node("ReduceSum", ["x", "axes"], ["out"], keepdims=1)
+    w.output("out", ir.F32, [1, 3])
+    out = _lower_and_run(w, {"x": x})[1]["out"]
+    assert out.shape == (1, 3) and out.reshape(-1).tolist() == [5.0, 7.0, 9.0]
+    # the other three reductions; no axes = every axis; noop_with_empty_axes leaves the operand alone
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [2, 3])
+    w.node("ReduceMax", ["x"], ["mx"], axes=[1], keepdims=0)
+    w.node("ReduceMin", ["x"], ["mn"], keepdims=0)
+    w.node("ReduceProd", ["x"], ["pr"], axes=[0, -2], keepdims=1)
+    w.node("ReduceSum", ["x"], ["noop"], noop_with_empty_axes=1)
+    w.node("Add", ["noop", "pr"], ["sum"])
+    for name, shape in (("mx", [2]), ("mn", []), ("pr", [1, 3]), ("sum", [2, 3])):
+        w.output(name, ir.F32, shape)
+    out = _lower_and_run(w, {"x": x})[1]
+    assert out["mx"].tolist() == [3.0, 6.0] and float(out["mn"]) == 1.0
+    assert out["pr"].reshape(-1).tolist() == [4.0, 10.0, 18.0]
+    assert np.array_equal(out["sum"], x + np.array([[4, 10, 18]], np.float32))
+
+
+def test_constant_of_shape_and_expand_over_a_symbolic_shape():
+    # lower_test.rs:308-327
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["S", 4])
+    w.initializer("bias", np.array([1, 2, 3, 4], np.float32))
+    w.node("Shape", ["x"], ["shp"])
+    w.node("ConstantOfShape", ["shp"], ["zeros"])
+    w.node("Expand", ["bias", "shp"], ["bias_full"])
+    w.node("Add", ["zeros", "bias_full"], ["out"])
+    w.output("out", ir.F32, ["S", 4])
+    out = _lower_and_run(w, {"x": np.zeros((2, 4), np.float32)})[1]["out"]
+    assert out.shape == (2, 4) and out.reshape(-1).tolist() == [1, 2, 3, 4, 1, 2, 3, 4]
+
+
+def test_constant_of_shape_keeps_the_value_tensors_type():
+    # lower_test.rs:330-358: an i64 ones-fill must survive with its type
+    w = onnx.OnnxWriter()
+    w.input("x", ir.I64, [3])
+    w.node("Shape", ["x"], ["shp"])
+    w.node("ConstantOfShape", ["shp"], ["ones"], value=np.array([1], np.int64))
+    w.node("Add", ["ones", "x"], ["out"])
+    w.output("out", ir.I64, [3])
+    out = _lower_and_run(w, {"x": np.array([10, 20, 30], np.int64)})[1]["out"]
+    assert out.dtype == np.int64 and out.tolist() == [11, 21, 31]
+
+
+def test_shape_value_consumed_by_a_tensor_operation_is_evaluated_at_run_time():
+    # lower_test.rs:361-415: seqlens = Shape(mask)[1] - 1 expanded to [batch, 1]
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["B", "T"])
+    w.initializer("idx0", np.array(0, np.int64))
+    w.initializer("idx1", np.array(1, np.int64))
+    w.initializer("c1", np.array(1, np.int64))
+    w.initializer("ax0", np.array([0], np.int64))
+    w.initializer("one_vec", np.array([1], np.int64))
+    w.node("Shape", ["x"], ["shp"])
+    w.node("Gather", ["shp", "idx1"], ["t"], axis=0)
+    w.node("Sub", ["t", "c1"], ["tm1"])
+    w.node("Unsqueeze", ["tm1", "ax0"], ["u"])
+    w.node("Gather", ["shp", "idx0"], ["b"], axis=0)
+    w.node("Unsqueeze", ["b", "ax0"], ["bu"])
+    w.node("Concat", ["bu", "one_vec"], ["tgt"], axis=0)
+    w.node("Expand", ["u", "tgt"], ["out"])
+    w.output("out", ir.I64, ["B", 1])
+    module, out = _lower_and_run(w, {"x": np.zeros((2, 5), np.float32)})
+    assert "dim_values" in " ".join(module.node_ops()).lower().replace("dimvalues", "dim_values")
+    assert out["out"].shape == (2, 1) and out["out"].reshape(-1).tolist() == [4, 4]
+
+
+def test_slice_sentinel_negative_symbolic_and_stepped_bounds():
+    # lower_test.rs:418-429
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [5])
+    w.initializer("starts", np.array([1], np.int64))
+    w.initializer("ends", np.array([np.iinfo(np.int64).max], np.int64))
+    w.node("Slice", ["x", "starts", "ends"], ["out"])
+    w.output("out", ir.F32, [4])
+    x = np.array([10, 11, 12, 13, 14], np.float32)
+    assert _lower_and_run(w, {"x": x})[1]["out"].tolist() == [11, 12, 13, 14]
+    # negative bounds on a named axis, a stride, an end past the extent, and an end that is shape arithmetic
+    w = onnx.OnnxWriter()
+    w.input("m", ir.F32, ["R", 6])
+    w.input("probe", ir.F32, ["K"])
+    w.initializer("s", np.array([-4], np.int64))
+    w.initializer("e", np.array([-1], np.int64))
+    w.initializer("ax", np.array([-1], np.int64))
+    w.node("Slice", ["m", "s", "e", "ax"], ["mid"])
+    w.initializer("s0", np.array([0], np.int64))
+    w.initializer("e9", np.array([9], np.int64))
+    w.initializer("ax1", np.array([1], np.int64))
+    w.initializer("st2", np.array([2], np.int64))
+    w.node("Slice", ["m", "s0", "e9", "ax1", "st2"], ["even"])
+    w.node("Shape", ["probe"], ["k"])
+    w.initializer("ax0", np.array([0], np.int64))
+    w.node("Slice", ["m", "s0", "k", "ax0"], ["head"])
+    w.output("mid", ir.F32, ["R", 3])
+    w.output("even", ir.F32, ["R", 3])
+    w.output("head", ir.F32, ["K", 6])
+    m = np.arange(24, dtype=np.float32).reshape(4, 6)
+    out = _lower_and_run(w, {"m": m, "probe": np.zeros(3, np.float32)})[1]
+    assert np.array_equal(out["mid"], m[:, -4:-1]) and np.array_equal(out["even"], m[:, 0:9:2]) and np.array_equal(out["head"], m[:3])
+
+
+def test_squeeze_scatter_range_trilu_and_constant_nodes():
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [1, 3, 1, 4])
+    w.input("len_probe", ir.F32, ["L"])
+    w.initializer("ax", np.array([0, -2], np.int64))
+    w.node("Squeeze", ["x", "ax"], ["sq"])        # [3, 4]
+    w.node("Squeeze", ["x"], ["sq_all"])          # every extent-1 axis
+    w.node("Constant", [], ["idx"], value=np.array([[2], [0]], np.int64))
+    w.node("Constant", [], ["upd"], value=np.array([[9, 9, 9, 9], [7, 7, 7, 7]], np.float32))
+    w.node("ScatterND", ["sq", "idx", "upd"], ["sc"])
+    w.node("Trilu", ["sq"], ["up"])
+    w.node("Constant", [], ["km1"], value_int=-1)
+    w.node("Trilu", ["sq", "km1"], ["low"], upper=0)
+    # Range(2, 2 + 3·L, 3): symbolic limit, constant start and delta
+    w.node("Shape", ["len_probe"], ["l"])
+    w.initializer("three", np.array([3], np.int64))
+    w.initializer("two", np.array([2], np.int64))
+    w.node("Mul", ["l", "three"], ["l3"])
+    w.node("Add", ["l3", "two"], ["lim"])
+    w.initializer("zero_ax", np.array([0], np.int64))
+    w.node("Squeeze", ["lim", "zero_ax"], ["lim_s"])
+    w.node("Constant", [], ["start"], value_int=2)
+    w.node("Constant", [], ["delta"], value_int=3)
+    w.node("Range", ["start", "lim_s", "delta"], ["rng"])
+    for name, dt, shape in (("sq_all", ir.F32, [3, 4]), ("sc", ir.F32, [3, 4]), ("up", ir.F32, [3, 4]), ("low", ir.F32, [3, 4]), ("rng", ir.I64, ["L"])):
+        w.output(name, dt, shape)
+    x = np.arange(12, dtype=np.float32).reshape(1, 3, 1, 4) + 1
+    module, out = _lower_and_run(w, {"x": x, "len_probe": np.zeros(4, np.float32)})
+    m = x.reshape(3, 4)
+    assert np.array_equal(out["sq_all"], m)
+    want = m.copy()
+    want[2], want[0] = 9, 7
+    assert np.array_equal(out["sc"], want)
+    assert np.array_equal(out["up"], np.triu(m)) and np.array_equal(out["low"], np.tril(m, -1))
+    assert out["rng"].tolist() == [2, 5, 8, 11]
+    assert "Trilu" in module.node_ops()
+    with pytest.raises(onnx.OnnxError, match="reduction"):
+        w2 = onnx.OnnxWriter()
+        w2.input("d", ir.F32, [3])
+        w2.input("i", ir.I64, [1, 1])
+        w2.input("u", ir.F32, [1])
+        w2.node("ScatterND", ["d", "i", "u"], ["o"], reduction="add")
+        w2.output("o", ir.F32, [3])
+        onnx.load_onnx_bytes(w2.tobytes())
+
+
+@pytest.mark.parametrize("op", ["RotaryEmbedding", "GemmaRotaryEmbedding"])
+def test_rotary_embedding_rule(op):
+    heads, d, seq, maxpos = 2, 8, 3, 16
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((1, seq, heads * d)).astype(np.float32)
+    ang = np.outer(np.arange(maxpos), 1.0 / 10000 ** (np.arange(d // 2) / (d // 2))).astype(np.float32)
+    pos = np.array([[5, 6, 7]], np.int64)
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [1, "S", heads * d])
+    w.input("pos", ir.I64, [1, "S"])
+    w.initializer("cos", np.cos(ang))
+    w.initializer("sin", np.sin(ang))
+    w.node(op, ["x", "pos", "cos", "sin"], ["out"], domain="com.microsoft", num_heads=heads, interleaved=0)
+    w.output("out", ir.F32, [1, "S", heads * d])
+    module, out = _lower_and_run(w, {"x": x, "pos": pos})
+    assert module.node_ops() == ["com.microsoft." + op]
+    x4 = x.reshape(1, seq, heads, d)
+    c, s = np.cos(ang)[pos[0]][None, :, None, :], np.sin(ang)[pos[0]][None, :, None, :]
+    x1, x2 = x4[..., :d // 2], x4[..., d // 2:]
+    want = np.concatenate([x1 * c - x2 * s, x2 * c + x1 * s], -1).reshape(1, seq, heads * d)
+    assert np.abs(out["out"] - want).max() < 1e-5
+
+
+@pytest.mark.gpu
+def test_graph_of_plain_operators_on_the_device():
+    """A graph mixing the plain rules (mask building, reductions, rotary, a stepped slice) gives on the device what
+    the CPU interpreter gives: integers and booleans bit-exact, f32 within 1e-5."""
+    from onyxia_b200 import backend as be
+    heads, d = 2, 8
+    rng = np.random.default_rng(12)
+    ang = np.outer(np.arange(32), 1.0 / 10000 ** (np.arange(d // 2) / (d // 2))).astype(np.float32)
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [1, "S", heads * d])
+    w.input("pos", ir.I64, [1, "S"])
+    w.initializer("cos", np.cos(ang))
+    w.initializer("sin", np.sin(ang))
+    w.node("RotaryEmbedding", ["x", "pos", "cos", "sin"], ["rot"], domain="com.microsoft", num_heads=heads)
+    # causal mask from Range / Unsqueeze / LessOrEqual, applied with Where
+    w.node("Shape", ["pos"], ["shp"])
+    w.initializer("i1", np.array(1, np.int64))
+    w.node("Gather", ["shp", "i1"], ["s"], axis=0)
+    w.node("Constant", [], ["zero"], value_int=0)
+    w.node("Constant", [], ["one"], value_int=1)
+    w.node("Range", ["zero", "s", "one"], ["r"])
+    w.initializer("ax0", np.array([0], np.int64))
+    w.initializer("ax1", np.array([1], np.int64))
+    w.node("Unsqueeze", ["r", "ax0"], ["cols"])
+    w.node("Unsqueeze", ["r", "ax1"], ["rows"])
+    w.node("LessOrEqual", ["cols", "rows"], ["causal"])
+    w.node("Transpose", ["rot"], ["rot_t"], perm=[0, 2, 1])
+    w.node("MatMul", ["rot", "rot_t"], ["scores"])                      # [1, S, S]
+    w.node("Constant", [], ["neg"], value=np.array(-1e9, np.float32))
+    w.node("Where", ["causal", "scores", "neg"], ["masked"])
+    w.node("Softmax", ["masked"], ["p"], axis=-1)
+    w.node("ReduceMax", ["p"], ["pmax"], axes=[-1], keepdims=0)
+    w.node("ReduceMean", ["rot"], ["mean"], axes=[1], keepdims=1)
+    w.node("Trilu", ["scores"], ["lower"], upper=0)
+    w.initializer("s0", np.array([1], np.int64))
+    w.initializer("e0", np.array([1 << 40], np.int64))
+    w.initializer("ax2", np.array([2], np.int64))
+    w.initializer("st", np.array([3], np.int64))
+    w.node("Slice", ["rot", "s0", "e0", "ax2", "st"], ["strided"])
+    w.node("Tanh", ["strided"], ["act"])
+    for name, dt, shape in (("causal", ir.BOOL, ["S", "S"]), ("p", ir.F32, [1, "S", "S"]), ("pmax", ir.F32, [1, "S"]),
+                            ("mean", ir.F32, [1, 1, heads * d]), ("lower", ir.F32, [1, "S", "S"]), ("act", ir.F32, [1, "S", 5]), ("r", ir.I64, ["S"])):
+        w.output(name, dt, shape)
+    module = onnx.load_onnx_bytes(w.tobytes())
+    for seq in (1, 7, 33):
+        feed = {"x": HostTensor.from_numpy(rng.standard_normal((1, seq, heads * d)).astype(np.float32)),
+                "pos": HostTensor.from_numpy(np.arange(seq, dtype=np.int64).reshape(1, seq) % 32)}
+        want = _run(module.clone(), feed)
+        got = dict(be.run_once(be.CudaBackend((0,)), module.clone(), feed))
+        for name, t in want.items():
+            a, b = got[name].numpy(), t.numpy()
+            assert a.shape == b.shape, name
+            if b.dtype.kind == "f":
+                assert np.abs(a - b).max() <= 1e-5, name
+            else:
+                assert np.array_equal(a, b), name
