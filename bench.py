@@ -408,6 +408,9 @@ def main():
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--config-table", action="store_true",
                     help="measure the other configurations: C1 decode, the C2 MatMulNBits sweep (M = 1, 8, 64, 512), the C3 attention sweep")
+    ap.add_argument("--gqa-sweep", action="store_true",
+                    help="only run the GroupQueryAttention decode sweep (config C3; --shapes BATCHxPAST,... --windows -1,1024 --steps N) and print it")
+    ap.add_argument("--windows", default="-1,1024")
     ap.add_argument("--shapes", default="")
     ap.add_argument("--ms", default="1,8")
     ap.add_argument("--ref-prompt-len", type=int, default=PROMPT_LEN,
@@ -470,6 +473,16 @@ def main():
         shapes = [tuple(int(x) for x in t.split("x")) for t in args.shapes.split(",") if t] or C2_SHAPES
         res = gemv_sweep(be.CudaBackend((local_rank,)), shapes, [int(x) for x in args.ms.split(",")], peak)
         print(json.dumps({"metric": "int4 GEMV HBM GB/s", "unit": "GB/s", "peak": peak, "peak_source": peak_kind, "gemv_sweep": res}))
+        return
+
+    if args.gqa_sweep:
+        from onyxia_b200 import backend as be
+        peak, peak_kind = load_peaks()
+        points = [tuple(int(x) for x in t.split("x")) for t in args.shapes.split(",") if t]
+        res = []
+        for bsz, past in points or [(b, p) for b in (1, 16, 64) for p in (512, 4096, 32768)]:
+            res += gqa_sweep(be.CudaBackend((local_rank,)), peak, (bsz,), (past,), tuple(int(w) for w in args.windows.split(",")), steps=args.steps if args.steps < 64 else 12)
+        print(json.dumps({"metric": "GroupQueryAttention decode K/V GB/s", "unit": "GB/s", "peak": peak, "peak_source": peak_kind, "gqa_sweep": res}))
         return
 
     import torch  # plumbing only: rendezvous, barrier, max over ranks

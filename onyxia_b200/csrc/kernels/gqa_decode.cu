@@ -26,6 +26,10 @@
 // drains), and the f16 kernel waits only on its own asynchronous copies.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+#include <map>
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.hpp"
 #include "persist.hpp"
@@ -374,6 +378,16 @@ constexpr int kRowPad = 8;  // f16 elements
 constexpr int kKeyBlockH = 64;
 constexpr int kRingH = 4;
 
+// round_f16(exp(−|d|)) for every f16 argument (the softmax argument is ≤ 0; NaN patterns give NaN), filled once per
+// device: the decomposition's Exp computes exp in f64 and rounds once, which for an f16 argument is a function of
+// its 15 magnitude bits.
+__device__ __half g_dec_exp_lut[32768];
+
+__global__ void gqa_decode_fill_lut() {
+    for (int i = (int)global_tid(); i < 32768; i += (int)global_threads())
+        g_dec_exp_lut[i] = __double2half(exp(-(double)__half2float(__ushort_as_half((unsigned short)i))));
+}
+
 __device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -458,15 +472,18 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             const int blk = is_v ? i - n_blocks : i;
             int rows = my_n - blk * kKeyBlockH;
             rows = rows > kKeyBlockH ? kKeyBlockH : rows;
-            const __half* src = (is_v ? cv : ck) + (my_lo + (long long)blk * kKeyBlockH) * D;
-            const unsigned dst = sm_addr(ring + (i % kRingH) * kBlockBytes);
-            const long long skip = owns_new ? qpos - (my_lo + (long long)blk * kKeyBlockH) : -1;
-            for (int c = tid; c < rows * (D / 8); c += kThreads) {
-                const int r = c / (D / 8), col = c % (D / 8);
-                if (r == skip) continue;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (r * RS + col * 8) * 2), "l"(src + (long long)r * D + col * 8)
-                             : "memory");
-            }
+            // thread → 16-byte column tid % (D/8) of rows tid / (D/8) + j·(threads / (D/8)): one address pair per
+            // block, the rest are constant offsets
+            constexpr int CPR = D / 8, RPP = kThreads / CPR;  // chunks per row, rows per pass of the CTA
+            const int r0 = tid / CPR, col = tid % CPR;
+            const __half* src = (is_v ? cv : ck) + (my_lo + (long long)blk * kKeyBlockH + r0) * D + col * 8;
+            const unsigned dst = sm_addr(ring + (i % kRingH) * kBlockBytes) + (unsigned)(r0 * RS + col * 8) * 2;
+            const int skip = owns_new ? (int)(qpos - (my_lo + (long long)blk * kKeyBlockH)) - r0 : -1 - r0;
+#pragma unroll
+            for (int j = 0; j < kKeyBlockH / RPP; j++)
+                if (r0 + j * RPP < rows && j * RPP != skip)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (unsigned)(j * RPP * RS * 2)), "l"(src + (long long)j * RPP * D)
+                                 : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -609,7 +626,9 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         for (int i = tid; i < my_n; i += kThreads) {
 #pragma unroll
             for (int hh = 0; hh < GT; hh++) {
-                const float e = rndd<DT>(exp((double)rndd<DT>((double)sc[hh * kpad + i] - (double)gmax[hh])));
+                // scores and maxima are f16 values: the rounded difference is one half subtraction, its exponential a table entry
+                const __half dlt = __hsub(__float2half_rn(sc[hh * kpad + i]), __float2half_rn(gmax[hh]));
+                const float e = __half2float(g_dec_exp_lut[__half_as_ushort(dlt) & 0x7FFF]);
                 sc[hh * kpad + i] = e;
                 local[hh] += (double)e;
             }
@@ -787,7 +806,11 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     int cx_fill = 1;
     while (cx_fill < 8 && pairs * cx_fill * 2 <= 2 * sm_count()) cx_fill <<= 1;
     int cx_long = 1;  // a single CTA streams a long key range slowly: at most ≈ 1 024 keys each
-    while (cx_long < 8 && span > 1024LL * cx_long) cx_long <<= 1;
+    static const long long keys_per_cta = [] {
+        const char* e = std::getenv("ONYXIA_GQA_KEYS_PER_CTA");  // diagnostics
+        return e && std::atoll(e) >= 64 ? std::atoll(e) : 1024LL;
+    }();
+    while (cx_long < 8 && span > keys_per_cta * cx_long) cx_long <<= 1;
     if (cx > std::max(cx_fill, cx_long)) cx = std::max(cx_fill, cx_long);
     // … unless a CTA's share of the scores would not fit in shared memory
     while (cx < 8 && (span + cx - 1) / cx > 6144) cx <<= 1;
@@ -807,6 +830,21 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     const Buf bufs[11] = {q.buf, k.buf, v.buf, present_k.buf, present_v.buf, seqlens.buf, cos ? cos->buf : null,
                           sin ? sin->buf : null, out.buf, Buf{kSlotErr, 0}, dyn_t};
     dim3 grid((unsigned)cx, (unsigned)(KV * groups), (unsigned)B);
+    if (q.dtype == DT_F16 && D >= 64) {  // the f16 kernel's exponential table, once per device
+        static std::mutex mu;
+        static std::map<int, bool> done;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev]) {
+            gqa_decode_fill_lut<<<32, 256>>>();
+            if (cudaDeviceSynchronize() != cudaSuccess) {
+                cudaGetLastError();
+                return false;
+            }
+            done[dev] = true;
+        }
+    }
     const bool ok = q.dtype == DT_F16 ? launch_decode_g<DT_F16>(em, p, grid, cx, bufs, D, GT)
                                       : launch_decode_g<DT_F32>(em, p, grid, cx, bufs, D, GT);
     // A single sequence in f16: the launch can also run as an operation of the persistent step kernel.
