@@ -734,6 +734,334 @@ template <int DPL, int GT> size_t decode_h_smem(int chunk_max) {
            (size_t)8 * GT * D * 4 + 128;
 }
 
+
+// ── f16, D ≤ 128: the streaming form ────────────────────────────────────────
+// Same phases and rounding points as gqa_decode_h, but no CTA-wide staging: a warp owns every eighth 16-key tile
+// of the CTA's key range.
+//   * Scores: the lane reads 16 bytes of key rows g and g + 8 per 32-dim chunk straight from the cache into
+//     registers (next tile's loads in flight while this one is multiplied). A dot product does not care in which
+//     order the dimensions are visited, so the eight dims a lane holds serve as the k slots (2t, 2t+1, 2t+8, 2t+9)
+//     of two MMAs, against the same eight dims of q read with one 16-byte load from shared memory.
+//   * P·V needs V transposed: each warp streams its tiles through a private two-stage ring in shared memory
+//     (cp.async, warp-level waits only), reads them with ldmatrix.trans, and keeps a partial output over its
+//     keys for all D dims; the eight partial outputs are added in warp order, then across the cluster in rank
+//     order as before.
+// The newest key's row is not read from the cache (its writer may belong to another cluster): every CTA forms it
+// from the step's k / v inputs and patches it into the tile that holds its position.
+template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_decode_s(const GqaDecP p) {
+    constexpr int DT = DT_F16;
+    constexpr int D = 32 * DPL, RS = D + kRowPad;
+    constexpr int NW = kThreads / 32, NCH = D / 32;
+    constexpr int kStageBytes = 16 * RS * 2;  // one 16-key tile of padded rows
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CX = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int kpad = (p.chunk_max + 15) & ~15;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* vring = smem;                                             // [NW][2] tiles; later [NW][GT][D] partial outputs
+    __half* q_h = reinterpret_cast<__half*>(vring + NW * 2 * kStageBytes);   // [8][RS] rotated q, zero rows beyond the group
+    __half* newk_h = q_h + 8 * RS;                                           // [D] rotated new key
+    __half* newv_h = newk_h + D;                                             // [D] new value
+    __half* sp = newv_h + D;                                                // [GT][kpad + 8] scores → exponentials → probabilities (f16 values throughout)
+    double* red = reinterpret_cast<double*>(sp + GT * (kpad + 8));          // [GT][NW]
+    float* xmax = reinterpret_cast<float*>(red + GT * NW);                  // [8 ranks][GT]
+    double* xsum = reinterpret_cast<double*>(xmax + 8 * GT);                // [8 ranks][GT]
+    float* xpart = reinterpret_cast<float*>(xsum + 8 * GT);                 // [CX ranks][GT][slice], slice = ⌈D / CX⌉
+
+    pdl_trigger();
+
+    const long long b = blockIdx.z;
+    const long long kvh = blockIdx.y / p.groups, gc = blockIdx.y % p.groups;
+    const long long G = p.H / p.KV, h0 = kvh * G + gc * GT;
+    const int live = (int)(G - gc * GT < GT ? G - gc * GT : GT);
+    const long long head_base = (b * p.KV + kvh) * p.cap * D;
+    __half* ck = reinterpret_cast<__half*>(p.cache_k) + head_base;
+    __half* cv = reinterpret_cast<__half*>(p.cache_v) + head_base;
+    const long long T = *p.dyn_t;
+    long long qpos, lo, my_lo;
+    int n, chunk, my_n, n_tiles, new_rel;  // new_rel: index of the newest key within this CTA's keys, or −1
+    auto set_range = [&](long long q) {
+        qpos = q;
+        const long long hi = qpos < T - 1 ? qpos : T - 1;
+        lo = (p.window >= 0 && qpos - p.window > 0) ? qpos - p.window : 0;
+        n = (int)(hi >= lo ? hi - lo + 1 : 0);
+        chunk = (n + CX - 1) / CX;
+        my_lo = lo + (long long)rank * chunk;
+        my_n = n - rank * chunk;
+        my_n = my_n < 0 ? 0 : (my_n > chunk ? chunk : my_n);
+        if (my_n > p.chunk_max) {
+            if (tid == 0) report(p.err, ERR_SLICE_OOB, p.node, my_n, p.chunk_max);
+            my_n = p.chunk_max;
+        }
+        n_tiles = (my_n + 15) >> 4;
+        const bool owns_new = qpos <= T - 1 && n > 0 && (int)((hi - lo) / chunk) == rank;
+        new_rel = owns_new && qpos - my_lo < my_n ? (int)(qpos - my_lo) : -1;
+    };
+    set_range(T - 1 > 0 ? T - 1 : 0);
+
+    // K rows g and g + 8 of a tile, the lane's 16 bytes of every 32-dim chunk (rows past the range read the last valid row)
+    uint4 kl[NCH], kh[NCH];
+    auto load_k = [&](int tile, uint4 (&l)[NCH], uint4 (&h)[NCH]) {
+        if (tile < n_tiles) {
+            const int r_lo = min(tile * 16 + g, my_n - 1), r_hi = min(tile * 16 + g + 8, my_n - 1);
+            const uint4* pl = reinterpret_cast<const uint4*>(ck + (my_lo + r_lo) * D + 8 * t);
+            const uint4* ph = reinterpret_cast<const uint4*>(ck + (my_lo + r_hi) * D + 8 * t);
+#pragma unroll
+            for (int c = 0; c < NCH; c++) {
+                l[c] = __ldcs(pl + 4 * c);
+                h[c] = __ldcs(ph + 4 * c);
+            }
+        }
+    };
+    load_k(warp, kl, kh);  // old cache rows: no kernel of this step writes them
+    pdl_wait();
+    {
+        const long long tot = (long long)p.seqlens[b] + 1, q = tot - 1 > 0 ? tot - 1 : 0;
+        if (q != qpos) {  // a row shorter than the batch's longest
+            set_range(q);
+            load_k(warp, kl, kh);
+        }
+    }
+    long long rope_row = qpos;
+    if (p.half && rope_row >= p.cache_rows) {
+        if (tid == 0 && rank == 0) report(p.err, ERR_GATHER_OOB, p.node, rope_row, p.cache_rows);
+        rope_row = 0;
+    }
+
+    // 1. rotated q rows, the new k / v rows (every CTA keeps them in shared memory; the owner of the newest
+    // position in group 0 also appends them to the cache)
+    if (tid < D) {
+        const int e = tid;
+        const bool rot = e < 2 * p.half, first = e < p.half;
+        const int j = first ? e : e - (int)p.half, e2 = first ? e + (int)p.half : e - (int)p.half;
+        const int jc = rot ? j : 0;
+        const long long kbase = (b * p.KV + kvh) * D;
+        const __half* hq = reinterpret_cast<const __half*>(p.q);
+        const __half* hk = reinterpret_cast<const __half*>(p.k);
+        const __half* hv = reinterpret_cast<const __half*>(p.v);
+        const __half* hcos = p.half ? reinterpret_cast<const __half*>(p.cos) : hq;
+        const __half* hsin = p.half ? reinterpret_cast<const __half*>(p.sin) : hq;
+        const __half rc = hcos[p.half ? rope_row * p.half + jc : 0], rsn = hsin[p.half ? rope_row * p.half + jc : 0];
+        __half rx[GT + 1], ry[GT + 1];
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) {
+            const long long base = (b * p.H + h0 + (hh < live ? hh : 0)) * D;
+            rx[hh] = hq[base + e];
+            ry[hh] = hq[base + (rot ? e2 : e)];
+        }
+        rx[GT] = hk[kbase + e];
+        ry[GT] = hk[kbase + (rot ? e2 : e)];
+        const __half rv = hv[kbase + e];
+        const float c = rot ? __half2float(rc) : 1.f, s = rot ? __half2float(rsn) : 0.f;
+        auto turn = [&](float own, float partner) {
+            if (!rot) return own;
+            return first ? rndf<DT>(own * c) - rndf<DT>(partner * s) : rndf<DT>(own * c) + rndf<DT>(partner * s);
+        };
+#pragma unroll
+        for (int hh = 0; hh < 8; hh++)
+            q_h[hh * RS + e] = __float2half_rn(hh < GT && hh < live ? turn(__half2float(rx[hh < GT ? hh : 0]), rot ? __half2float(ry[hh < GT ? hh : 0]) : 0.f) : 0.f);
+        const __half nk = __float2half_rn(turn(__half2float(rx[GT]), rot ? __half2float(ry[GT]) : 0.f));
+        newk_h[e] = nk;
+        newv_h[e] = rv;
+        if (new_rel >= 0 && gc == 0) {
+            ck[qpos * D + e] = nk;
+            cv[qpos * D + e] = rv;
+            for (long long z = qpos + 1; z < T; z++) {  // a row shorter than the batch's longest
+                ck[z * D + e] = __float2half(0.f);
+                cv[z * D + e] = __float2half(0.f);
+            }
+        }
+    }
+    for (int i = tid; i < GT * (kpad + 8); i += kThreads) sp[i] = __float2half(0.f);  // keys past the range keep probability 0
+    cluster.sync();  // also: every CTA of the cluster has started, so its shared memory may be written remotely
+
+    // 2. scores
+    {
+        uint4 qb[NCH];  // q[head g][dims 32c + 8t … + 8]
+#pragma unroll
+        for (int c = 0; c < NCH; c++) qb[c] = *reinterpret_cast<const uint4*>(q_h + g * RS + 32 * c + 8 * t);
+        for (int tile = warp; tile < n_tiles; tile += NW) {
+            uint4 nl[NCH], nh[NCH];
+#pragma unroll
+            for (int c = 0; c < NCH; c++) nl[c] = nh[c] = make_uint4(0, 0, 0, 0);
+            load_k(tile + NW, nl, nh);
+            if (new_rel >= 0 && (new_rel >> 4) == tile) {  // the newest key's row comes from this step's input
+                const int r = new_rel & 15;
+#pragma unroll
+                for (int c = 0; c < NCH; c++) {
+                    const uint4 nv = *reinterpret_cast<const uint4*>(newk_h + 32 * c + 8 * t);
+                    if (r == g) kl[c] = nv;
+                    if (r == g + 8) kh[c] = nv;
+                }
+            }
+            float c4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < NCH; c++) {
+                mma_f16(c4, kl[c].x, kh[c].x, kl[c].y, kh[c].y, qb[c].x, qb[c].y);
+                mma_f16(c4, kl[c].z, kh[c].z, kl[c].w, kh[c].w, qb[c].z, qb[c].w);
+            }
+            // c0: (key g, head 2t)  c1: (key g, head 2t+1)  c2: (key g+8, head 2t)  c3: (key g+8, head 2t+1)
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int key = tile * 16 + g + (q >= 2 ? 8 : 0), head = 2 * t + (q & 1);
+                if (head < GT && key < my_n) sp[head * (kpad + 8) + key] = __float2half_rn(rndf<DT>(c4[q]) * p.scale);
+            }
+#pragma unroll
+            for (int c = 0; c < NCH; c++) {
+                kl[c] = nl[c];
+                kh[c] = nh[c];
+            }
+        }
+    }
+
+    // V tile → stage `s` of this warp's ring: lane → 16-byte column lane % (D/8) of rows lane / (D/8) + j·(32 / (D/8)).
+    // Rows past the range are zeroed (their probability is 0, but 0·NaN is NaN); always commits one group.
+    auto fetch_v = [&](int tile, int s) {
+        if (tile < n_tiles) {
+            constexpr int CPR = D / 8, RPP = 32 / CPR;
+            const int r0 = lane / CPR, col = lane % CPR;
+            unsigned char* stage = vring + (warp * 2 + s) * kStageBytes;
+            const __half* src = cv + (my_lo + tile * 16 + r0) * D + col * 8;
+            const unsigned dst = sm_addr(stage) + (unsigned)(r0 * RS + col * 8) * 2;
+#pragma unroll
+            for (int j = 0; j < 16 / RPP; j++) {
+                const int key = tile * 16 + r0 + j * RPP;
+                if (key == new_rel)
+                    *reinterpret_cast<uint4*>(stage + ((r0 + j * RPP) * RS + col * 8) * 2) = *reinterpret_cast<const uint4*>(newv_h + col * 8);
+                else if (key < my_n)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (unsigned)(j * RPP * RS * 2)), "l"(src + (long long)j * RPP * D) : "memory");
+                else
+                    *reinterpret_cast<uint4*>(stage + ((r0 + j * RPP) * RS + col * 8) * 2) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_v(warp, 0);       // on their way while the softmax statistics are exchanged
+    fetch_v(warp + NW, 1);
+    __syncthreads();        // every warp's scores are in shared memory
+
+    // 3. softmax statistics (as in gqa_decode_h)
+    for (int hh = warp; hh < GT; hh += NW) {
+        float m = -INFINITY;
+        for (int i = lane; i < my_n; i += 32) m = fmaxf(m, __half2float(sp[hh * (kpad + 8) + i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane < CX) cluster.map_shared_rank(xmax, lane)[rank * GT + hh] = m;
+    }
+    cluster.sync();
+    float gmax[GT];
+#pragma unroll
+    for (int hh = 0; hh < GT; hh++) {
+        float m = -INFINITY;
+        for (int r = 0; r < CX; r++) m = fmaxf(m, xmax[r * GT + hh]);
+        gmax[hh] = m;
+    }
+    {
+        double local[GT];
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) local[hh] = 0.0;
+        for (int i = tid; i < my_n; i += kThreads) {
+#pragma unroll
+            for (int hh = 0; hh < GT; hh++) {
+                const __half dlt = __hsub(sp[hh * (kpad + 8) + i], __float2half_rn(gmax[hh]));
+                const __half e = g_dec_exp_lut[__half_as_ushort(dlt) & 0x7FFF];
+                sp[hh * (kpad + 8) + i] = e;
+                local[hh] += (double)__half2float(e);
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) {
+            double v = local[hh];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) red[hh * NW + warp] = v;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            for (int hh = 0; hh < GT; hh++) {
+                double v = 0.0;
+                for (int w = 0; w < NW; w++) v += red[hh * NW + w];
+                if (lane < CX) cluster.map_shared_rank(xsum, lane)[rank * GT + hh] = v;
+            }
+        }
+    }
+    cluster.sync();
+    float total[GT];
+#pragma unroll
+    for (int hh = 0; hh < GT; hh++) {
+        double v = 0.0;
+        for (int r = 0; r < CX; r++) v += xsum[r * GT + hh];
+        total[hh] = rndd<DT>(v);
+    }
+    for (int i = tid; i < my_n; i += kThreads)
+#pragma unroll
+        for (int hh = 0; hh < GT; hh++) sp[hh * (kpad + 8) + i] = __float2half_rn(__half2float(sp[hh * (kpad + 8) + i]) / total[hh]);
+    __syncthreads();
+
+    // 4. P·V over this warp's tiles, all D dims
+    constexpr int NT = D / 8;
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    {
+        int it = 0;
+        for (int tile = warp; tile < n_tiles; tile += NW, it++) {
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group: this tile has landed
+            __syncwarp();
+            const __half* rows = reinterpret_cast<const __half*>(vring + (warp * 2 + (it & 1)) * kStageBytes);
+            // rows of the A operand are heads: the ones past the group are zero
+            const unsigned a0 = g < GT ? *reinterpret_cast<const unsigned*>(sp + g * (kpad + 8) + tile * 16 + 2 * t) : 0u;
+            const unsigned a2 = g < GT ? *reinterpret_cast<const unsigned*>(sp + g * (kpad + 8) + tile * 16 + 2 * t + 8) : 0u;
+            const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt += 2) {
+                unsigned bm[4];
+                ldsm_x4_t(bm, sm_addr(rows + ((m & 1) * 8 + r) * RS + nt * 8 + (m >> 1) * 8));
+                mma_f16(o[nt], a0, 0u, a2, 0u, bm[0], bm[1]);
+                mma_f16(o[nt + 1], a0, 0u, a2, 0u, bm[2], bm[3]);
+            }
+            __syncwarp();  // every lane has read the stage before it is refilled
+            fetch_v(tile + 2 * NW, it & 1);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // the rings are free: they take the warps' partial outputs
+    float* part = reinterpret_cast<float*>(vring);  // [NW][GT][D]
+    if (g < GT)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            part[(warp * GT + g) * D + nt * 8 + 2 * t] = o[nt][0];
+            part[(warp * GT + g) * D + nt * 8 + 2 * t + 1] = o[nt][1];
+        }
+    __syncthreads();
+    // Dim c belongs to the CTA c / slice, which adds the CX partial values in rank order.
+    const int slice = (D + CX - 1) / CX;
+    for (int i = tid; i < GT * D; i += kThreads) {
+        const int hh = i / D, c = i % D, owner = c / slice;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; w++) v += part[(w * GT + hh) * D + c];  // warp order
+        cluster.map_shared_rank(xpart, owner)[(rank * GT + hh) * slice + c - owner * slice] = v;
+    }
+    cluster.sync();
+    for (int i = tid; i < GT * slice; i += kThreads) {
+        const int hh = i / slice, c = rank * slice + i % slice;
+        if (hh >= live || c >= D) continue;
+        float v = 0.f;
+        for (int r = 0; r < CX; r++) v += xpart[(r * GT + hh) * slice + i % slice];
+        st<DT>(p.out, (b * p.H + h0 + hh) * D + c, v);
+    }
+}
+
+template <int DPL, int GT> size_t decode_s_smem(int chunk_max, int cx) {
+    constexpr int D = 32 * DPL, RS = D + kRowPad;
+    const int kpad = (chunk_max + 15) & ~15, slice = (D + cx - 1) / cx;
+    return (size_t)(kThreads / 32) * 2 * 16 * RS * 2 + (size_t)8 * RS * 2 + (size_t)2 * D * 2 + (size_t)GT * (kpad + 8) * 2 +
+           (size_t)GT * (kThreads / 32) * 8 + (size_t)8 * GT * 4 + (size_t)8 * GT * 8 + (size_t)cx * GT * slice * 4 + 128;
+}
+
 }  // namespace
 
 namespace {
@@ -752,6 +1080,13 @@ bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf 
     if constexpr (DT == DT_F16 && DPL >= 2) {  // D ≥ 64: whole n-tiles per warp
         smem = decode_h_smem<DPL, GT>(p0.chunk_max);
         fn = gqa_decode_h<DPL, GT>;
+        if constexpr (DPL <= 4) {  // D ≤ 128: the streaming form (its P·V accumulators for all of D fit in registers)
+            static const bool off = std::getenv("ONYXIA_DISABLE_GQA_STREAM") && std::atoi(std::getenv("ONYXIA_DISABLE_GQA_STREAM")) != 0;  // diagnostics
+            if (!off) {
+                smem = decode_s_smem<DPL, GT>(p0.chunk_max, cx);
+                fn = gqa_decode_s<DPL, GT>;
+            }
+        }
     }
     if (smem > 224 * 1024) return false;
     if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)fn, 224 * 1024);  // cached per device and kernel
@@ -814,6 +1149,37 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     if (cx > std::max(cx_fill, cx_long)) cx = std::max(cx_fill, cx_long);
     // … unless a CTA's share of the scores would not fit in shared memory
     while (cx < 8 && (span + cx - 1) / cx > 6144) cx <<= 1;
+    // For the streaming f16 kernel (D ≤ 128) the cluster size is chosen by cost: a CTA takes a fixed ≈ 10 µs (start,
+    // four cluster barriers, the dependent loads of the prologue) plus its keys at the rate its warps' two-deep
+    // pipelines sustain — measured ≈ 33 GB/s alone on an SM, ≈ 20 GB/s each for two; clusters of 8 / 4 leave
+    // 32 / 8 of the 296 CTA slots unused; a few waves count whole, many waves overlap their ends. Fewer, longer
+    // CTAs win as soon as the (batch row, KV head) pairs alone fill the machine.
+    static const bool model_off = std::getenv("ONYXIA_GQA_KEYS_PER_CTA") != nullptr;
+    if (q.dtype == DT_F16 && (D == 64 || D == 128) && !model_off) {
+        const double row_bytes = (double)D * 2 * 2;
+        const int sms = sm_count();
+        double best = 1e300;
+        int best_cx = cx;
+        for (int c = 1; c <= 8; c <<= 1) {
+            const long long chunk = (span + c - 1) / c;
+            if (c > 1 && chunk < 16) break;
+            const size_t bytes = 76 * 1024 + (size_t)GT * (chunk + 24) * 2;  // upper bound of the kernel's shared memory
+            if (bytes > 220 * 1024) continue;
+            const int per_sm = bytes <= 112 * 1024 ? 2 : 1;
+            const long long ctas = pairs * c;
+            long long slots = (long long)sms * per_sm;
+            if (c == 8) slots = slots * 264 / 296;
+            if (c == 4) slots = slots * 288 / 296;
+            const double waves = ctas <= 4 * slots ? (double)((ctas + slots - 1) / slots) : (double)ctas / (double)slots;
+            const bool shared = per_sm == 2 && ctas > sms;
+            const double t = waves * (10.0 + (double)chunk * row_bytes / (shared ? 20e3 : 33e3));
+            if (t < best) {
+                best = t;
+                best_cx = c;
+            }
+        }
+        cx = best_cx;
+    }
 
     GqaDecP p{};
     p.H = H;
