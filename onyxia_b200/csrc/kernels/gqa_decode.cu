@@ -88,6 +88,7 @@ struct GqaDecP {
     float scale;          // rounded to the tensor dtype
     int groups;           // query-head groups per KV head
     int chunk_max;        // keys a CTA may be given (sizes the score rows in shared memory)
+    int l2_ahead;         // streaming kernel: tiles (of this warp) by which K / V rows are asked into L2 ahead of their loads; 0: none
     int node;
 };
 
@@ -815,6 +816,15 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             }
         }
     };
+    // A tile's 16 rows are contiguous in the cache: one 128-byte line per lane asks them into L2, so
+    // that the loads issued one tile ahead find them there instead of waiting for memory.
+    auto prefetch_tile = [&](const __half* base, int tile) {
+        if (p.l2_ahead > 0 && tile < n_tiles) {
+            const char* row0 = reinterpret_cast<const char*>(base + (my_lo + (long long)tile * 16) * D);
+            const int valid = min(16, my_n - tile * 16) * D * 2;  // bytes of the tile inside the key range
+            for (int off = lane * 128; off < valid; off += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(row0 + off));
+        }
+    };
     load_k(warp, kl, kh);  // old cache rows: no kernel of this step writes them
     pdl_wait();
     {
@@ -887,6 +897,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
 #pragma unroll
             for (int c = 0; c < NCH; c++) nl[c] = nh[c] = make_uint4(0, 0, 0, 0);
             load_k(tile + NW, nl, nh);
+            prefetch_tile(ck, tile + (1 + p.l2_ahead) * NW);
             if (new_rel >= 0 && (new_rel >> 4) == tile) {  // the newest key's row comes from this step's input
                 const int r = new_rel & 15;
 #pragma unroll
@@ -1024,6 +1035,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             }
             __syncwarp();  // every lane has read the stage before it is refilled
             fetch_v(tile + 2 * NW, it & 1);
+            prefetch_tile(cv, tile + (2 + p.l2_ahead) * NW);
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -1191,6 +1203,11 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     p.scale = q.dtype == DT_F16 ? __half2float(__double2half(d.scale)) : (float)d.scale;
     p.groups = groups;
     p.chunk_max = (int)((span + cx - 1) / cx);
+    static const int l2_ahead = [] {
+        const char* e = std::getenv("ONYXIA_GQA_L2_AHEAD");  // diagnostics
+        return e ? std::max(0, std::min(std::atoi(e), 8)) : 2;
+    }();
+    p.l2_ahead = l2_ahead;
     p.node = em.node;
     const Buf null{kSlotNull, 0};
     const Buf bufs[11] = {q.buf, k.buf, v.buf, present_k.buf, present_v.buf, seqlens.buf, cos ? cos->buf : null,
