@@ -355,3 +355,51 @@ def test_gqa_batched_decode_crosses_the_cluster_size_bucket_under_graph_replay()
         d_pk, d_pv, o_pk, o_pv = got["present_key"], got["present_value"], want["present_key"], want["present_value"]
         past += 1
     assert dev.plan_stats()["graph_launches"] >= 8  # the steps did run as graph replays
+
+
+@pytest.mark.parametrize("batch,heads,kv,d,past,window", [
+    (1, 8, 2, 128, 700, -1),      # few pairs: clusters of 8 CTAs split the keys; 4 heads per KV head
+    (3, 12, 2, 128, 333, 100),    # 6 heads per KV head: two head groups, the second only half full; window; ragged
+    (40, 8, 8, 64, 300, -1),      # many pairs: one CTA each; head size 64; one head per KV head
+    (5, 8, 4, 128, 1500, 600),    # two heads per KV head; window inside a long cache; ragged
+    (2, 4, 1, 64, 37, -1),        # a key range shorter than three tiles
+])
+def test_gqa_f16_decode_steps_ragged_rows_windows_and_cluster_sizes(batch, heads, kv, d, past, window):
+    """Two consecutive decode steps of the f16 kernel for head sizes up to 128 (the second one appends in place), rows of
+    different lengths with garbage behind their last valid key, against the oracle: output and the whole present cache."""
+    from oracle import ref
+    ref.set_threads(8)
+    rng = np.random.default_rng([batch, heads, kv, d, past])
+    b = ir.GraphBuilder()
+    P = b.sym("P")
+    q = b.input("q", ir.F16, [batch, 1, heads * d])
+    k = b.input("k", ir.F16, [batch, 1, kv * d])
+    v = b.input("v", ir.F16, [batch, 1, kv * d])
+    pk = b.input("past_key", ir.F16, [batch, kv, P, d])
+    pv = b.input("past_value", ir.F16, [batch, kv, P, d])
+    sl = b.input("seqlens_k", ir.I32, [batch])
+    cfg = models.DecoderConfig("t", 0, 0, heads, kv, d, 0, 0, act_dtype=ir.F16, max_positions=past + 8)
+    c, s = models.rope_caches(cfg)
+    outs = b.composite(GQA, {"num_heads": heads, "kv_num_heads": kv, "local_window_size": window, "do_rotary": 1},
+                       [q, k, v, pk, pv, sl, b.constant(ht(c)), b.constant(ht(s))],
+                       [(ir.F16, [batch, 1, heads * d]), (ir.F16, [batch, kv, P + 1, d]), (ir.F16, [batch, kv, P + 1, d])])
+    b.output("out", outs[0])
+    b.output("present_key", outs[1])
+    b.output("present_value", outs[2])
+    mod = b.finish()
+    dev = cuda_backend().prepare(mod.clone())
+    cpu = ref.RefBackend().prepare(mod)
+    # row 0 is full; the others stop earlier (what lies behind their last key is garbage the kernels must not read into the result)
+    lens = np.array([past] + [int(x) for x in rng.integers(max(1, past // 3), past, batch - 1)], np.int32)
+    h_pk = ht(rng.standard_normal((batch, kv, past, d)).astype(f16))
+    h_pv = ht(rng.standard_normal((batch, kv, past, d)).astype(f16))
+    d_pk, d_pv = dev.upload(h_pk), dev.upload(h_pv)
+    for step in range(2):
+        feed = {"q": ht(rng.standard_normal((batch, 1, heads * d)).astype(f16)), "k": ht(rng.standard_normal((batch, 1, kv * d)).astype(f16)),
+                "v": ht(rng.standard_normal((batch, 1, kv * d)).astype(f16)), "seqlens_k": ht(lens + step)}
+        want = dict(cpu.run({**feed, "past_key": h_pk, "past_value": h_pv}))
+        got = dict(dev.run({**{n: dev.upload(x) for n, x in feed.items()}, "past_key": d_pk, "past_value": d_pv}))
+        assert_tensors_match(dev.download(got["out"]), want["out"], atol=1e-2, rtol=4e-3)
+        for name in ("present_key", "present_value"):
+            assert_tensors_match(dev.download(got[name]), want[name], atol=4e-3, rtol=4e-3)
+        d_pk, d_pv, h_pk, h_pv = got["present_key"], got["present_value"], want["present_key"], want["present_value"]
