@@ -749,10 +749,11 @@ template <int DPL, int GT> size_t decode_h_smem(int chunk_max) {
 //     order as before.
 // The newest key's row is not read from the cache (its writer may belong to another cluster): every CTA forms it
 // from the step's k / v inputs and patches it into the tile that holds its position.
-template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_decode_s(const GqaDecP p) {
+template <int DPL, int GT, int NW> __global__ void __launch_bounds__(NW * 32, 16 / NW) gqa_decode_s(const GqaDecP p) {
+    constexpr int kT = NW * 32;  // threads: 8 warps, or 4 (twice as many CTAs per SM: their fixed phases overlap better on short key ranges)
     constexpr int DT = DT_F16;
     constexpr int D = 32 * DPL, RS = D + kRowPad;
-    constexpr int NW = kThreads / 32, NCH = D / 32;
+    constexpr int NCH = D / 32;
     constexpr int kStageBytes = 16 * RS * 2;  // one 16-key tile of padded rows
     cg::cluster_group cluster = cg::this_cluster();
     const int CX = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
@@ -884,7 +885,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
             }
         }
     }
-    for (int i = tid; i < GT * (kpad + 8); i += kThreads) sp[i] = __float2half(0.f);  // keys past the range keep probability 0
+    for (int i = tid; i < GT * (kpad + 8); i += kT) sp[i] = __float2half(0.f);  // keys past the range keep probability 0
     cluster.sync();  // also: every CTA of the cluster has started, so its shared memory may be written remotely
 
     // 2. scores
@@ -973,7 +974,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         double local[GT];
 #pragma unroll
         for (int hh = 0; hh < GT; hh++) local[hh] = 0.0;
-        for (int i = tid; i < my_n; i += kThreads) {
+        for (int i = tid; i < my_n; i += kT) {
 #pragma unroll
             for (int hh = 0; hh < GT; hh++) {
                 const __half dlt = __hsub(sp[hh * (kpad + 8) + i], __float2half_rn(gmax[hh]));
@@ -1006,7 +1007,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         for (int r = 0; r < CX; r++) v += xsum[r * GT + hh];
         total[hh] = rndd<DT>(v);
     }
-    for (int i = tid; i < my_n; i += kThreads)
+    for (int i = tid; i < my_n; i += kT)
 #pragma unroll
         for (int hh = 0; hh < GT; hh++) sp[hh * (kpad + 8) + i] = __float2half_rn(__half2float(sp[hh * (kpad + 8) + i]) / total[hh]);
     __syncthreads();
@@ -1050,7 +1051,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
     __syncthreads();
     // Dim c belongs to the CTA c / slice, which adds the CX partial values in rank order.
     const int slice = (D + CX - 1) / CX;
-    for (int i = tid; i < GT * D; i += kThreads) {
+    for (int i = tid; i < GT * D; i += kT) {
         const int hh = i / D, c = i % D, owner = c / slice;
         float v = 0.f;
 #pragma unroll
@@ -1058,7 +1059,7 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
         cluster.map_shared_rank(xpart, owner)[(rank * GT + hh) * slice + c - owner * slice] = v;
     }
     cluster.sync();
-    for (int i = tid; i < GT * slice; i += kThreads) {
+    for (int i = tid; i < GT * slice; i += kT) {
         const int hh = i / slice, c = rank * slice + i % slice;
         if (hh >= live || c >= D) continue;
         float v = 0.f;
@@ -1067,11 +1068,11 @@ template <int DPL, int GT> __global__ void __launch_bounds__(kThreads, 2) gqa_de
     }
 }
 
-template <int DPL, int GT> size_t decode_s_smem(int chunk_max, int cx) {
+template <int DPL, int GT> size_t decode_s_smem(int chunk_max, int cx, int nw) {
     constexpr int D = 32 * DPL, RS = D + kRowPad;
     const int kpad = (chunk_max + 15) & ~15, slice = (D + cx - 1) / cx;
-    return (size_t)(kThreads / 32) * 2 * 16 * RS * 2 + (size_t)8 * RS * 2 + (size_t)2 * D * 2 + (size_t)GT * (kpad + 8) * 2 +
-           (size_t)GT * (kThreads / 32) * 8 + (size_t)8 * GT * 4 + (size_t)8 * GT * 8 + (size_t)cx * GT * slice * 4 + 128;
+    return (size_t)nw * 2 * 16 * RS * 2 + (size_t)8 * RS * 2 + (size_t)2 * D * 2 + (size_t)GT * (kpad + 8) * 2 +
+           (size_t)GT * nw * 8 + (size_t)8 * GT * 4 + (size_t)8 * GT * 8 + (size_t)cx * GT * slice * 4 + 128;
 }
 
 }  // namespace
@@ -1086,7 +1087,8 @@ template <int DT, int DPL, int GT> size_t decode_smem(int chunk_max) {
 }
 
 template <int DT, int DPL, int GT>
-bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf (&bufs)[11]) {
+bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf (&bufs)[11], int stream_warps) {
+    int nw = kThreads / 32;
     size_t smem = decode_smem<DT, DPL, GT>(p0.chunk_max);
     void (*fn)(const GqaDecP) = gqa_decode<DT, DPL, GT>;
     if constexpr (DT == DT_F16 && DPL >= 2) {  // D ≥ 64: whole n-tiles per warp
@@ -1095,15 +1097,16 @@ bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf 
         if constexpr (DPL <= 4) {  // D ≤ 128: the streaming form (its P·V accumulators for all of D fit in registers)
             static const bool off = std::getenv("ONYXIA_DISABLE_GQA_STREAM") && std::atoi(std::getenv("ONYXIA_DISABLE_GQA_STREAM")) != 0;  // diagnostics
             if (!off) {
-                smem = decode_s_smem<DPL, GT>(p0.chunk_max, cx);
-                fn = gqa_decode_s<DPL, GT>;
+                nw = stream_warps;
+                smem = decode_s_smem<DPL, GT>(p0.chunk_max, cx, nw);
+                fn = nw == 4 ? gqa_decode_s<DPL, GT, 4> : gqa_decode_s<DPL, GT, 8>;
             }
         }
     }
     if (smem > 224 * 1024) return false;
     if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)fn, 224 * 1024);  // cached per device and kernel
     GqaDecP p = p0;
-    em.launch(fn, grid, dim3(kThreads), (unsigned)smem, p,
+    em.launch(fn, grid, dim3((unsigned)nw * 32), (unsigned)smem, p,
               {{&p.q, bufs[0]}, {&p.k, bufs[1]}, {&p.v, bufs[2]}, {&p.cache_k, bufs[3]}, {&p.cache_v, bufs[4]},
                {&p.seqlens, bufs[5]}, {&p.cos, bufs[6]}, {&p.sin, bufs[7]}, {&p.out, bufs[8]}, {&p.err, bufs[9]},
                {&p.dyn_t, bufs[10]}},
@@ -1113,20 +1116,20 @@ bool launch_decode(Emitter& em, const GqaDecP& p0, dim3 grid, int cx, const Buf 
 }
 
 template <int DT, int GT>
-bool launch_decode_d(Emitter& em, const GqaDecP& p, dim3 grid, int cx, const Buf (&bufs)[11], long long D) {
+bool launch_decode_d(Emitter& em, const GqaDecP& p, dim3 grid, int cx, const Buf (&bufs)[11], long long D, int sw) {
     switch (D) {
-        case 32: return launch_decode<DT, 1, GT>(em, p, grid, cx, bufs);
-        case 64: return launch_decode<DT, 2, GT>(em, p, grid, cx, bufs);
-        case 128: return launch_decode<DT, 4, GT>(em, p, grid, cx, bufs);
-        case 256: return launch_decode<DT, 8, GT>(em, p, grid, cx, bufs);
+        case 32: return launch_decode<DT, 1, GT>(em, p, grid, cx, bufs, sw);
+        case 64: return launch_decode<DT, 2, GT>(em, p, grid, cx, bufs, sw);
+        case 128: return launch_decode<DT, 4, GT>(em, p, grid, cx, bufs, sw);
+        case 256: return launch_decode<DT, 8, GT>(em, p, grid, cx, bufs, sw);
         default: return false;
     }
 }
 
-template <int DT> bool launch_decode_g(Emitter& em, const GqaDecP& p, dim3 grid, int cx, const Buf (&bufs)[11], long long D, int gt) {
-    if (gt == 4) return launch_decode_d<DT, 4>(em, p, grid, cx, bufs, D);
-    if (gt == 2) return launch_decode_d<DT, 2>(em, p, grid, cx, bufs, D);
-    return launch_decode_d<DT, 1>(em, p, grid, cx, bufs, D);
+template <int DT> bool launch_decode_g(Emitter& em, const GqaDecP& p, dim3 grid, int cx, const Buf (&bufs)[11], long long D, int gt, int sw) {
+    if (gt == 4) return launch_decode_d<DT, 4>(em, p, grid, cx, bufs, D, sw);
+    if (gt == 2) return launch_decode_d<DT, 2>(em, p, grid, cx, bufs, D, sw);
+    return launch_decode_d<DT, 1>(em, p, grid, cx, bufs, D, sw);
 }
 
 }  // namespace
@@ -1161,36 +1164,51 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
     if (cx > std::max(cx_fill, cx_long)) cx = std::max(cx_fill, cx_long);
     // … unless a CTA's share of the scores would not fit in shared memory
     while (cx < 8 && (span + cx - 1) / cx > 6144) cx <<= 1;
-    // For the streaming f16 kernel (D ≤ 128) the cluster size is chosen by cost: a CTA takes a fixed ≈ 10 µs (start,
-    // four cluster barriers, the dependent loads of the prologue) plus its keys at the rate its warps' two-deep
-    // pipelines sustain — measured ≈ 33 GB/s alone on an SM, ≈ 20 GB/s each for two; clusters of 8 / 4 leave
-    // 32 / 8 of the 296 CTA slots unused; a few waves count whole, many waves overlap their ends. Fewer, longer
-    // CTAs win as soon as the (batch row, KV head) pairs alone fill the machine.
+    // For the streaming f16 kernel (D ≤ 128) the cluster size and the CTA's warp count are chosen by cost: a CTA takes
+    // a fixed ≈ 10 µs (start, four cluster barriers, the dependent loads of the prologue) plus its keys at the rate
+    // its warps' two-deep pipelines sustain — measured ≈ 33 GB/s for 8 warps alone on an SM (17 for 4), and an SM
+    // gives its resident CTAs ≈ 40 GB/s together; clusters of 8 / 4 leave 32 / 8 of the 296 CTA slots unused; a few
+    // waves count whole, many waves overlap their ends. Fewer, longer CTAs win as soon as the (batch row, KV head)
+    // pairs alone fill the machine; CTAs of 4 warps (four per SM) overlap their fixed phases better on short ranges.
     static const bool model_off = std::getenv("ONYXIA_GQA_KEYS_PER_CTA") != nullptr;
+    static const int warps_env = [] {
+        const char* e = std::getenv("ONYXIA_GQA_WARPS");  // diagnostics: 4 or 8 forces the warp count
+        return e ? std::atoi(e) : 0;
+    }();
+    int stream_warps = 8;
     if (q.dtype == DT_F16 && (D == 64 || D == 128) && !model_off) {
         const double row_bytes = (double)D * 2 * 2;
         const int sms = sm_count();
         double best = 1e300;
-        int best_cx = cx;
-        for (int c = 1; c <= 8; c <<= 1) {
-            const long long chunk = (span + c - 1) / c;
-            if (c > 1 && chunk < 16) break;
-            const size_t bytes = 76 * 1024 + (size_t)GT * (chunk + 24) * 2;  // upper bound of the kernel's shared memory
-            if (bytes > 220 * 1024) continue;
-            const int per_sm = bytes <= 112 * 1024 ? 2 : 1;
-            const long long ctas = pairs * c;
-            long long slots = (long long)sms * per_sm;
-            if (c == 8) slots = slots * 264 / 296;
-            if (c == 4) slots = slots * 288 / 296;
-            const double waves = ctas <= 4 * slots ? (double)((ctas + slots - 1) / slots) : (double)ctas / (double)slots;
-            const bool shared = per_sm == 2 && ctas > sms;
-            const double t = waves * (10.0 + (double)chunk * row_bytes / (shared ? 20e3 : 33e3));
-            if (t < best) {
-                best = t;
-                best_cx = c;
+        int best_cx = cx, best_nw = 8;
+        for (int nw = 8; nw >= 4; nw >>= 1) {
+            if (warps_env == 4 || warps_env == 8) {
+                if (nw != warps_env) continue;
+            }
+            for (int c = 1; c <= 8; c <<= 1) {
+                const long long chunk = (span + c - 1) / c;
+                if (c > 1 && chunk < 16) break;
+                if (nw == 4 && chunk > 1536) continue;  // measured: long ranges stream faster through 8-warp CTAs
+                const size_t bytes = (size_t)nw * 8960 + 6 * 1024 + (size_t)GT * (chunk + 24) * 2;  // upper bound of the kernel's shared memory
+                if (bytes > 220 * 1024) continue;
+                const int per_sm = (int)std::min<size_t>(16 / nw, (228 * 1024) / (bytes + 1024));
+                const long long ctas = pairs * c;
+                long long slots = (long long)sms * per_sm;
+                if (c == 8) slots = slots * 264 / 296;
+                if (c == 4) slots = slots * 288 / 296;
+                const double waves = ctas <= 4 * slots ? (double)((ctas + slots - 1) / slots) : (double)ctas / (double)slots;
+                const long long together = std::min<long long>(per_sm, (ctas + sms - 1) / sms);  // CTAs that share an SM
+                const double rate = std::min(nw == 8 ? 33e3 : 17e3, 40e3 / (double)together);   // bytes per µs and CTA
+                const double t = waves * (10.0 + (double)chunk * row_bytes / rate);
+                if (t < best) {
+                    best = t;
+                    best_cx = c;
+                    best_nw = nw;
+                }
             }
         }
         cx = best_cx;
+        stream_warps = best_nw;
     }
 
     GqaDecP p{};
@@ -1228,8 +1246,8 @@ bool emit_gqa_decode(Emitter& em, const GqaDesc& d, const TRef& q, const TRef& k
             done[dev] = true;
         }
     }
-    const bool ok = q.dtype == DT_F16 ? launch_decode_g<DT_F16>(em, p, grid, cx, bufs, D, GT)
-                                      : launch_decode_g<DT_F32>(em, p, grid, cx, bufs, D, GT);
+    const bool ok = q.dtype == DT_F16 ? launch_decode_g<DT_F16>(em, p, grid, cx, bufs, D, GT, stream_warps)
+                                      : launch_decode_g<DT_F32>(em, p, grid, cx, bufs, D, GT, stream_warps);
     // A single sequence in f16: the launch can also run as an operation of the persistent step kernel.
     if (ok && B == 1 && q.dtype == DT_F16 && D >= 64 && G <= 8 && p.cap < (1LL << 31) && d.cache_rows < (1LL << 31)) {
         auto op = std::make_shared<PersistOp>();
