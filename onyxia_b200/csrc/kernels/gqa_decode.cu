@@ -20,10 +20,14 @@
 //   4. V rows stream through the same ring; p = round(e / Σ) and Σ p·v in f64 per
 //      CTA; the partial outputs are added across the cluster in rank order by the
 //      CTA that owns a slice of the head dimension, rounded and stored.
+// Three kernels share these phases: gqa_decode (any dtype, f64 products; described
+// above), gqa_decode_h (f16, head size 256: 64-key blocks staged by the whole CTA,
+// tensor-core products) and gqa_decode_s (f16, head size 64 / 128: every warp
+// streams its own 16-key tiles; see its own comment).
 // Nothing spins on memory: CTAs meet at hardware cluster barriers; the generic
 // kernel's waits on bulk-copy completion are bounded (an expired wait sets the
 // error word and the CTA carries on to the barriers, so the cluster always
-// drains), and the f16 kernel waits only on its own asynchronous copies.
+// drains), and the f16 kernels wait only on their own asynchronous copies.
 #include <cooperative_groups.h>
 
 #include <cstdlib>
