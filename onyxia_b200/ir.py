@@ -92,6 +92,25 @@ class DimExpr:
     def __hash__(self):
         return hash(tuple(sorted(self.terms.items())))
 
+    def div_exact(self, divisor) -> "DimExpr | None":
+        """Exact division by a monomial (dim.rs:254-280): None when the divisor is not a single term or some term's
+        coefficient or symbols are not divisible by it."""
+        d = DimExpr.of(divisor)
+        if len(d.terms) != 1:
+            return None
+        (dsyms, dcoeff), = d.terms.items()
+        out = {}
+        for syms, coeff in self.terms.items():
+            if coeff % dcoeff:
+                return None
+            rest = list(syms)
+            for sy in dsyms:
+                if sy not in rest:
+                    return None
+                rest.remove(sy)
+            out[tuple(rest)] = out.get(tuple(rest), 0) + coeff // dcoeff
+        return DimExpr(out)
+
     def as_const(self):
         if not self.terms:
             return 0

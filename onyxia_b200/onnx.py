@@ -263,6 +263,7 @@ class _Lower:
         self.nodes, self.inits, self.outputs = nodes, inits, outputs
         self.vals: dict = {}
         self.syms: dict = {}
+        self._fresh = 0
         for name, elem, shape in inputs:
             if name in inits:
                 continue
@@ -632,22 +633,35 @@ class _Lower:
             dims = [int(v) for v in np.asarray(arr).reshape(-1)]
         out, unknown = [], -1
         for i, d in enumerate(dims):
+            if isinstance(d, DimExpr) and self._signed_const(d) is not None:
+                d = self._signed_const(d)  # a constant that came through shape arithmetic
             if isinstance(d, DimExpr):
                 out.append(d)
             elif d == 0 and not int(n.attrs.get("allowzero", 0)):
                 out.append(x.shape[i])  # 0 copies the input's dimension
             elif d == -1:
+                if unknown >= 0:
+                    raise OnnxError(f"Reshape '{n.name}' allows at most one -1")
                 unknown = i
                 out.append(None)
+            elif d < 0:
+                raise OnnxError(f"Reshape '{n.name}': invalid dimension {d}")
             else:
                 out.append(DimExpr.of(d))
-        if unknown >= 0:  # the one free dimension: only when every other extent is a constant
-            known = [d.as_const() for j, d in enumerate(out) if j != unknown]
-            total = [d.as_const() for d in x.shape]
-            if None in known or None in total:
-                raise OnnxError(f"Reshape '{n.name}': -1 beside symbolic dimensions is not lowered here")
-            rest = int(np.prod(known)) if known else 1
-            out[unknown] = DimExpr.of(int(np.prod(total)) // max(rest, 1))
+        if unknown >= 0:
+            # the one free dimension: the element count divided by the known extents when that is exact, otherwise a
+            # fresh symbol that is bound from the element count when the graph runs (rules.rs:247-259)
+            numel, known = DimExpr.of(1), DimExpr.of(1)
+            for d in x.shape:
+                numel = numel * d
+            for j, d in enumerate(out):
+                if j != unknown:
+                    known = known * d
+            inferred = numel.div_exact(known)
+            if inferred is None:
+                self._fresh += 1
+                inferred = self.b.sym(f"reshape#{self._fresh}")
+            out[unknown] = inferred
         self.set(n, 0, _Val(self.b.reshape(self.vid(x), out), x.dtype, out))
 
     def op_Unsqueeze(self, n):

@@ -600,3 +600,37 @@ def test_graph_of_plain_operators_on_the_device():
                 assert np.abs(a - b).max() <= 1e-5, name
             else:
                 assert np.array_equal(a, b), name
+
+
+def test_reshape_infers_the_free_dimension_beside_symbolic_extents():
+    """-1 in a Reshape target: the element count divided by the known extents when that is exact (a monomial
+    division, dim.rs:254-280), otherwise a symbol bound from the element count when the graph runs (rules.rs:247-259)."""
+    assert (ir.DimExpr.sym(0) * ir.DimExpr.sym(1) * 6).div_exact(ir.DimExpr.sym(1) * 3) == ir.DimExpr.sym(0) * 2
+    assert (ir.DimExpr.sym(0) * 4 + 4).div_exact(2) == ir.DimExpr.sym(0) * 2 + 2
+    assert (ir.DimExpr.sym(0) * 3).div_exact(2) is None and ir.DimExpr.of(8).div_exact(ir.DimExpr.sym(0) + 1) is None
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["B", "S", 256])
+    w.input("y", ir.F32, ["R", 3])
+    w.initializer("heads", np.array([0, 0, 4, -1], np.int64))
+    w.initializer("pairs", np.array([-1, 2], np.int64))
+    w.initializer("halves", np.array([2, -1], np.int64))
+    w.node("Reshape", ["x", "heads"], ["h"])       # 256 / 4 = 64, constant
+    w.node("Reshape", ["x", "pairs"], ["p"])       # B·S·256 / 2 = 128·B·S, symbolic and exact
+    w.node("Reshape", ["y", "halves"], ["q"])      # 3·R / 2: only known when R is
+    w.output("h", ir.F32, ["B", "S", 4, 64])
+    w.output("p", ir.F32, ["N", 2])
+    w.output("q", ir.F32, [2, "M"])
+    module = onnx.load_onnx_bytes(w.tobytes())
+    x = np.arange(2 * 3 * 256, dtype=np.float32).reshape(2, 3, 256)
+    y = np.arange(12, dtype=np.float32).reshape(4, 3)
+    out = _run(module, {"x": HostTensor.from_numpy(x), "y": HostTensor.from_numpy(y)})
+    assert np.array_equal(out["h"].numpy(), x.reshape(2, 3, 4, 64))
+    assert np.array_equal(out["p"].numpy(), x.reshape(-1, 2))
+    assert np.array_equal(out["q"].numpy(), y.reshape(2, 6))
+    with pytest.raises(onnx.OnnxError, match="at most one -1"):
+        w2 = onnx.OnnxWriter()
+        w2.input("x", ir.F32, [4, 4])
+        w2.initializer("t", np.array([-1, -1], np.int64))
+        w2.node("Reshape", ["x", "t"], ["o"])
+        w2.output("o", ir.F32, [4, 4])
+        onnx.load_onnx_bytes(w2.tobytes())
