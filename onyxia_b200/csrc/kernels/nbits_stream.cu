@@ -218,20 +218,22 @@ __device__ __forceinline__ float geglu_value(const StreamP& p, float x, float up
     return r16(hx * one_plus) * up;
 }
 
-template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2) nbits_stream(const StreamP p) {
+// ST tile records per pipeline stage, NS stages per warp: 3 × 3 by default; 1 × 3 (a third of the ring) where the
+// staged activation rows would otherwise leave room for one CTA per SM only.
+template <int MR, bool HAS_ZP, int ST = kStageTiles, int NS = kStages> __global__ void __launch_bounds__(kWarps * 32, 2) nbits_stream(const StreamP p) {
     constexpr int kTileBytes = kTileW + kTileS + (HAS_ZP ? kTileZ : 0);
-    constexpr int kStageBytes = kStageTiles * kTileBytes;
+    constexpr int kStageBytes = ST * kTileBytes;
     extern __shared__ __align__(128) unsigned char smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     // activations | aux: scratch of the prologue, later the output staging | rings | barriers | pieces
     float* aux = reinterpret_cast<float*>(smem + p.act_bytes);
     unsigned char* ring_base = smem + p.act_bytes + p.aux_bytes;
-    unsigned char* ring = ring_base + warp * (kStages * kStageBytes);
-    const unsigned bars = smem_addr(ring_base + kWarps * kStages * kStageBytes) + warp * kStages * 8;
+    unsigned char* ring = ring_base + warp * (NS * kStageBytes);
+    const unsigned bars = smem_addr(ring_base + kWarps * NS * kStageBytes) + warp * NS * 8;
 
     // pieces of row tiles shared between warps of this CTA: [warp][first / last piece][128]
-    double* pieces = reinterpret_cast<double*>(ring_base + kWarps * kStages * kStageBytes + kWarps * kStages * 8);
+    double* pieces = reinterpret_cast<double*>(ring_base + kWarps * NS * kStageBytes + kWarps * NS * 8);
 
     // This CTA owns `cta_rts` consecutive row tiles = cta_tiles consecutive tile
     // records, cut into equal ranges for its warps.
@@ -241,12 +243,12 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
     const int per = (cta_tiles + kWarps - 1) / kWarps;
     const int beg = warp * per;
     const int n_tiles = beg >= cta_tiles ? 0 : (cta_tiles - beg < per ? cta_tiles - beg : per);
-    const int n_stages = (n_tiles + kStageTiles - 1) / kStageTiles;
+    const int n_stages = (n_tiles + ST - 1) / ST;
     const unsigned char* src = p.tiles + ((long long)cta_rt0 * p.k_tiles + beg) * kTileBytes;
 
     auto issue = [&](int st, int slot) {  // lane 0 only
-        int cnt = n_tiles - st * kStageTiles;
-        if (cnt > kStageTiles) cnt = kStageTiles;
+        int cnt = n_tiles - st * ST;
+        if (cnt > ST) cnt = ST;
         const unsigned bytes = (unsigned)cnt * kTileBytes;
         mbar_expect(bars + slot * 8, bytes);
         bulk_load(smem_addr(ring + slot * kStageBytes), src + (size_t)st * kStageBytes, bytes, bars + slot * 8);
@@ -255,10 +257,10 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
     // The weights do not depend on the kernels before this one: start streaming
     // them before waiting for the producer of the activations.
     if (lane == 0) {
-        for (int s = 0; s < kStages; s++) mbar_init(bars + s * 8, 1);
+        for (int s = 0; s < NS; s++) mbar_init(bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        for (int s = 0; s < kStages && s < n_stages; s++) issue(s, s);
+        for (int s = 0; s < NS && s < n_stages; s++) issue(s, s);
     }
     __syncwarp();
     ox_trace(p.err, 1);
@@ -527,7 +529,7 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
         }
         const unsigned char* rec = ring + slot * kStageBytes;
 #pragma unroll
-        for (int j = 0; j < kStageTiles; j++) {
+        for (int j = 0; j < ST; j++) {
             if (j < remaining) {
                 const uint4* wq = reinterpret_cast<const uint4*>(rec + j * kTileBytes);
                 const uint4 wl = wq[lane], wh = wq[32 + lane];
@@ -591,10 +593,10 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
                 }
             }
         }
-        remaining -= kStageTiles;
+        remaining -= ST;
         __syncwarp();  // every lane is done with this stage before it is refilled
-        if (lane == 0 && st + kStages < n_stages) issue(st + kStages, slot);
-        if (++slot == kStages) {
+        if (lane == 0 && st + NS < n_stages) issue(st + NS, slot);
+        if (++slot == NS) {
             slot = 0;
             parity ^= 1;
         }
@@ -603,8 +605,8 @@ template <int MR, bool HAS_ZP> __global__ void __launch_bounds__(kWarps * 32, 2)
         // A copy did not land in time. Record it, then give the copies still in
         // flight a last bounded chance to land before this warp's ring goes away.
         if (lane == 0) report(p.err, ERR_WAIT_TIMEOUT, p.node, (long long)blockIdx.x, (long long)st);
-        const int issued = st + kStages < n_stages ? st + kStages : n_stages;
-        for (int s = st; s < issued; s++) mbar_wait(bars + (s % kStages) * 8, (s / kStages) & 1);
+        const int issued = st + NS < n_stages ? st + NS : n_stages;
+        for (int s = st; s < issued; s++) mbar_wait(bars + (s % NS) * 8, (s / NS) & 1);
     }
 
     ox_trace(p.err, 4);
@@ -687,7 +689,16 @@ int env_int(const char* name, int dflt, int lo, int hi) {
 }
 
 using StreamFn = void (*)(const StreamP);
-template <bool Z> StreamFn stream_fn(int mr) {
+constexpr int kSmallStageTiles = 1, kSmallStages = 3;
+template <bool Z> StreamFn stream_fn(int mr, bool small_ring) {
+    if (small_ring) {
+        switch (mr) {
+            case 2: return nbits_stream<2, Z, kSmallStageTiles, kSmallStages>;
+            case 4: return nbits_stream<4, Z, kSmallStageTiles, kSmallStages>;
+            case 8: return nbits_stream<8, Z, kSmallStageTiles, kSmallStages>;
+            default: break;
+        }
+    }
     switch (mr) {
         case 1: return nbits_stream<1, Z>;
         case 2: return nbits_stream<2, Z>;
@@ -817,8 +828,17 @@ void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TR
         p.m0 = m0;
         p.act_bytes = (p.k_tiles * 256 * mr + 127) / 128 * 128;
         p.aux_bytes = (int)aux_bytes(mr);
-        const size_t smem = (size_t)p.act_bytes + p.aux_bytes + fixed;
-        StreamFn fn = gr.has_zp ? stream_fn<true>(mr) : stream_fn<false>(mr);
+        size_t smem = (size_t)p.act_bytes + p.aux_bytes + fixed;
+        // several activation rows: if the full rings leave room for one CTA per SM only and a third of them for two,
+        // take the small rings (the kernel is bound by the instructions of the widening, not by bytes in flight)
+        const size_t fixed_small = (size_t)kWarps * kSmallStages * kSmallStageTiles * tile_bytes + (size_t)kWarps * kSmallStages * 8 +
+                                   (size_t)kWarps * 2 * 128 * sizeof(double);
+        const size_t two_per_sm = 112 * 1024;
+        static const bool small_off = env_int("ONYXIA_GEMV_SMALL_RING", 1, 0, 1) == 0;  // diagnostics
+        const bool small_ring = mr > 1 && !small_off && grid > sm_count() /* CTAs do share SMs */ && smem > two_per_sm &&
+                                (size_t)p.act_bytes + p.aux_bytes + fixed_small <= two_per_sm;
+        if (small_ring) smem = (size_t)p.act_bytes + p.aux_bytes + fixed_small;
+        StreamFn fn = gr.has_zp ? stream_fn<true>(mr, small_ring) : stream_fn<false>(mr, small_ring);
         if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)fn, (int)kSmemBudget);
         em.launch(fn, dim3((unsigned)grid), dim3(kWarps * 32), (unsigned)smem, p,
                   {{&p.a, a.buf}, {&p.tiles, tiles.buf}, {&p.err, Buf{kSlotErr, 0}}, {&p.y[0], gr.y[0].buf},
