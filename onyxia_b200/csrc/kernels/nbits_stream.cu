@@ -528,68 +528,83 @@ template <int MR, bool HAS_ZP, int ST = kStageTiles, int NS = kStages> __global_
             break;
         }
         const unsigned char* rec = ring + slot * kStageBytes;
+        // one tile record against the staged activations: 8 widenings + 8 MMAs on the two chains
+        auto tile_product = [&](int j) {
+            const uint4* wq = reinterpret_cast<const uint4*>(rec + j * kTileBytes);
+            const uint4 wl = wq[lane], wh = wq[32 + lane];
+            const __half2 s2 = reinterpret_cast<const __half2*>(rec + j * kTileBytes + kTileW)[lane];  // {row g, row g+8}
+            const __half2 s2l = __low2half2(s2), s2h = __high2half2(s2);
+            __half2 subl = sub_c, subh = sub_c, addl = add_c, addh = add_c;
+            if (HAS_ZP) {
+                const uchar2 z = reinterpret_cast<const uchar2*>(rec + j * kTileBytes + kTileW + kTileS)[lane];
+                subl = __float2half2_rn(1024.f + (float)z.x);
+                subh = __float2half2_rn(1024.f + (float)z.y);
+                addl = __float2half2_rn(-64.f - (float)z.x);
+                addh = __float2half2_rn(-64.f - (float)z.y);
+            }
+            const uint4 av0 = ap[0], av1 = ap[4 * MR], av2 = ap[8 * MR], av3 = ap[12 * MR];
+            unsigned al[4], ah[4];
+            widen_word(wl.x, subl, addl, s2l, al);
+            widen_word(wh.x, subh, addh, s2h, ah);
+            mma16816s(ca, al[0], ah[0], al[1], ah[1], av0.x, av0.y);
+            mma16816s(cb, al[2], ah[2], al[3], ah[3], av0.z, av0.w);
+            widen_word(wl.y, subl, addl, s2l, al);
+            widen_word(wh.y, subh, addh, s2h, ah);
+            mma16816s(ca, al[0], ah[0], al[1], ah[1], av1.x, av1.y);
+            mma16816s(cb, al[2], ah[2], al[3], ah[3], av1.z, av1.w);
+            widen_word(wl.z, subl, addl, s2l, al);
+            widen_word(wh.z, subh, addh, s2h, ah);
+            mma16816s(ca, al[0], ah[0], al[1], ah[1], av2.x, av2.y);
+            mma16816s(cb, al[2], ah[2], al[3], ah[3], av2.z, av2.w);
+            widen_word(wl.w, subl, addl, s2l, al);
+            widen_word(wh.w, subh, addh, s2h, ah);
+            mma16816s(ca, al[0], ah[0], al[1], ah[1], av3.x, av3.y);
+            mma16816s(cb, al[2], ah[2], al[3], ah[3], av3.z, av3.w);
+            ap += 16 * MR;
+        };
+        auto fold = [&]() {  // f32 tile sums → f64 running sum
 #pragma unroll
-        for (int j = 0; j < ST; j++) {
-            if (j < remaining) {
-                const uint4* wq = reinterpret_cast<const uint4*>(rec + j * kTileBytes);
-                const uint4 wl = wq[lane], wh = wq[32 + lane];
-                const __half2 s2 = reinterpret_cast<const __half2*>(rec + j * kTileBytes + kTileW)[lane];  // {row g, row g+8}
-                const __half2 s2l = __low2half2(s2), s2h = __high2half2(s2);
-                __half2 subl = sub_c, subh = sub_c, addl = add_c, addh = add_c;
-                if (HAS_ZP) {
-                    const uchar2 z = reinterpret_cast<const uchar2*>(rec + j * kTileBytes + kTileW + kTileS)[lane];
-                    subl = __float2half2_rn(1024.f + (float)z.x);
-                    subh = __float2half2_rn(1024.f + (float)z.y);
-                    addl = __float2half2_rn(-64.f - (float)z.x);
-                    addh = __float2half2_rn(-64.f - (float)z.y);
-                }
-                const uint4 av0 = ap[0], av1 = ap[4 * MR], av2 = ap[8 * MR], av3 = ap[12 * MR];
-                unsigned al[4], ah[4];
-                widen_word(wl.x, subl, addl, s2l, al);
-                widen_word(wh.x, subh, addh, s2h, ah);
-                mma16816s(ca, al[0], ah[0], al[1], ah[1], av0.x, av0.y);
-                mma16816s(cb, al[2], ah[2], al[3], ah[3], av0.z, av0.w);
-                widen_word(wl.y, subl, addl, s2l, al);
-                widen_word(wh.y, subh, addh, s2h, ah);
-                mma16816s(ca, al[0], ah[0], al[1], ah[1], av1.x, av1.y);
-                mma16816s(cb, al[2], ah[2], al[3], ah[3], av1.z, av1.w);
-                widen_word(wl.z, subl, addl, s2l, al);
-                widen_word(wh.z, subh, addh, s2h, ah);
-                mma16816s(ca, al[0], ah[0], al[1], ah[1], av2.x, av2.y);
-                mma16816s(cb, al[2], ah[2], al[3], ah[3], av2.z, av2.w);
-                widen_word(wl.w, subl, addl, s2l, al);
-                widen_word(wh.w, subh, addh, s2h, ah);
-                mma16816s(ca, al[0], ah[0], al[1], ah[1], av3.x, av3.y);
-                mma16816s(cb, al[2], ah[2], al[3], ah[3], av3.z, av3.w);
-                ap += 16 * MR;
-                group++;
-                seg_left--;
-                if (group == kFoldTiles || seg_left == 0) {
-                    // f32 tile sums → f64 running sum
+            for (int q = 0; q < 4; q++) {
+                acc[q] += (double)(ca[q] + cb[q]);
+                ca[q] = 0.f;
+                cb[q] = 0.f;
+            }
+            group = 0;
+        };
+        auto end_of_piece = [&]() {  // the row tile's piece is complete: hand it over, start the next row tile
+            if (seg_len == p.k_tiles) {
+                stream_stage<MR>(aux, acc, rt, lane);
+            } else {
+                double2* mine = reinterpret_cast<double2*>(pieces + (warp * 2 + (first_seg ? 0 : 1)) * 128) + 2 * lane;
+                mine[0] = make_double2(acc[0], acc[1]);
+                mine[1] = make_double2(acc[2], acc[3]);
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.0;
+            rt++;
+            ap = as_lane;
+            first_seg = false;
+            const int rest = n_tiles - consumed;
+            seg_left = p.k_tiles < rest ? p.k_tiles : rest;
+            seg_len = seg_left;
+        };
+        if (ST > 1 && remaining >= ST && seg_left >= ST) {
+            // the whole stage lies inside one row tile's piece: no per-tile bookkeeping
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        acc[q] += (double)(ca[q] + cb[q]);
-                        ca[q] = 0.f;
-                        cb[q] = 0.f;
-                    }
-                    group = 0;
-                }
-                consumed++;
-                if (seg_left == 0) {
-                    if (seg_len == p.k_tiles) {
-                        stream_stage<MR>(aux, acc, rt, lane);
-                    } else {
-                        double2* mine = reinterpret_cast<double2*>(pieces + (warp * 2 + (first_seg ? 0 : 1)) * 128) + 2 * lane;
-                        mine[0] = make_double2(acc[0], acc[1]);
-                        mine[1] = make_double2(acc[2], acc[3]);
-                    }
-                    acc[0] = acc[1] = acc[2] = acc[3] = 0.0;
-                    rt++;
-                    ap = as_lane;
-                    first_seg = false;
-                    const int rest = n_tiles - consumed;
-                    seg_left = p.k_tiles < rest ? p.k_tiles : rest;
-                    seg_len = seg_left;
+            for (int j = 0; j < ST; j++) tile_product(j);
+            seg_left -= ST;
+            consumed += ST;
+            fold();  // chains of ST tiles (never longer than kFoldTiles − 1 + ST with what the other path left)
+            if (seg_left == 0) end_of_piece();
+        } else {
+#pragma unroll
+            for (int j = 0; j < ST; j++) {
+                if (j < remaining) {
+                    tile_product(j);
+                    group++;
+                    seg_left--;
+                    if (group >= kFoldTiles || seg_left == 0) fold();
+                    consumed++;
+                    if (seg_left == 0) end_of_piece();
                 }
             }
         }
