@@ -182,6 +182,7 @@ struct StreamP {
     int n_seg;
     int geglu;                  // 0: plain outputs; 1 / 2: out = gelu_tanh / gelu_erf(segment 0)·segment 1, row tiles interleaved
     int k_tiles, row_tiles, rts_per_cta, act_bytes, aux_bytes, node;
+    int rts_extra, rts_step;  // the first rts_extra CTAs own rts_per_cta row tiles, the others rts_step fewer (0: all alike)
 };
 
 // Result fragment of one row tile → the CTA's staging area [row tile][16 rows][MR], rounded to f16.
@@ -237,8 +238,10 @@ template <int MR, bool HAS_ZP, int ST = kStageTiles, int NS = kStages> __global_
 
     // This CTA owns `cta_rts` consecutive row tiles = cta_tiles consecutive tile
     // records, cut into equal ranges for its warps.
-    const int cta_rt0 = blockIdx.x * p.rts_per_cta;
-    const int cta_rts = p.row_tiles - cta_rt0 < p.rts_per_cta ? p.row_tiles - cta_rt0 : p.rts_per_cta;
+    const int b_x = (int)blockIdx.x, b_few = b_x > p.rts_extra ? b_x - p.rts_extra : 0;  // CTAs before this one with the smaller share
+    const int cta_rt0 = b_x * p.rts_per_cta - b_few * p.rts_step;
+    const int cta_want = p.rts_per_cta - (b_x >= p.rts_extra ? p.rts_step : 0);
+    const int cta_rts = p.row_tiles - cta_rt0 < cta_want ? p.row_tiles - cta_rt0 : cta_want;
     const int cta_tiles = cta_rts * p.k_tiles;
     const int per = (cta_tiles + kWarps - 1) / kWarps;
     const int beg = warp * per;
@@ -820,6 +823,26 @@ void emit_nbits_group(Emitter& em, const NBitsGroup& gr, const TRef& a, const TR
         if (load1 <= load) {
             p.rts_per_cta = rts1;
             grid = grid1;
+        }
+    }
+
+    // Two CTAs per SM and more row tiles than CTA slots: deal the row tiles as evenly as whole tiles allow — every CTA
+    // ⌊tiles / slots⌋ of them, the first ones one more (a gate/up pair more) — instead of ⌈tiles / slots⌉ to as many
+    // CTAs as that takes, which leaves SMs with one CTA beside SMs with two full ones.
+    p.rts_extra = 1 << 30;
+    p.rts_step = 0;
+    {
+        const long long slots = (long long)sm_count() * ctas_per_sm;
+        const int step = gr.geglu ? 2 : 1;
+        long long base = p.row_tiles / slots;
+        if (gr.geglu) base &= ~1LL;
+        if (grid < slots && base >= step && p.rts_per_cta == base + step && ctas_per_sm > 1) {
+            const long long extra = (p.row_tiles - base * slots + step - 1) / step;  // CTAs with the larger share
+            if (extra > 0 && extra < slots) {
+                p.rts_extra = (int)extra;
+                p.rts_step = step;
+                grid = slots;
+            }
         }
     }
 
