@@ -109,10 +109,21 @@ class _Node:
     __slots__ = ("op", "domain", "name", "inputs", "outputs", "attrs")
 
 
-def _parse_tensor(buf):
+def _parse_tensor(buf, external=None):
+    """TensorProto → (name, dtype, dims, bytes). `external` resolves a tensor whose bytes live outside the model file
+    (data_location = EXTERNAL with location / offset / length entries, parser.rs:297-380): a callable
+    (location, offset, length or None) → uint8 array."""
     dims, dt, raw, name = [], 0, None, ""
     f32, i32, i64 = [], [], []
+    ext, ext_loc = {}, 0
     for f, w, v in _fields(buf):
+        if f == 13:  # external_data: StringStringEntryProto {key = 1, value = 2}
+            kv = {f2: bytes(v2).decode() for f2, _, v2 in _fields(v)}
+            ext[kv.get(1, "")] = kv.get(2, "")
+            continue
+        if f == 14:  # data_location
+            ext_loc = v
+            continue
         if f == 1:
             if w == 2:  # packed
                 j = 0
@@ -148,13 +159,21 @@ def _parse_tensor(buf):
     if dt not in _ONNX_DT:
         raise OnnxError(f"initializer '{name}': unsupported ONNX data type {dt}")
     dtype = _ONNX_DT[dt]
+    if ext_loc == 1:
+        if external is None or "location" not in ext:
+            raise OnnxError(f"initializer '{name}' keeps its data in an external file; load the model from its path")
+        try:
+            offset, length = int(ext.get("offset", "0")), (int(ext["length"]) if "length" in ext else None)
+        except ValueError:
+            raise OnnxError(f"initializer '{name}': invalid offset / length in external_data") from None
+        return name, dtype, dims, external(ext["location"], offset, length)
     if raw is None:
         src = f32 if dtype == ir.F32 else (i64 if dtype == ir.I64 else i32)
         raw = np.asarray(src, dtype=_NP_OF[dtype]).tobytes()
     return name, dtype, dims, np.frombuffer(raw, np.uint8).copy()
 
 
-def _parse_attr(buf):
+def _parse_attr(buf, external=None):
     name, out, ints, floats, typ = "", None, [], [], 0
     for f, w, v in _fields(buf):
         if f == 1:
@@ -166,7 +185,7 @@ def _parse_attr(buf):
         elif f == 4:
             out = bytes(v).decode()
         elif f == 5:
-            out = _parse_tensor(v)
+            out = _parse_tensor(v, external)
         elif f == 7:
             floats += list(np.frombuffer(v, "<f4")) if w == 2 else [struct.unpack("<f", struct.pack("<I", v))[0]]
         elif f == 8:
@@ -211,8 +230,9 @@ def _parse_value_info(buf):
     return name, elem, shape
 
 
-def parse_model(data: bytes):
-    """ModelProto bytes → (nodes, initializers{name: (dtype, dims, bytes)}, inputs[(name, dtype, shape)], output names)."""
+def parse_model(data: bytes, external=None):
+    """ModelProto bytes → (nodes, initializers{name: (dtype, dims, bytes)}, inputs[(name, dtype, shape)], output names).
+    `external`: see `_parse_tensor`."""
     graph = None
     for f, _, v in _fields(data):
         if f == 7:
@@ -234,13 +254,13 @@ def parse_model(data: bytes):
                 elif f2 == 4:
                     n.op = bytes(v2).decode()
                 elif f2 == 5:
-                    k, a = _parse_attr(v2)
+                    k, a = _parse_attr(v2, external)
                     n.attrs[k] = a
                 elif f2 == 7:
                     n.domain = bytes(v2).decode()
             nodes.append(n)
         elif f == 5:
-            name, dtype, dims, raw = _parse_tensor(v)
+            name, dtype, dims, raw = _parse_tensor(v, external)
             inits[name] = (dtype, dims, raw)
         elif f == 11:
             inputs.append(_parse_value_info(v))
@@ -863,21 +883,57 @@ class _Lower:
             self.set(n, i, _Val(o, q.dtype if i == 0 else past.dtype, q.shape if i == 0 else present))
 
 
-def load_onnx_bytes(data: bytes) -> ir.Module:
-    return _Lower(*parse_model(data)).lower()
+def load_onnx_bytes(data: bytes, external_buffers: dict | None = None) -> ir.Module:
+    """Model bytes → module. `external_buffers` maps the `location` of external tensor data to its bytes (the form the
+    reference uses where there is no file system, parser.rs:297-330)."""
+    resolver = None
+    if external_buffers is not None:
+        def resolver(location, offset, length):
+            if location not in external_buffers:
+                raise OnnxError(f"external data '{location}' was not provided")
+            buf = np.frombuffer(external_buffers[location], np.uint8)
+            end = len(buf) if length is None else offset + length
+            if offset < 0 or end > len(buf):
+                raise OnnxError(f"external data '{location}': bytes {offset}..{end} lie outside the buffer")
+            return buf[offset:end].copy()
+    return _Lower(*parse_model(data, resolver)).lower()
 
 
 def load_onnx(path: str) -> ir.Module:
+    """Model file → module; tensors with external data are read from the files beside it (memory-mapped, copied per tensor)."""
+    import os
+    base = os.path.dirname(os.path.abspath(path))
+    maps: dict = {}
+
+    def resolver(location, offset, length):
+        full = os.path.normpath(os.path.join(base, location))
+        if not full.startswith(base + os.sep):
+            raise OnnxError(f"external data location '{location}' leaves the model's directory")
+        if full not in maps:
+            if not os.path.isfile(full):
+                raise OnnxError(f"external data file '{location}' not found beside the model")
+            maps[full] = np.memmap(full, np.uint8, "r")
+        buf = maps[full]
+        end = len(buf) if length is None else offset + length
+        if offset < 0 or end > len(buf):
+            raise OnnxError(f"external data '{location}': bytes {offset}..{end} lie outside the file")
+        return np.array(buf[offset:end])
+
     with open(path, "rb") as f:
-        return load_onnx_bytes(f.read())
+        return _Lower(*parse_model(f.read(), resolver)).lower()
 
 
 # ── writing ──────────────────────────────────────────────────────────────
-def _tensor_proto(name, arr, onnx_dtype=None, dims=None):
+def _tensor_proto(name, arr, onnx_dtype=None, dims=None, external=None):
+    """`external` = (location, offset): the bytes are not embedded; the caller writes them to that file at that offset."""
     arr = np.ascontiguousarray(arr)
     dt = onnx_dtype if onnx_dtype is not None else _ONNX_DT_REV[{np.dtype(v): k for k, v in _NP_OF.items()}[arr.dtype]]
     out = b"".join(_f_int(1, d) for d in (dims if dims is not None else arr.shape))
-    return out + _f_int(2, dt) + _f_str(8, name) + _f_bytes(9, arr.tobytes())
+    out += _f_int(2, dt) + _f_str(8, name)
+    if external is None:
+        return out + _f_bytes(9, arr.tobytes())
+    entries = (("location", external[0]), ("offset", str(external[1])), ("length", str(arr.nbytes)))
+    return out + b"".join(_f_bytes(13, _f_str(1, k) + _f_str(2, v)) for k, v in entries) + _f_int(14, 1)
 
 
 def _attr_proto(name, v):
@@ -906,6 +962,7 @@ class OnnxWriter:
 
     def __init__(self, name="graph"):
         self.name, self.nodes, self.inits, self.inputs, self.outputs = name, [], [], [], []
+        self.external: dict = {}  # location → bytes of the initializers written as external data
 
     def node(self, op, inputs, outputs, name="", domain="", **attrs):
         body = b"".join(_f_str(1, i) for i in inputs) + b"".join(_f_str(2, o) for o in outputs)
@@ -915,7 +972,14 @@ class OnnxWriter:
         self.nodes.append(body)
         return outputs[0]
 
-    def initializer(self, name, arr, onnx_dtype=None, dims=None):
+    def initializer(self, name, arr, onnx_dtype=None, dims=None, external=None):
+        """`external`: a location (file name beside the model); the bytes are appended to `self.external[location]`."""
+        if external is not None:
+            blob = self.external.setdefault(external, bytearray())
+            blob.extend(b"\0" * (-len(blob) % 64))  # tensors start on 64-byte boundaries, as exporters write them
+            self.inits.append(_tensor_proto(name, arr, onnx_dtype, dims, external=(external, len(blob))))
+            blob.extend(np.ascontiguousarray(arr).tobytes())
+            return name
         self.inits.append(_tensor_proto(name, arr, onnx_dtype, dims))
         return name
 

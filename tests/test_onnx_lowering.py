@@ -634,3 +634,36 @@ def test_reshape_infers_the_free_dimension_beside_symbolic_extents():
         w2.node("Reshape", ["x", "t"], ["o"])
         w2.output("o", ir.F32, [4, 4])
         onnx.load_onnx_bytes(w2.tobytes())
+
+
+def test_external_tensor_data_from_files_and_from_buffers(tmp_path):
+    """Initializers whose bytes live outside the model (data_location = EXTERNAL, parser.rs:297-380): read from the file
+    beside the model, or from buffers handed over with the bytes; a missing file or range is named."""
+    rng = np.random.default_rng(3)
+    wgt = rng.standard_normal((4, 3)).astype(np.float32)
+    bias = rng.standard_normal(3).astype(np.float32)
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["B", 4])
+    w.initializer("w", wgt, external="weights.bin")
+    w.initializer("b", bias, external="weights.bin")
+    w.node("MatMul", ["x", "w"], ["xw"])
+    w.node("Add", ["xw", "b"], ["y"])
+    w.output("y", ir.F32, ["B", 3])
+    model = w.tobytes()
+    assert set(w.external) == {"weights.bin"} and len(w.external["weights.bin"]) == 64 + 12
+    (tmp_path / "m.onnx").write_bytes(model)
+    (tmp_path / "weights.bin").write_bytes(bytes(w.external["weights.bin"]))
+    x = rng.standard_normal((2, 4)).astype(np.float32)
+    want = x @ wgt + bias
+    for module in (onnx.load_onnx(str(tmp_path / "m.onnx")), onnx.load_onnx_bytes(model, {"weights.bin": bytes(w.external["weights.bin"])})):
+        got = _run(module, {"x": HostTensor.from_numpy(x)})["y"].numpy()
+        assert np.abs(got - want).max() < 1e-5
+    with pytest.raises(onnx.OnnxError, match="external file"):
+        onnx.load_onnx_bytes(model)
+    with pytest.raises(onnx.OnnxError, match="not provided"):
+        onnx.load_onnx_bytes(model, {})
+    with pytest.raises(onnx.OnnxError, match="outside the buffer"):
+        onnx.load_onnx_bytes(model, {"weights.bin": b"\0" * 16})
+    (tmp_path / "weights.bin").unlink()
+    with pytest.raises(onnx.OnnxError, match="not found"):
+        onnx.load_onnx(str(tmp_path / "m.onnx"))
