@@ -114,7 +114,7 @@ def _parse_tensor(buf, external=None):
     (data_location = EXTERNAL with location / offset / length entries, parser.rs:297-380): a callable
     (location, offset, length or None) → uint8 array."""
     dims, dt, raw, name = [], 0, None, ""
-    f32, i32, i64 = [], [], []
+    f32, i32, i64, u64, other_typed = [], [], [], [], False
     ext, ext_loc = {}, 0
     for f, w, v in _fields(buf):
         if f == 13:  # external_data: StringStringEntryProto {key = 1, value = 2}
@@ -156,6 +156,16 @@ def _parse_tensor(buf, external=None):
             name = bytes(v).decode()
         elif f == 9:
             raw = bytes(v)
+        elif f == 11:  # uint64_data
+            if w == 2:
+                j = 0
+                while j < len(v):
+                    d, j = _varint(v, j)
+                    u64.append(d)
+            else:
+                u64.append(v)
+        elif f in (6, 10):  # string_data, double_data
+            other_typed = True
     if dt not in _ONNX_DT:
         raise OnnxError(f"initializer '{name}': unsupported ONNX data type {dt}")
     dtype = _ONNX_DT[dt]
@@ -168,9 +178,47 @@ def _parse_tensor(buf, external=None):
             raise OnnxError(f"initializer '{name}': invalid offset / length in external_data") from None
         return name, dtype, dims, external(ext["location"], offset, length)
     if raw is None:
-        src = f32 if dtype == ir.F32 else (i64 if dtype == ir.I64 else i32)
-        raw = np.asarray(src, dtype=_NP_OF[dtype]).tobytes()
+        raw = _typed_to_raw(name, dtype, f32, i32, i64, u64, other_typed)
+        if raw is None:
+            if int(np.prod(dims)) if dims else 1:
+                raise OnnxError(f"initializer '{name}' ({int(np.prod(dims)) if dims else 1} elements) carries no data: raw_data, "
+                                "external data and the typed data fields are all empty")
+            raw = b""
     return name, dtype, dims, np.frombuffer(raw, np.uint8).copy()
+
+
+def _typed_to_raw(name, dtype, f32, i32, i64, u64, other_typed):
+    """The typed data fields (the older encoding some exporters still write) as little-endian bytes, like raw_data;
+    None when none is filled. int32_data carries every integer type below 32 bits, bool, and float16 as bit patterns
+    (parser.rs:221-292). A filled field that does not match the declared type is an error, not an empty weight."""
+    def mismatch(field):
+        return OnnxError(f"initializer '{name}': {field} is populated but the declared data type is {ir.DTYPE_NAMES[dtype]}")
+    if f32:
+        if dtype != ir.F32:
+            raise mismatch("float_data")
+        return np.asarray(f32, "<f4").tobytes()
+    if i64:
+        if dtype != ir.I64:
+            raise mismatch("int64_data")
+        return np.asarray(i64, "<i8").tobytes()
+    if i32:
+        a = np.asarray(i32, np.int64)
+        if dtype == ir.I32:
+            return a.astype("<i4").tobytes()
+        if dtype in (ir.U8, ir.I8):
+            return (a & 0xFF).astype(np.uint8).tobytes()
+        if dtype == ir.BOOL:
+            return (a != 0).astype(np.uint8).tobytes()
+        if dtype == ir.F16:
+            return (a & 0xFFFF).astype("<u2").tobytes()  # bit patterns in the low 16 bits
+        raise OnnxError(f"initializer '{name}': int32_data with data type {ir.DTYPE_NAMES[dtype]}")
+    if u64:
+        if dtype != ir.U32:
+            raise mismatch("uint64_data")
+        return (np.asarray(u64, np.uint64) & 0xFFFFFFFF).astype("<u4").tobytes()
+    if other_typed:
+        raise OnnxError(f"initializer '{name}': double / string typed data")
+    return None
 
 
 def _parse_attr(buf, external=None):

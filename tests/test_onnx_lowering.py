@@ -667,3 +667,46 @@ def test_external_tensor_data_from_files_and_from_buffers(tmp_path):
     (tmp_path / "weights.bin").unlink()
     with pytest.raises(onnx.OnnxError, match="not found"):
         onnx.load_onnx(str(tmp_path / "m.onnx"))
+
+
+def _tensor_bytes(dt, dims, **typed):
+    """A TensorProto written field by field: dims (1), data_type (2), float_data (4, packed), int32_data (5), int64_data (7), name (8)."""
+    import struct
+    from onyxia_b200.onnx import _f_bytes, _f_int, _f_str
+    t = b"".join(_f_int(1, d) for d in dims) + _f_int(2, dt) + _f_str(8, "w")
+    if "f" in typed:
+        t += _f_bytes(4, struct.pack(f"<{len(typed['f'])}f", *typed["f"]))
+    t += b"".join(_f_int(5, v) for v in typed.get("i32", ()))
+    t += b"".join(_f_int(7, v) for v in typed.get("i64", ()))
+    t += b"".join(_f_int(11, v) for v in typed.get("u64", ()))
+    return t
+
+
+def test_typed_data_fields_follow_the_declared_type():
+    # parser.rs:662-711: every case gives the bytes raw_data would hold
+    import struct
+    from onyxia_b200.onnx import _parse_tensor
+    cases = [((1, [2], dict(f=[1.5, -2.0])), struct.pack("<2f", 1.5, -2.0)),
+             ((7, [2], dict(i64=[-1, 7])), struct.pack("<2q", -1, 7)),
+             ((2, [3], dict(i32=[0, 128, 255])), bytes([0, 128, 255])),          # uint8 in int32_data
+             ((9, [2], dict(i32=[1, 0])), bytes([1, 0])),                        # bool in int32_data
+             ((10, [2], dict(i32=[0x3C00, 0xC000])), struct.pack("<2H", 0x3C00, 0xC000)),  # float16 bit patterns: 1.0, −2.0
+             ((6, [2], dict(i32=[-5, 9])), struct.pack("<2i", -5, 9)),
+             ((12, [1], dict(u64=[4000000000])), struct.pack("<I", 4000000000))]
+    for (dt, dims, typed), want in cases:
+        _, _, got_dims, raw = _parse_tensor(_tensor_bytes(dt, dims, **typed))
+        assert got_dims == dims and raw.tobytes() == want, (dt, typed)
+    assert _parse_tensor(_tensor_bytes(1, [0]))[3].size == 0                      # a zero-element tensor may be empty
+
+
+def test_initializer_without_data_or_with_the_wrong_typed_field_is_an_error():
+    # parser.rs:713-735: never a silently empty weight
+    from onyxia_b200.onnx import _parse_tensor
+    with pytest.raises(onnx.OnnxError, match="carries no data"):
+        _parse_tensor(_tensor_bytes(1, [4]))
+    with pytest.raises(onnx.OnnxError, match="float_data is populated"):
+        _parse_tensor(_tensor_bytes(7, [1], f=[1.0]))
+    with pytest.raises(onnx.OnnxError, match="int64_data is populated"):
+        _parse_tensor(_tensor_bytes(1, [1], i64=[3]))
+    with pytest.raises(onnx.OnnxError, match="int32_data with data type"):
+        _parse_tensor(_tensor_bytes(1, [1], i32=[3]))
