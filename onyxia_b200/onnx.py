@@ -345,8 +345,10 @@ class _Lower:
             if d not in self.syms:
                 self.syms[d] = self.b.sym(d)
             return self.syms[d]
-        if d is None or d < 0:
-            raise OnnxError("input dimension without a value or a name")
+        if d is None:  # neither a value nor a name: the symbol "unknown", as the reference names it (parser.rs:619-622)
+            return self._dim("unknown")
+        if d < 0:
+            raise OnnxError("negative input dimension")
         return DimExpr.of(d)
 
     # operands ----------------------------------------------------------

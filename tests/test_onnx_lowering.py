@@ -710,3 +710,16 @@ def test_initializer_without_data_or_with_the_wrong_typed_field_is_an_error():
         _parse_tensor(_tensor_bytes(1, [1], i64=[3]))
     with pytest.raises(onnx.OnnxError, match="int32_data with data type"):
         _parse_tensor(_tensor_bytes(1, [1], i32=[3]))
+
+
+def test_input_dimension_without_value_or_name_is_the_symbol_unknown():
+    # parser.rs:611-623
+    from onyxia_b200.onnx import _f_bytes, _f_int, _f_str
+    dims = _f_bytes(1, b"") + _f_bytes(1, _f_int(1, 3))           # one empty Dimension, then dim_value 3
+    vi = lambda name: _f_str(1, name) + _f_bytes(2, _f_bytes(1, _f_int(1, 1) + _f_bytes(2, dims)))
+    node = _f_str(1, "x") + _f_str(2, "y") + _f_str(4, "Neg")
+    graph = _f_bytes(1, node) + _f_str(2, "g") + _f_bytes(11, vi("x")) + _f_bytes(12, vi("y"))
+    module = onnx.load_onnx_bytes(_f_bytes(7, graph))
+    x = np.arange(6, dtype=np.float32).reshape(2, 3)
+    assert module.eval_input_shape(0, {"unknown": 2}) == (2, 3)
+    assert np.array_equal(_run(module, {"x": HostTensor.from_numpy(x)})["y"].numpy(), -x)
