@@ -464,11 +464,17 @@ class _Lower:
 
     def _finish_outputs(self):
         for name in self.outputs:
-            if name not in self.vals:
-                raise OnnxError(f"graph output '{name}' is not produced")
-            v = self.vals[name]
+            if name not in self.vals and name not in self.inits:
+                raise OnnxError(f"graph output '{name}' was never produced")
+            v = self.val(name)
             if v.vid is None:
-                raise OnnxError(f"graph output '{name}' is a compile-time shape value")
+                # a shape value whose elements are all constants leaves as an i64 constant; a symbolic one cannot (lib.rs:513-523)
+                vals = [self._signed_const(c) for c in v.content]
+                if None in vals:
+                    raise OnnxError(f"graph output '{name}' is a symbolic shape value")
+                dims = [d.as_const() for d in v.shape]
+                self.b.output(name, self.b.const_i64(vals, dims))
+                continue
             self.b.output(name, v.vid)
 
     def op_Identity(self, n):
@@ -574,8 +580,18 @@ class _Lower:
             self.set(n, 0, _Val(self.b.cast(x.vid, to), to, x.shape))
 
     def op_Shape(self, n):
+        """The operand's dimensions as a compile-time value, never a tensor; `start` / `end` (negative from the end,
+        clamped to the rank) select a range (rules.rs:536-563)."""
         x = self.val(n.inputs[0])
-        self.set(n, 0, _Val(None, ir.I64, [DimExpr.of(len(x.shape))], content=list(x.shape)))
+        dims = list(x.shape) if x.content is None else [DimExpr.of(len(x.content))]
+        rank = len(dims)
+
+        def bound(v):
+            v = v + rank if v < 0 else v
+            return max(0, min(rank, v))
+        start, end = bound(int(n.attrs.get("start", 0))), bound(int(n.attrs.get("end", rank)))
+        picked = dims[min(start, end):end]
+        self.set(n, 0, _Val(None, ir.I64, [DimExpr.of(len(picked))], content=picked))
 
     def op_Gather(self, n):
         data, axis = self.val(n.inputs[0]), int(n.attrs.get("axis", 0))

@@ -723,3 +723,27 @@ def test_input_dimension_without_value_or_name_is_the_symbol_unknown():
     x = np.arange(6, dtype=np.float32).reshape(2, 3)
     assert module.eval_input_shape(0, {"unknown": 2}) == (2, 3)
     assert np.array_equal(_run(module, {"x": HostTensor.from_numpy(x)})["y"].numpy(), -x)
+
+
+def test_graph_outputs_that_are_shape_values():
+    # lib.rs:506-529: constant shape values leave as i64 constants, symbolic ones are refused, unknown names are named
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["B", 3, 5])
+    w.node("Shape", ["x"], ["shp"], start=1)
+    w.node("Neg", ["x"], ["y"])
+    w.output("shp", ir.I64, [2])
+    w.output("y", ir.F32, ["B", 3, 5])
+    out = _run(onnx.load_onnx_bytes(w.tobytes()), {"x": HostTensor.from_numpy(np.zeros((2, 3, 5), np.float32))})
+    assert out["shp"].numpy().tolist() == [3, 5] and out["shp"].numpy().dtype == np.int64
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, ["B", 3])
+    w.node("Shape", ["x"], ["shp"])
+    w.output("shp", ir.I64, [2])
+    with pytest.raises(onnx.OnnxError, match="symbolic shape value"):
+        onnx.load_onnx_bytes(w.tobytes())
+    w = onnx.OnnxWriter()
+    w.input("x", ir.F32, [1])
+    w.node("Neg", ["x"], ["y"])
+    w.output("z", ir.F32, [1])
+    with pytest.raises(onnx.OnnxError, match="never produced"):
+        onnx.load_onnx_bytes(w.tobytes())
