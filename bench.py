@@ -500,10 +500,10 @@ def main():
     from onyxia_b200 import ir, llm
     from onyxia_b200.ir import HostTensor
 
+    backend = be.CudaBackend((local_rank,))  # first: without a CUDA device this raises, and nothing below runs on the CPU instead
     cfg, module, build_s = build_model(depth=args.depth)
     cpu_module = module.clone() if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
     e2e_module = module.clone()
-    backend = be.CudaBackend((local_rank,))
     lm = llm.LlmSession(backend, module, 4096)
     sess = lm.session
     rng = np.random.default_rng(0)
